@@ -1,0 +1,180 @@
+/*
+ * tango_b200 -- C ABI of the B200 (sm_100a) library behind Tango's quantized
+ * GNN-training operators.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers and sizes,
+ * launches on the CUDA stream it is given (a cudaStream_t passed as void*),
+ * never allocates or frees device memory, never synchronises the device and
+ * never exits the process: it returns TANGO_OK (0) or a negative error code
+ * (see tango_strerror).  All pointers are device pointers unless a comment says
+ * "host".  The device that owns the pointers must be current in the calling
+ * thread.  No global mutable state is kept, so the library may be entered from
+ * several host threads (PyTorch's autograd thread runs the backward calls).
+ *
+ * Each declaration cites the reference interface it replaces as file:line
+ * inside the Tango repository (cuda/src/cuda.cpp holds its pybind table).
+ *
+ * Layout conventions
+ *   - matrices are row-major with an explicit leading dimension (elements);
+ *   - int8 feature/operand matrices use a leading dimension that is a multiple
+ *     of 16 bytes on the fast paths; columns in [cols, ld) must be zero (the
+ *     quantizers here write them as zero);
+ *   - sparse structure is CSR with int32 `indptr`/`indices`; an optional
+ *     `edge_ids` array maps a CSR slot to the id of the edge stored there;
+ *   - scales are 1-element fp32 tensors in device memory, as in the reference.
+ */
+#ifndef TANGO_B200_H_
+#define TANGO_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TANGO_OK 0
+#define TANGO_EINVAL (-1)   /* bad argument (null pointer, negative size, bad mode) */
+#define TANGO_EALIGN (-2)   /* pointer or leading dimension not aligned as required */
+#define TANGO_ECUDA (-3)    /* a CUDA runtime/driver call failed (see tango_last_cuda_error) */
+#define TANGO_ETIMEOUT (-4) /* a bounded device-side wait expired (reported via status word) */
+#define TANGO_ESIZE (-5)    /* size beyond what the entry point supports */
+
+#define TANGO_ROUND_TRUNC 0      /* (int8)(x/s): the reference's fused forward GEMM, cuda/src/iterator.h:155-164 */
+#define TANGO_ROUND_NEAREST 1    /* rint + clamp: the reference's quantize kernel, cuda/src/quantization.cu:6-35 */
+#define TANGO_ROUND_STOCHASTIC 2 /* floor(x/s + u), u from Philox4x32-10 keyed by (seed, call) -- not in the reference */
+
+#define TANGO_OP_ADD 0
+#define TANGO_OP_SUB 1
+#define TANGO_OP_MUL 2
+#define TANGO_OP_DIV 3
+
+typedef void *tango_stream_t; /* cudaStream_t */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int tango_version(void);
+/* Static string for an error code. */
+const char *tango_strerror(int code);
+/* cudaError_t of the last failing CUDA call made by this thread inside the library (0 if none). */
+int tango_last_cuda_error(void);
+
+/* ---------------------------------------------------------------- quantisation */
+
+/* scale[0] = max|x| / 127 over a [rows, cols] fp32 matrix with leading dimension ld.
+ * If row_scale != NULL the maximum is taken over x[r,c] * row_scale[r].
+ * Replaces get_scale (cuda/src/cuda.cpp:186, cuda/src/quantization.cu:45-93). */
+int tango_absmax_scale(const float *x, int64_t rows, int64_t cols, int64_t ld, const float *row_scale,
+                       float *scale, tango_stream_t stream);
+
+/* q[r,c] = round_mode(x[r,c] * (1/scale[0])) clamped to [-127,127]; columns [cols, ldq) of q are set to 0.
+ * row_scale (optional) multiplies x[r,:] first.  `seed`/`call` key the stochastic stream; the random
+ * number of element (r,c) depends only on (seed, call, r*cols + c).
+ * Replaces quantize (cuda/src/cuda.cpp:185, cuda/src/quantization.cu:17-43). */
+int tango_quantize(const float *x, int64_t rows, int64_t cols, int64_t ldx, const float *row_scale,
+                   const float *scale, int8_t *q, int64_t ldq, int mode, uint64_t seed, uint64_t call,
+                   tango_stream_t stream);
+
+/* out[c, r] = nearest(x[r, c] / scale[0]) for x fp32 [nrow, ncol] contiguous -> int8 [ncol, nrow] contiguous.
+ * Replaces transpose_quant (cuda/src/cuda.cpp:187, cuda/src/quantization.cu:95-167). */
+int tango_quantize_transpose(const float *x, int64_t nrow, int64_t ncol, const float *scale, int8_t *out,
+                             tango_stream_t stream);
+
+/* ---------------------------------------------------------------- int8 GEMMs (tcgen05 kind::i8) */
+
+/* Bytes of scratch tango_qgemm_dw needs for an [n, k] weight gradient. */
+int64_t tango_qgemm_dw_workspace_bytes(int64_t n, int64_t k);
+
+/* Y[M,N] = float(Xq[M,K] . Wq[N,K]^T) * (sx[0]*sw[0]) (+ bias[N]); if scale_y != NULL it must hold 0 on entry and
+ * receives max|Y|/127.  `status` is a 1-int device word that receives TANGO_ETIMEOUT if a bounded wait expires.
+ * Replaces the GEMM + epilogue of QGEMM_forward (cuda/src/cuda.cpp:11-16,183, cuda/src/QGEMM_forward.cu:125-157). */
+int tango_qgemm_nt(const int8_t *xq, int64_t ldx, const int8_t *wq, int64_t ldw, int64_t m, int64_t n, int64_t k,
+                   const float *sx, const float *sw, const float *bias, float *y, int64_t ldy, float *scale_y,
+                   int *status, tango_stream_t stream);
+
+/* The reference's fused forward: quantises X[M,K] and W[N,K] (writing xq, wq) with the given rounding mode and the
+ * scales sx, sw, then the GEMM above.  Replaces QGEMM_forward (cuda/src/cuda.cpp:183, cuda/kernels.py:79-94). */
+int tango_qgemm_forward(const float *x, int64_t ldx_f, const float *w, int64_t ldw_f, int64_t m, int64_t n, int64_t k,
+                        const float *sx, const float *sw, int8_t *xq, int64_t ldxq, int8_t *wq, int64_t ldwq,
+                        const float *bias, float *y, int64_t ldy, float *scale_y, int mode, uint64_t seed,
+                        uint64_t call, int *status, tango_stream_t stream);
+
+/* dX[M,K] = float(dYq[M,N] . Wq[N,K]) * (sdy[0]*sw[0]).
+ * Replaces QGEMM_backward_gradX (cuda/src/cuda.cpp:191, cuda/src/QGEMM_backward.cu:21-48). */
+int tango_qgemm_dx(const int8_t *dyq, int64_t lddy, const int8_t *wq, int64_t ldw, int64_t m, int64_t n, int64_t k,
+                   const float *sdy, const float *sw, float *dx, int64_t lddx, int *status, tango_stream_t stream);
+
+/* dW[N,K] = float(dYq^T[N,M] . Xq[M,K]) * (sdy[0]*sx[0]); split over M with int32 atomics into `workspace`
+ * (tango_qgemm_dw_workspace_bytes; contents on entry are irrelevant), then dequantised.
+ * Replaces QGEMM_backward_gradW (cuda/src/cuda.cpp:192, cuda/src/QGEMM_backward.cu:50-113). */
+int tango_qgemm_dw(const int8_t *dyq, int64_t lddy, const int8_t *xq, int64_t ldx, int64_t m, int64_t n, int64_t k,
+                   const float *sdy, const float *sx, float *dw, int64_t lddw, void *workspace,
+                   int64_t workspace_bytes, int *status, tango_stream_t stream);
+
+/* ---------------------------------------------------------------- SpMM (CSR, int8 features, int32 accumulation) */
+
+/* Optional schedule for rows too long for one warp.  A row whose degree exceeds `split_threshold` is cut into
+ * `n_units` units (vrow, begin, end, slot) stored as int32 quadruples; each unit adds its partial sums into
+ * int32 scratch `ws` ([n_heavy * nseg, ws_ld]) and the rows listed in `heavy_rows` ([n_heavy]) are finished by a
+ * second kernel.  With n_units == 0 every row is handled by one warp. */
+typedef struct tango_spmm_plan {
+    const int32_t *units;      /* [n_units, 4] */
+    int64_t n_units;
+    const int32_t *heavy_rows; /* [n_heavy] */
+    int64_t n_heavy;
+    int32_t *ws;               /* [n_heavy * nseg, ws_ld] int32 scratch */
+    int64_t ws_ld;             /* >= round_up(F, 16) */
+    int32_t split_threshold;
+} tango_spmm_plan;
+
+/* out[v,:] = sum_k scales[k] * float(sum_{j in segment k of row v} Nq[indices[j], :]) for v < n_rows.
+ * `indptr` has n_rows*nseg + 1 entries: row v owns the nseg consecutive segments v*nseg .. v*nseg+nseg-1, segment k
+ * holding the neighbours that live on shard k (nseg = 1 and one scale on a single GPU).  Optional fused epilogue:
+ * out = act((acc) * row_scale[v] + bias[:]) with relu != 0 selecting max(.,0); out_absmax (optional, must hold 0)
+ * receives max|out|/127.  Replaces csr_SPMM (cuda/src/cuda.cpp:194, cuda/src/SPMM.cu:23-68). */
+int tango_spmm_copy_u(const int32_t *indptr, const int32_t *indices, int64_t n_rows, int nseg, const int8_t *nq,
+                      int64_t ldn, int64_t f, const float *scales, const float *row_scale, const float *bias,
+                      int relu, float *out, int64_t ldo, float *out_absmax, const tango_spmm_plan *plan /* host */,
+                      tango_stream_t stream);
+
+/* out[v,h,:] = scale[0] * float(sum_j Eq[eid(j), h] * Nq[indices[j], h, :]); Nq is [*, H*D] with leading dimension
+ * ldn, Eq is int8 [E, H] contiguous in edge-id order, eid(j) = edge_ids ? edge_ids[j] : j.
+ * Replaces multi_cusparse_SPMM (cuda/src/cuda.cpp:138-160,196, cuda/src/SPMM.cu:70-130, cuda/kernels.py:122-136). */
+int tango_spmm_u_mul_e(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids, int64_t n_rows,
+                       const int8_t *nq, int64_t ldn, int h, int d, const int8_t *eq, const float *scale, float *out,
+                       int64_t ldo, const tango_spmm_plan *plan /* host */, tango_stream_t stream);
+
+/* out[v,:] = scale[0] * float(sum_{j in row v} Zq[eid(j), :]) -- sum of the int8 edge features incident to a node.
+ * Replaces incidence_SPMM (cuda/src/cuda.cpp:198, cuda/src/SPMM.cu:259-303). */
+int tango_spmm_incidence(const int32_t *indptr, const int32_t *edge_ids, int64_t n_rows, const int8_t *zq, int64_t ldz,
+                         int64_t f, const float *scale, float *out, int64_t ldo, const tango_spmm_plan *plan /* host */,
+                         tango_stream_t stream);
+
+/* ---------------------------------------------------------------- SDDMM */
+
+/* out[e,h] = float(sum_d Uq[src[e],h,d] * Vq[dst[e],h,d]) * (su[0]*sv[0]); out is [E, H] contiguous.
+ * out_absmax (optional, must hold 0) receives max|out|/127.
+ * Replaces mySDDMM_int8 with op "dot" (cuda/src/cuda.cpp:201, cuda/src/SDDMM.cu:8-47,124-153). */
+int tango_sddmm_dot(const int32_t *src, const int32_t *dst, int64_t n_edges, const int8_t *uq, int64_t ldu,
+                    const int8_t *vq, int64_t ldv, int h, int d, const float *su, const float *sv, float *out,
+                    float *out_absmax, tango_stream_t stream);
+
+/* out[e,:] = op(float(Uq[src[e],:])*su[0], float(Vq[dst[e],:])*sv[0]) over `dim` features; out is [E, dim] contiguous.
+ * Replaces mySDDMM_int8 with op add/sub/mul/div (cuda/src/cuda.cpp:201, cuda/src/SDDMM.cu:49-100,154-176). */
+int tango_sddmm_elementwise(int op, const int32_t *src, const int32_t *dst, int64_t n_edges, const int8_t *uq,
+                            int64_t ldu, const int8_t *vq, int64_t ldv, int64_t dim, const float *su, const float *sv,
+                            float *out, float *out_absmax, tango_stream_t stream);
+
+/* ---------------------------------------------------------------- fused GAT edge pipeline */
+
+/* For every destination row v of a CSC (indptr, indices = source ids, edge_ids):
+ *   z[j] = leaky_relu(float(elq[indices[j],h])*sl[0] + float(erq[v,h])*sr[0], slope)
+ *   a[eid(j),h] = exp(z[j]-max_v)/sum_v
+ * i.e. the reference's sddmm_u_add_v -> LeakyReLU -> dgl edge_softmax chain (evaluation/test_gat.py:141-146,
+ * cuda/SDDMM.py:10-20) in one pass; `a` is fp32 [E, H] in edge-id order. */
+int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids, int64_t n_rows,
+                           const int8_t *elq, const int8_t *erq, int h, const float *sl, const float *sr, float slope,
+                           float *a, tango_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TANGO_B200_H_ */

@@ -1,0 +1,93 @@
+"""Quantized linear layer: the autograd surface of the reference's cuda/QLinear.py (Qlinear_func,
+Qlinear_func_reduce, QgemmNT_func, QLinear) on top of the tcgen05 int8 GEMMs."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+from torch.autograd.function import Function, once_differentiable
+
+from . import config, kernels
+
+
+def _forward_common(ctx, X, W, b, want_scale):
+    """Forward of cuda/QLinear.py:28-35,52-60: absmax scales of X and W, fused quantize + GEMM (+ output scale),
+    and the quantized operands cached for the backward pass."""
+    sX = kernels.cuda_kernels.get_scale(X)
+    sW = kernels.cuda_kernels.get_scale(W)
+    Xq = kernels.alloc_int8(X.shape, X.device)
+    Wq = kernels.alloc_int8(W.shape, X.device)
+    res = kernels.QGEMM_forward(X, Xq, sX, W, Wq, sW, b, want_scale, mode=config.mode_for("gemm_fwd"),
+                                seed=config.seed())
+    ctx.backward_cache = (Xq, sX, Wq, sW, b)
+    return res
+
+
+def _backward_common(ctx, grad_output):
+    """Backward of cuda/QLinear.py:37-47,62-72: quantize dY (nearest), dX and dW by int8 GEMMs, bias grad in fp32."""
+    Xq, sX, Wq, sW, b = ctx.backward_cache
+    dYq, sdY = kernels.quantize(grad_output, mode=config.mode_for("quantize"), seed=config.seed())
+    dX, dW = kernels.QGEMM_backward(dYq, Xq, Wq, sdY, sX, sW, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+    db = grad_output.sum(0) if (b is not None and ctx.needs_input_grad[2]) else None
+    return dX, dW, db
+
+
+class Qlinear_func(Function):
+    @staticmethod
+    def forward(ctx, X, W, b=None):
+        return _forward_common(ctx, X, W, b, False)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        return _backward_common(ctx, grad_output)
+
+
+class Qlinear_func_reduce(Function):
+    """Also returns max|Y|/127 computed in the GEMM epilogue, so the consumer can skip its own absmax pass."""
+
+    @staticmethod
+    def forward(ctx, X, W, b=None):
+        out, scale_out = _forward_common(ctx, X, W, b, True)
+        ctx.mark_non_differentiable(scale_out)
+        return out, scale_out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output, _grad_scale):
+        return _backward_common(ctx, grad_output)
+
+
+class QgemmNT_func(Function):
+    """A . B^T with both operands quantized per call (cuda/QLinear.py:9-23, the reference's legacy cuBLAS path)."""
+
+    @staticmethod
+    def forward(ctx, A, B):
+        ctx.save_for_backward(A, B)
+        return kernels.cuda_kernels.QgemmNT(A, B)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        A, B = ctx.saved_tensors
+        gA = kernels.cuda_kernels.QgemmNN(grad_output, B) if ctx.needs_input_grad[0] else None
+        gB = kernels.cuda_kernels.QgemmTN(grad_output, A) if ctx.needs_input_grad[1] else None
+        return gA, gB
+
+
+class QLinear(nn.Linear):
+    """nn.Linear whose matmuls run as int8 GEMMs (cuda/QLinear.py:75-93).  The reference requires K % 4 == 0; any K
+    is accepted here because the quantized operands are stored with rows padded to 16 bytes."""
+
+    def __init__(self, in_features, out_features, bias=True):
+        super().__init__(in_features, out_features, bias)
+        self.isReduce = False
+
+    def enable_reduce(self):
+        self.isReduce = True
+
+    def forward(self, input):
+        t = input.reshape(-1, input.size(-1))
+        out_shape = input.shape[:-1] + (self.weight.size(0),)
+        if self.isReduce:
+            out, scale = Qlinear_func_reduce.apply(t, self.weight, self.bias)
+            return out.reshape(out_shape), scale
+        return Qlinear_func.apply(t, self.weight, self.bias).reshape(out_shape)

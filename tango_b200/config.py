@@ -1,0 +1,34 @@
+"""Process-wide quantisation settings (rounding mode and seed of the stochastic-rounding stream).
+
+The reference has no such switch: its stand-alone quantizer rounds to nearest (cuda/src/quantization.cu:6-15) and its
+fused forward GEMM truncates (cuda/src/iterator.h:155-164).  `reference` keeps exactly those per-call-site modes;
+`nearest` and `stochastic` apply one mode everywhere.
+"""
+from __future__ import annotations
+
+from ._lib import ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_TRUNC
+
+_state = {"rounding": "reference", "seed": 0}
+
+
+def set_rounding(mode: str = "reference", seed: int = 0) -> None:
+    if mode not in ("reference", "nearest", "trunc", "stochastic"):
+        raise ValueError(mode)
+    _state["rounding"] = mode
+    _state["seed"] = int(seed)
+
+
+def get_rounding() -> str:
+    return _state["rounding"]
+
+
+def seed() -> int:
+    return _state["seed"]
+
+
+def mode_for(site: str) -> int:
+    """Rounding mode for a call site: 'gemm_fwd' (the fused forward GEMM) or 'quantize' (everything else)."""
+    r = _state["rounding"]
+    if r == "reference":
+        return ROUND_TRUNC if site == "gemm_fwd" else ROUND_NEAREST
+    return {"nearest": ROUND_NEAREST, "trunc": ROUND_TRUNC, "stochastic": ROUND_STOCHASTIC}[r]

@@ -1,0 +1,65 @@
+// Shared helpers for the tango_b200 kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tango_b200.h"
+
+namespace tango {
+
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return TANGO_ECUDA;
+}
+
+#define TANGO_CUDA_TRY(expr)                                   \
+    do {                                                       \
+        cudaError_t _e = (expr);                               \
+        if (_e != cudaSuccess) return ::tango::cuda_fail(_e);  \
+    } while (0)
+
+#define TANGO_LAUNCH_CHECK() TANGO_CUDA_TRY(cudaPeekAtLastError())
+
+inline bool aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+inline int64_t ceil_div(int64_t x, int64_t m) { return (x + m - 1) / m; }
+
+constexpr int kNumSMs = 148;  // B200
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Non-negative floats order like their bit patterns, so an integer atomicMax is an exact float max.
+__device__ __forceinline__ void atomic_max_nonneg(float *addr, float v) {
+    atomicMax(reinterpret_cast<int *>(addr), __float_as_int(v));
+}
+
+// Block-wide max of a non-negative value, then one atomic per block of (max / 127).
+__device__ __forceinline__ void block_absmax_to_scale(float thread_max, float *scale_out) {
+    __shared__ float s_warp[32];
+    float m = warp_max(thread_max);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    if (lane == 0) s_warp[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        m = lane < nwarp ? s_warp[lane] : 0.f;
+        m = warp_max(m);
+        if (lane == 0) atomic_max_nonneg(scale_out, __fdiv_rn(m, 127.0f));
+    }
+}
+
+__device__ __forceinline__ float inv_scale(float s) { return s == 0.f ? 0.f : __fdiv_rn(1.0f, s); }
+
+// sign-extended byte i (0..3) of a packed word, added into acc: dp4a with a one-hot selector.
+template <int I>
+__device__ __forceinline__ int add_byte(uint32_t w, int acc) {
+    return __dp4a((int)w, (int)(1u << (8 * I)), acc);
+}
+
+}  // namespace tango

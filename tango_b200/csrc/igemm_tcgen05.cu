@@ -1,0 +1,464 @@
+// int8 x int8 -> int32 GEMMs for the quantized linear layer on sm_100a:
+// tcgen05.mma kind::i8 (M=128, N<=256, K=32 per instruction), operands staged in shared memory by TMA with the
+// 128-byte swizzle, accumulators in tensor memory, read back with tcgen05.ld for the dequantising epilogue.
+//
+// One kernel serves the three products of the layer by choosing the operand "major" per call:
+//   forward  Y [M,N]  = Xq[M,K]  . Wq[N,K]^T   A K-major,  B K-major
+//   dX       dX[M,K]  = dYq[M,N] . Wq[N,K]     A K-major,  B MN-major (reduction index is the row of Wq)
+//   dW       dW[N,K]  = dYq^T    . Xq[M,K]     A MN-major, B MN-major, split over the long reduction (M) with
+//                                              int32 atomics into scratch, then a small dequantising kernel.
+// so no transposed copies of the quantized tensors are ever written.
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns tensor memory and issues the MMAs (one lane), warps 2-5 run the
+// epilogue (each reads the 32 TMEM lanes it may access).  Every mbarrier wait is bounded: after ~2 s without
+// progress the kernel records TANGO_ETIMEOUT in the status word, lets outstanding copies land, frees its tensor
+// memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace tango {
+
+constexpr int kBlockK = 128;          // bytes of reduction per pipeline stage
+constexpr int kTileM = 128;           // UMMA M
+constexpr int kABytes = kTileM * kBlockK;  // 16 KiB either major
+constexpr int kMaxStages = 8;
+constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
+
+struct GemmParams {
+    int M, N, K;     // D is [M, N], reduction length K
+    int n_tile;      // UMMA N: multiple of 16, <= 256
+    int kb_total;    // ceil(K / 128)
+    int kb_per_split;
+    int a_mn, b_mn;  // 1 = the operand is stored with the reduction index as its row (MN-major)
+    int b_boxes;     // MN-major B: number of 128-column TMA boxes per stage; K-major: 1
+    int b_bytes;     // bytes of B per stage
+    int stages;
+    int mode;        // 0: dequantise and store fp32; 1: atomically add int32 partial sums into ws
+    float *out;
+    int64_t ldo;
+    int32_t *ws;
+    int64_t ldws;
+    const float *sa, *sb, *bias;
+    float *absmax;
+    int *status;
+    uint32_t tmem_cols;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the wait was abandoned (timeout here or abort raised by another role).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+            *abort_flag = 1;
+            return false;
+        }
+        __nanosleep(128);
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+// Bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+// [46,48) version, [61,64) layout type (2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+        "[%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(192, 1)
+igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_acc;
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // the swizzle needs 1024-byte aligned tiles
+    const uint32_t stage_bytes = kABytes + p.b_bytes;
+    const int m0 = blockIdx.x * kTileM;
+    const int n0 = blockIdx.y * p.n_tile;
+    const int kb_begin = blockIdx.z * p.kb_per_split;
+    const int kb_end = min(p.kb_total, kb_begin + p.kb_per_split);
+    const int n_iter = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_acc), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                     "r"(p.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = s_tmem_base;
+    volatile int *abort_flag = &s_abort;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0 && n_iter > 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_b) : "memory");
+            for (int it = 0; it < n_iter; ++it) {
+                const int s = it % p.stages;
+                const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+                if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag)) break;
+                const uint32_t full = smem_u32(&bar_full[s]);
+                const uint32_t a_dst = smem_base + s * stage_bytes, b_dst = a_dst + kABytes;
+                const int kc = (kb_begin + it) * kBlockK;
+                mbar_expect_tx(full, stage_bytes);
+                if (!p.a_mn) tma_load_2d(a_dst, &tm_a, full, kc, m0);
+                else tma_load_2d(a_dst, &tm_a, full, m0, kc);
+                if (!p.b_mn) {
+                    tma_load_2d(b_dst, &tm_b, full, kc, n0);
+                } else {
+                    for (int j = 0; j < p.b_boxes; ++j) tma_load_2d(b_dst + j * kABytes, &tm_b, full, n0 + j * 128, kc);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_iter > 0) {
+            // Instruction descriptor: D = s32 (bits 4-5 = 2), A and B signed int8 (bits 7-9, 10-12 = 1),
+            // operand majors (bits 15, 16), N >> 3 (bits 17-22), M >> 4 (bits 24-28).
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn << 15) |
+                                   ((uint32_t)p.b_mn << 16) | ((uint32_t)(p.n_tile >> 3) << 17) |
+                                   ((uint32_t)(kTileM >> 4) << 24);
+            const uint32_t a_kstep = p.a_mn ? 32u * 128u : 32u;  // bytes to advance per K=32 instruction
+            const uint32_t b_kstep = p.b_mn ? 32u * 128u : 32u;
+            const uint32_t a_lbo = p.a_mn ? (uint32_t)kABytes : 16u, b_lbo = p.b_mn ? (uint32_t)kABytes : 16u;
+            bool ok = true;
+            for (int it = 0; it < n_iter; ++it) {
+                const int s = it % p.stages;
+                const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+                if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_src = smem_base + s * stage_bytes, b_src = a_src + kABytes;
+                const int k_rem = p.K - (kb_begin + it) * kBlockK;
+                const int nk = min(4, (k_rem + 31) >> 5);
+                for (int k = 0; k < nk; ++k) {
+                    const uint64_t da = make_smem_desc(a_src + k * a_kstep, a_lbo, 1024u);
+                    const uint64_t db = make_smem_desc(b_src + k * b_kstep, b_lbo, 1024u);
+                    umma_i8(tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&bar_empty[s]));  // frees the stage once the MMAs above have read it
+            }
+            if (ok) umma_commit(smem_u32(&bar_acc));   // accumulator complete
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;  // the 32-lane quarter of tensor memory this warp may read
+        const int row = m0 + q * 32 + lane;
+        bool ok = n_iter > 0;
+        if (ok) ok = mbar_wait(smem_u32(&bar_acc), 0u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        float amax = 0.f;
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float sc = 0.f;
+            if (p.mode == 0) sc = __fmul_rn(__ldg(p.sa), __ldg(p.sb));
+            for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                const int col0 = n0 + c0;
+                if (row < p.M && col0 < p.N) {
+                    if (p.mode == 0) {
+                        float v[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            v[i] = __fmul_rn((float)(int)r[i], sc);
+                            if (p.bias && col0 + i < p.N) v[i] = __fadd_rn(v[i], __ldg(p.bias + col0 + i));
+                            if (col0 + i < p.N) amax = fmaxf(amax, fabsf(v[i]));
+                        }
+                        float *o = p.out + (int64_t)row * p.ldo + col0;
+                        if (col0 + 16 <= p.N && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                reinterpret_cast<float4 *>(o)[i] =
+                                    make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (col0 + i < p.N) o[i] = v[i];
+                        }
+                    } else {
+                        int32_t *o = p.ws + (int64_t)row * p.ldws + col0;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (col0 + i < p.N && r[i] != 0) atomicAdd(o + i, (int)r[i]);
+                    }
+                }
+            }
+        }
+        if (p.absmax && p.mode == 0) {
+            amax = warp_max(amax);
+            if (lane == 0 && amax > 0.f) {
+                const float s = __fdiv_rn(amax, 127.0f);
+                if (s > __ldcg(p.absmax)) atomic_max_nonneg(p.absmax, s);
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort) {
+        // give copies that are still in flight time to land before the CTA's shared memory is released
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, TANGO_ETIMEOUT);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
+                     : "memory");
+    }
+}
+
+__global__ void __launch_bounds__(256) dequant_ws_kernel(const int32_t *__restrict__ ws, int64_t ldws, int64_t rows,
+                                                         int64_t cols, const float *__restrict__ sa,
+                                                         const float *__restrict__ sb, float *__restrict__ out,
+                                                         int64_t ldo) {
+    const float sc = __fmul_rn(__ldg(sa), __ldg(sb));
+    const int64_t total = rows * cols;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols, c = i - r * cols;
+        out[r * ldo + c] = __fmul_rn((float)ws[r * ldws + c], sc);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;  // benign race: every thread resolves the same pointer
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &qres) ==
+                cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D uint8 tensor map over a row-major [outer, inner] byte matrix with leading dimension ld; 128-byte swizzle.
+static int make_map(CUtensorMap *map, const void *base, int64_t inner, int64_t outer, int64_t ld, int box_inner,
+                    int box_outer) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return TANGO_ECUDA;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = (int)r;
+        return TANGO_ECUDA;
+    }
+    return TANGO_OK;
+}
+
+struct GemmCall {
+    const int8_t *a; int64_t lda; int a_mn;
+    const int8_t *b; int64_t ldb; int b_mn;
+    int64_t M, N, K;
+    int mode; int splits;
+    float *out; int64_t ldo; int32_t *ws; int64_t ldws;
+    const float *sa, *sb, *bias; float *absmax; int *status;
+};
+
+static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
+    if (c.M <= 0 || c.N <= 0) return TANGO_OK;
+    if (c.M > 0x7fffffff || c.N > 0x7fffffff || c.K > 0x7fffffff) return TANGO_ESIZE;
+    if (!aligned(c.a, 16) || !aligned(c.b, 16) || c.lda % 16 || c.ldb % 16) return TANGO_EALIGN;
+    GemmParams p{};
+    p.M = (int)c.M; p.N = (int)c.N; p.K = (int)c.K;
+    const int n_tiles = (int)ceil_div(c.N, 256);
+    p.n_tile = (int)round_up(ceil_div(c.N, n_tiles), 16);
+    p.kb_total = (int)ceil_div(c.K, kBlockK);
+    int splits = c.splits < 1 ? 1 : c.splits;
+    if (splits > p.kb_total) splits = p.kb_total > 0 ? p.kb_total : 1;
+    p.kb_per_split = (int)ceil_div(p.kb_total, splits);
+    splits = p.kb_per_split > 0 ? (int)ceil_div(p.kb_total, p.kb_per_split) : 1;
+    p.a_mn = c.a_mn; p.b_mn = c.b_mn;
+    p.b_boxes = c.b_mn ? (int)ceil_div(p.n_tile, 128) : 1;
+    p.b_bytes = c.b_mn ? p.b_boxes * kABytes : (int)round_up((int64_t)p.n_tile * kBlockK, 1024);
+    const int stage_bytes = kABytes + p.b_bytes;
+    p.stages = 98304 / stage_bytes;
+    if (p.stages < 2) p.stages = 2;
+    if (p.stages > 6) p.stages = 6;
+    p.mode = c.mode; p.out = c.out; p.ldo = c.ldo; p.ws = c.ws; p.ldws = c.ldws;
+    p.sa = c.sa; p.sb = c.sb; p.bias = c.bias; p.absmax = c.absmax; p.status = c.status;
+    p.tmem_cols = 32;
+    while ((int)p.tmem_cols < p.n_tile) p.tmem_cols <<= 1;
+    if (c.K <= 0) return TANGO_EINVAL;
+
+    CUtensorMap tm_a, tm_b;
+    int rc;
+    // A: K-major [M rows, K bytes] box {128 k, 128 m};  MN-major [K rows, M bytes] box {128 m, 128 k}
+    if (!c.a_mn) rc = make_map(&tm_a, c.a, c.K, c.M, c.lda, kBlockK, kTileM);
+    else rc = make_map(&tm_a, c.a, c.M, c.K, c.lda, 128, kBlockK);
+    if (rc) return rc;
+    // B: K-major [N rows, K bytes] box {128 k, n_tile};  MN-major [K rows, N bytes] boxes {128 n, 128 k}
+    if (!c.b_mn) rc = make_map(&tm_b, c.b, c.K, c.N, c.ldb, kBlockK, p.n_tile);
+    else rc = make_map(&tm_b, c.b, c.N, c.K, c.ldb, 128, kBlockK);
+    if (rc) return rc;
+
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024;
+    // per-device attribute; setting it on every call keeps the entry point free of global state
+    TANGO_CUDA_TRY(cudaFuncSetAttribute(igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    const dim3 grid((unsigned)ceil_div(c.M, kTileM), (unsigned)n_tiles, (unsigned)splits);
+    if (grid.y > 65535 || grid.z > 65535) return TANGO_ESIZE;
+    igemm_kernel<<<grid, 192, smem, stream>>>(tm_a, tm_b, p);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}
+
+}  // namespace tango
+
+using namespace tango;
+
+extern "C" int64_t tango_qgemm_dw_workspace_bytes(int64_t n, int64_t k) {
+    if (n < 0 || k < 0) return 0;
+    return n * round_up(k, 4) * (int64_t)sizeof(int32_t);
+}
+
+extern "C" int tango_qgemm_nt(const int8_t *xq, int64_t ldx, const int8_t *wq, int64_t ldw, int64_t m, int64_t n,
+                              int64_t k, const float *sx, const float *sw, const float *bias, float *y, int64_t ldy,
+                              float *scale_y, int *status, tango_stream_t stream) {
+    if (m < 0 || n < 0 || k <= 0 || ldx < k || ldw < k || ldy < n) return TANGO_EINVAL;
+    if (m == 0 || n == 0) return TANGO_OK;
+    if (!xq || !wq || !sx || !sw || !y) return TANGO_EINVAL;
+    GemmCall c{xq, ldx, 0, wq, ldw, 0, m, n, k, 0, 1, y, ldy, nullptr, 0, sx, sw, bias, scale_y, status};
+    return launch_gemm(c, (cudaStream_t)stream);
+}
+
+extern "C" int tango_qgemm_forward(const float *x, int64_t ldx_f, const float *w, int64_t ldw_f, int64_t m, int64_t n,
+                                   int64_t k, const float *sx, const float *sw, int8_t *xq, int64_t ldxq, int8_t *wq,
+                                   int64_t ldwq, const float *bias, float *y, int64_t ldy, float *scale_y, int mode,
+                                   uint64_t seed, uint64_t call, int *status, tango_stream_t stream) {
+    int rc = tango_quantize(x, m, k, ldx_f, nullptr, sx, xq, ldxq, mode, seed, call, stream);
+    if (rc) return rc;
+    rc = tango_quantize(w, n, k, ldw_f, nullptr, sw, wq, ldwq, mode, seed, call + 1, stream);
+    if (rc) return rc;
+    return tango_qgemm_nt(xq, ldxq, wq, ldwq, m, n, k, sx, sw, bias, y, ldy, scale_y, status, stream);
+}
+
+extern "C" int tango_qgemm_dx(const int8_t *dyq, int64_t lddy, const int8_t *wq, int64_t ldw, int64_t m, int64_t n,
+                              int64_t k, const float *sdy, const float *sw, float *dx, int64_t lddx, int *status,
+                              tango_stream_t stream) {
+    if (m < 0 || n <= 0 || k < 0 || lddy < n || ldw < k || lddx < k) return TANGO_EINVAL;
+    if (m == 0 || k == 0) return TANGO_OK;
+    if (!dyq || !wq || !sdy || !sw || !dx) return TANGO_EINVAL;
+    // D[m, k] = A[m, n] . B[n, k]: reduction n; B is stored with the reduction index as its row
+    GemmCall c{dyq, lddy, 0, wq, ldw, 1, m, k, n, 0, 1, dx, lddx, nullptr, 0, sdy, sw, nullptr, nullptr, status};
+    return launch_gemm(c, (cudaStream_t)stream);
+}
+
+extern "C" int tango_qgemm_dw(const int8_t *dyq, int64_t lddy, const int8_t *xq, int64_t ldx, int64_t m, int64_t n,
+                              int64_t k, const float *sdy, const float *sx, float *dw, int64_t lddw, void *workspace,
+                              int64_t workspace_bytes, int *status, tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (m <= 0 || n < 0 || k < 0 || lddy < n || ldx < k || lddw < k) return TANGO_EINVAL;
+    if (n == 0 || k == 0) return TANGO_OK;
+    if (!dyq || !xq || !sdy || !sx || !dw || !workspace) return TANGO_EINVAL;
+    if (workspace_bytes < tango_qgemm_dw_workspace_bytes(n, k)) return TANGO_ESIZE;
+    if (!aligned(workspace, 16)) return TANGO_EALIGN;
+    const int64_t ldws = round_up(k, 4);
+    TANGO_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)(n * ldws) * sizeof(int32_t), stream));
+    // D[n, k] = A[n, m] . B[m, k]^T-free form: both operands are stored with the reduction index m as their row
+    const int64_t tiles = ceil_div(n, kTileM) * ceil_div(k, 256);
+    int splits = (int)(kNumSMs / (tiles > 0 ? tiles : 1));
+    if (splits < 1) splits = 1;
+    GemmCall c{dyq, lddy, 1, xq, ldx, 1, n, k, m, 1, splits, nullptr, 0, (int32_t *)workspace, ldws,
+               sdy, sx, nullptr, nullptr, status};
+    int rc = launch_gemm(c, stream);
+    if (rc) return rc;
+    int64_t blocks = ceil_div(n * k, 256);
+    if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+    dequant_ws_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const int32_t *)workspace, ldws, n, k, sdy, sx, dw, lddw);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}

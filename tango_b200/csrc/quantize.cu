@@ -1,0 +1,259 @@
+// Per-tensor symmetric int8 quantisation: absmax scale, three rounding modes, transposing variant.
+// All kernels are HBM-streaming: 128-bit loads, 128-bit packed stores, grids sized in multiples of the SM count.
+#include "common.cuh"
+
+namespace tango {
+
+thread_local int g_last_cuda_error = 0;
+
+// ---------------------------------------------------------------------------------------------- Philox4x32-10
+struct Philox {
+    uint32_t k0, k1;
+    __device__ __forceinline__ uint4 operator()(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3) const {
+        uint32_t a = k0, b = k1;
+#pragma unroll
+        for (int r = 0; r < 10; ++r) {
+            const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+            const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+            const uint32_t n0 = hi1 ^ c1 ^ a, n2 = hi0 ^ c3 ^ b;
+            c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+            a += 0x9E3779B9u; b += 0xBB67AE85u;
+        }
+        return make_uint4(c0, c1, c2, c3);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------- absmax
+template <bool VEC4>
+__global__ void __launch_bounds__(256) absmax_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
+                                                     int64_t ld, const float *__restrict__ row_scale,
+                                                     float *__restrict__ scale) {
+    float m = 0.f;
+    if (VEC4) {
+        // cols % 4 == 0, ld % 4 == 0, base 16-byte aligned
+        const int64_t c4 = cols >> 2, total = rows * c4;
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+             i += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t r = i / c4, c = (i - r * c4) << 2;
+            const float4 v = __ldcs(reinterpret_cast<const float4 *>(x + r * ld + c));
+            float t = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            if (row_scale) t = __fmul_rn(t, fabsf(__ldg(row_scale + r)));
+            m = fmaxf(m, t);
+        }
+    } else {
+        const int64_t total = rows * cols;
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+             i += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t r = i / cols, c = i - r * cols;
+            float t = fabsf(x[r * ld + c]);
+            if (row_scale) t = __fmul_rn(t, fabsf(__ldg(row_scale + r)));
+            m = fmaxf(m, t);
+        }
+    }
+    block_absmax_to_scale(m, scale);
+}
+
+// ---------------------------------------------------------------------------------------------- quantize
+__device__ __forceinline__ int round_to_i8(float t, int mode, float u) {
+    float r;
+    if (mode == TANGO_ROUND_NEAREST) r = rintf(t);
+    else if (mode == TANGO_ROUND_TRUNC) r = truncf(t);
+    else r = floorf(__fadd_rn(t, u));
+    r = fminf(fmaxf(r, -127.f), 127.f);
+    return (int)r;
+}
+
+// One thread produces 16 consecutive output bytes of one row (a 128-bit store).
+template <bool VEC4>
+__global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
+                                                       int64_t ldx, const float *__restrict__ row_scale,
+                                                       const float *__restrict__ scale, int8_t *__restrict__ q,
+                                                       int64_t ldq, int mode, uint64_t seed, uint64_t call) {
+    const float inv = inv_scale(__ldg(scale));
+    const int64_t groups = (ldq + 15) >> 4, total = rows * groups;
+    const Philox ph{(uint32_t)seed, (uint32_t)(seed >> 32)};
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / groups, c0 = (i - r * groups) << 4;
+        const float rs = row_scale ? __ldg(row_scale + r) : 1.f;
+        float v[16];
+        if (VEC4 && c0 + 16 <= cols) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 t = __ldcs(reinterpret_cast<const float4 *>(x + r * ldx + c0 + 4 * k));
+                v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) v[k] = (c0 + k < cols) ? x[r * ldx + c0 + k] : 0.f;
+        }
+        uint32_t packed[4] = {0, 0, 0, 0};
+        uint64_t cached_blk = ~0ull;
+        uint4 rnd = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float t = row_scale ? __fmul_rn(v[k], rs) : v[k];
+            t = __fmul_rn(t, inv);
+            float u = 0.f;
+            if (mode == TANGO_ROUND_STOCHASTIC) {
+                const uint64_t flat = (uint64_t)(r * cols + c0 + k);
+                const uint64_t blk = flat >> 2;
+                if (blk != cached_blk) {
+                    rnd = ph((uint32_t)blk, (uint32_t)(blk >> 32), (uint32_t)call, (uint32_t)(call >> 32));
+                    cached_blk = blk;
+                }
+                const uint32_t lane = (uint32_t)flat & 3u;
+                const uint32_t rr = lane == 0 ? rnd.x : lane == 1 ? rnd.y : lane == 2 ? rnd.z : rnd.w;
+                u = __fmul_rn((float)(rr >> 8), 5.9604644775390625e-08f);  // 2^-24
+            }
+            const int qi = (c0 + k < cols) ? round_to_i8(t, mode, u) : 0;
+            packed[k >> 2] |= ((uint32_t)qi & 0xffu) << (8 * (k & 3));
+        }
+        if (c0 + 16 <= ldq) {
+            __stcs(reinterpret_cast<uint4 *>(q + r * ldq + c0), make_uint4(packed[0], packed[1], packed[2], packed[3]));
+        } else {  // ragged end of a flat (single-row) tensor
+            for (int k = 0; c0 + k < ldq; ++k) q[r * ldq + c0 + k] = (int8_t)(packed[k >> 2] >> (8 * (k & 3)));
+        }
+    }
+}
+
+// Generic (unaligned output) version: one thread per output byte.
+__global__ void __launch_bounds__(256) quantize_scalar_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
+                                                              int64_t ldx, const float *__restrict__ row_scale,
+                                                              const float *__restrict__ scale, int8_t *__restrict__ q,
+                                                              int64_t ldq, int mode, uint64_t seed, uint64_t call) {
+    const float inv = inv_scale(__ldg(scale));
+    const int64_t total = rows * ldq;
+    const Philox ph{(uint32_t)seed, (uint32_t)(seed >> 32)};
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / ldq, c = i - r * ldq;
+        int qi = 0;
+        if (c < cols) {
+            float t = x[r * ldx + c];
+            if (row_scale) t = __fmul_rn(t, __ldg(row_scale + r));
+            t = __fmul_rn(t, inv);
+            float u = 0.f;
+            if (mode == TANGO_ROUND_STOCHASTIC) {
+                const uint64_t flat = (uint64_t)(r * cols + c), blk = flat >> 2;
+                const uint4 rnd = ph((uint32_t)blk, (uint32_t)(blk >> 32), (uint32_t)call, (uint32_t)(call >> 32));
+                const uint32_t lane = (uint32_t)flat & 3u;
+                const uint32_t rr = lane == 0 ? rnd.x : lane == 1 ? rnd.y : lane == 2 ? rnd.z : rnd.w;
+                u = __fmul_rn((float)(rr >> 8), 5.9604644775390625e-08f);
+            }
+            qi = round_to_i8(t, mode, u);
+        }
+        q[r * ldq + c] = (int8_t)qi;
+    }
+}
+
+// fp32 [nrow, ncol] -> int8 [ncol, nrow] through a padded shared tile (32 x 32 elements per block step).
+__global__ void __launch_bounds__(256) quantize_transpose_kernel(const float *__restrict__ x, int64_t nrow,
+                                                                 int64_t ncol, const float *__restrict__ scale,
+                                                                 int8_t *__restrict__ out) {
+    __shared__ int8_t tile[32][33];
+    const float inv = inv_scale(__ldg(scale));
+    const int64_t r0 = (int64_t)blockIdx.x * 32, c0 = (int64_t)blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int64_t r = r0 + ty + 8 * k, c = c0 + tx;
+        int qi = 0;
+        if (r < nrow && c < ncol) qi = round_to_i8(__fmul_rn(x[r * ncol + c], inv), TANGO_ROUND_NEAREST, 0.f);
+        tile[ty + 8 * k][tx] = (int8_t)qi;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int64_t c = c0 + ty + 8 * k, r = r0 + tx;
+        if (r < nrow && c < ncol) out[c * nrow + r] = tile[tx][ty + 8 * k];
+    }
+}
+
+static inline int stream_grid(int64_t work_items, int threads, int per_sm) {
+    int64_t blocks = ceil_div(work_items, threads);
+    const int64_t cap = (int64_t)kNumSMs * per_sm;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+}  // namespace tango
+
+using namespace tango;
+
+extern "C" int tango_version(void) { return 100; }
+
+extern "C" const char *tango_strerror(int code) {
+    switch (code) {
+        case TANGO_OK: return "ok";
+        case TANGO_EINVAL: return "invalid argument";
+        case TANGO_EALIGN: return "pointer or leading dimension not aligned as required";
+        case TANGO_ECUDA: return "CUDA call failed";
+        case TANGO_ETIMEOUT: return "bounded device-side wait expired";
+        case TANGO_ESIZE: return "size not supported by this entry point";
+        default: return "unknown error";
+    }
+}
+
+extern "C" int tango_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int tango_absmax_scale(const float *x, int64_t rows, int64_t cols, int64_t ld, const float *row_scale,
+                                  float *scale, tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!scale || rows < 0 || cols < 0 || ld < cols) return TANGO_EINVAL;
+    TANGO_CUDA_TRY(cudaMemsetAsync(scale, 0, sizeof(float), stream));
+    if (rows == 0 || cols == 0) return TANGO_OK;
+    if (!x) return TANGO_EINVAL;
+    if (ld == cols && !row_scale) {  // contiguous: treat as one long row so the vector path applies to any shape
+        cols = rows * cols; rows = 1; ld = cols;
+    }
+    const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && aligned(x, 16);
+    if (vec) {
+        const int grid = stream_grid(rows * (cols / 4), 256, 8);
+        absmax_kernel<true><<<grid, 256, 0, stream>>>(x, rows, cols, ld, row_scale, scale);
+    } else {
+        const int grid = stream_grid(rows * cols, 256, 8);
+        absmax_kernel<false><<<grid, 256, 0, stream>>>(x, rows, cols, ld, row_scale, scale);
+    }
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}
+
+extern "C" int tango_quantize(const float *x, int64_t rows, int64_t cols, int64_t ldx, const float *row_scale,
+                              const float *scale, int8_t *q, int64_t ldq, int mode, uint64_t seed, uint64_t call,
+                              tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (rows < 0 || cols < 0 || ldx < cols || ldq < cols || mode < 0 || mode > 2) return TANGO_EINVAL;
+    if (rows == 0 || ldq == 0) return TANGO_OK;
+    if (!x || !q || !scale) return TANGO_EINVAL;
+    if (ldq == cols && ldx == cols && !row_scale) {  // contiguous in and out: one flat row (same flat element index)
+        cols = rows * cols; rows = 1; ldx = ldq = cols;
+    }
+    if ((ldq % 16 == 0 || rows == 1) && aligned(q, 16)) {
+        const bool vec = (ldx % 4 == 0 || rows == 1) && aligned(x, 16);
+        const int grid = stream_grid(rows * ceil_div(ldq, 16), 256, 8);
+        if (vec)
+            quantize_kernel<true><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+        else
+            quantize_kernel<false><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+    } else {
+        const int grid = stream_grid(rows * ldq, 256, 8);
+        quantize_scalar_kernel<<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+    }
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}
+
+extern "C" int tango_quantize_transpose(const float *x, int64_t nrow, int64_t ncol, const float *scale, int8_t *out,
+                                        tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (nrow < 0 || ncol < 0) return TANGO_EINVAL;
+    if (nrow == 0 || ncol == 0) return TANGO_OK;
+    if (!x || !scale || !out) return TANGO_EINVAL;
+    const int64_t gx = ceil_div(nrow, 32), gy = ceil_div(ncol, 32);
+    if (gy > 65535) return TANGO_ESIZE;
+    quantize_transpose_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream>>>(x, nrow, ncol, scale, out);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}

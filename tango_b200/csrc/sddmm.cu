@@ -1,0 +1,277 @@
+// SDDMM over int8 node features (per-edge dot products / element-wise ops) and the fused GAT edge-softmax pass.
+//
+// dot: a group of G lanes owns one (edge, head) pair; every lane loads VEC bytes of the source row and of the
+// destination row, multiplies them with dp4a into an exact int32 and the group reduces by shuffle.  Edge endpoints
+// are read 32 at a time with coalesced loads and handed out by shuffle.
+#include "common.cuh"
+
+namespace tango {
+
+struct DotArgs {
+    const int32_t *src, *dst;
+    int64_t n_edges;
+    const int8_t *u, *v;
+    int64_t ldu, ldv;
+    int H, D;
+    int d_pad;  // bytes per head the lanes may read (multiple of VEC)
+    int G;      // lanes per (edge, head), power of two
+    const float *su, *sv;
+    float *out;
+    float *out_absmax;
+};
+
+template <int VEC>
+__device__ __forceinline__ int dot_bytes(const int8_t *pu, const int8_t *pv) {
+    if (VEC == 16) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4 *>(pu));
+        const uint4 b = __ldg(reinterpret_cast<const uint4 *>(pv));
+        int s = __dp4a((int)a.x, (int)b.x, 0);
+        s = __dp4a((int)a.y, (int)b.y, s);
+        s = __dp4a((int)a.z, (int)b.z, s);
+        return __dp4a((int)a.w, (int)b.w, s);
+    } else if (VEC == 4) {
+        return __dp4a((int)__ldg(reinterpret_cast<const uint32_t *>(pu)),
+                      (int)__ldg(reinterpret_cast<const uint32_t *>(pv)), 0);
+    } else {
+        return (int)__ldg(pu) * (int)__ldg(pv);
+    }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(256) sddmm_dot_kernel(const DotArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int G = a.G, IPS = 32 / G, grp = lane / G, sub = lane % G;
+    const float sc = __fmul_rn(__ldg(a.su), __ldg(a.sv));
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t nwarp = (int64_t)gridDim.x * (blockDim.x >> 5);
+    float amax = 0.f;
+    for (int64_t e0 = warp * 32; e0 < a.n_edges; e0 += nwarp * 32) {
+        const int64_t e = e0 + lane;
+        int my_s = 0, my_d = 0;
+        if (e < a.n_edges) { my_s = __ldg(a.src + e); my_d = __ldg(a.dst + e); }
+        const int n_e = (int)min((int64_t)32, a.n_edges - e0);
+        const int items = n_e * a.H;
+        for (int it0 = 0; it0 < items; it0 += IPS) {
+            const int item = it0 + grp;
+            const int el = item / a.H, hd = item - el * a.H;
+            const int s_id = __shfl_sync(0xffffffffu, my_s, el & 31);
+            const int d_id = __shfl_sync(0xffffffffu, my_d, el & 31);
+            int acc = 0;
+            if (item < items) {
+                const int8_t *pu = a.u + (int64_t)s_id * a.ldu + (int64_t)hd * a.D;
+                const int8_t *pv = a.v + (int64_t)d_id * a.ldv + (int64_t)hd * a.D;
+                for (int off = sub * VEC; off < a.d_pad; off += G * VEC) acc += dot_bytes<VEC>(pu + off, pv + off);
+            }
+            for (int o = G >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (item < items && sub == 0) {
+                const float r = __fmul_rn((float)acc, sc);
+                __stcs(a.out + (e0 + el) * a.H + hd, r);
+                amax = fmaxf(amax, fabsf(r));
+            }
+        }
+    }
+    if (a.out_absmax) {
+        amax = warp_max(amax);
+        if (lane == 0 && amax > 0.f) {
+            const float s = __fdiv_rn(amax, 127.0f);
+            if (s > __ldcg(a.out_absmax)) atomic_max_nonneg(a.out_absmax, s);
+        }
+    }
+}
+
+struct ElemArgs {
+    const int32_t *src, *dst;
+    int64_t n_edges;
+    const int8_t *u, *v;
+    int64_t ldu, ldv;
+    int64_t dim;
+    const float *su, *sv;
+    float *out;
+    float *out_absmax;
+};
+
+template <int OP>
+__device__ __forceinline__ float apply_op(float x, float y) {
+    if (OP == TANGO_OP_ADD) return __fadd_rn(x, y);
+    if (OP == TANGO_OP_SUB) return __fsub_rn(x, y);
+    if (OP == TANGO_OP_MUL) return __fmul_rn(x, y);
+    return __fdiv_rn(x, y);
+}
+
+// One thread per (edge, group of 4 features).  VEC4: 32-bit loads of both rows, 128-bit store when dim % 4 == 0.
+template <int OP, bool VEC4>
+__global__ void __launch_bounds__(256) sddmm_elem_kernel(const ElemArgs a) {
+    const float su = __ldg(a.su), sv = __ldg(a.sv);
+    const int64_t groups = (a.dim + 3) >> 2, total = a.n_edges * groups;
+    float amax = 0.f;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e = i / groups, c0 = (i - e * groups) << 2;
+        const int64_t s = __ldg(a.src + e), d = __ldg(a.dst + e);
+        const int8_t *pu = a.u + s * a.ldu + c0, *pv = a.v + d * a.ldv + c0;
+        int8_t bu[4], bv[4];
+        if (VEC4) {
+            const uint32_t wu = __ldg(reinterpret_cast<const uint32_t *>(pu));
+            const uint32_t wv = __ldg(reinterpret_cast<const uint32_t *>(pv));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { bu[k] = (int8_t)(wu >> (8 * k)); bv[k] = (int8_t)(wv >> (8 * k)); }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const bool ok = c0 + k < a.dim;
+                bu[k] = ok ? __ldg(pu + k) : (int8_t)0;
+                bv[k] = ok ? __ldg(pv + k) : (int8_t)1;
+            }
+        }
+        float r[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            r[k] = apply_op<OP>(__fmul_rn((float)bu[k], su), __fmul_rn((float)bv[k], sv));
+            if (c0 + k < a.dim) amax = fmaxf(amax, fabsf(r[k]));
+        }
+        float *o = a.out + e * a.dim + c0;
+        if (VEC4 && (a.dim & 3) == 0) {
+            __stcs(reinterpret_cast<float4 *>(o), make_float4(r[0], r[1], r[2], r[3]));
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (c0 + k < a.dim) o[k] = r[k];
+        }
+    }
+    if (a.out_absmax) {
+        amax = warp_max(amax);
+        if ((threadIdx.x & 31) == 0 && amax > 0.f) {
+            const float s = __fdiv_rn(amax, 127.0f);
+            if (s > __ldcg(a.out_absmax)) atomic_max_nonneg(a.out_absmax, s);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ fused GAT edge softmax
+// One warp per destination row, all heads.  Three sweeps over the row's slots (max, sum, write); the gathered
+// operands are one int8 per (source, head), so the sweeps hit L1/L2.
+__global__ void __launch_bounds__(256) gat_edge_softmax_kernel(const int32_t *__restrict__ indptr,
+                                                               const int32_t *__restrict__ indices,
+                                                               const int32_t *__restrict__ edge_ids, int64_t n_rows,
+                                                               const int8_t *__restrict__ elq,
+                                                               const int8_t *__restrict__ erq, int H,
+                                                               const float *__restrict__ sl_,
+                                                               const float *__restrict__ sr_, float slope,
+                                                               float *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const float sl = __ldg(sl_), sr = __ldg(sr_);
+    const int beg = __ldg(indptr + row), end = __ldg(indptr + row + 1);
+    for (int h = 0; h < H; ++h) {
+        const float er = __fmul_rn((float)__ldg(erq + row * H + h), sr);
+        float m = -INFINITY;
+        for (int j = beg + lane; j < end; j += 32) {
+            float z = __fadd_rn(__fmul_rn((float)__ldg(elq + (int64_t)__ldg(indices + j) * H + h), sl), er);
+            z = z >= 0.f ? z : __fmul_rn(z, slope);
+            m = fmaxf(m, z);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float sum = 0.f;
+        for (int j = beg + lane; j < end; j += 32) {
+            float z = __fadd_rn(__fmul_rn((float)__ldg(elq + (int64_t)__ldg(indices + j) * H + h), sl), er);
+            z = z >= 0.f ? z : __fmul_rn(z, slope);
+            sum += __expf(z - m);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float inv = 1.f / sum;
+        for (int j = beg + lane; j < end; j += 32) {
+            float z = __fadd_rn(__fmul_rn((float)__ldg(elq + (int64_t)__ldg(indices + j) * H + h), sl), er);
+            z = z >= 0.f ? z : __fmul_rn(z, slope);
+            const int64_t eid = edge_ids ? __ldg(edge_ids + j) : j;
+            out[eid * H + h] = __expf(z - m) * inv;
+        }
+    }
+}
+
+static int pow2_ceil(int x) {
+    int p = 1;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+}  // namespace tango
+
+using namespace tango;
+
+extern "C" int tango_sddmm_dot(const int32_t *src, const int32_t *dst, int64_t n_edges, const int8_t *uq, int64_t ldu,
+                               const int8_t *vq, int64_t ldv, int h, int d, const float *su, const float *sv,
+                               float *out, float *out_absmax, tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (n_edges < 0 || h < 1 || d < 1 || ldu < (int64_t)h * d || ldv < (int64_t)h * d) return TANGO_EINVAL;
+    if (n_edges == 0) return TANGO_OK;
+    if (!src || !dst || !uq || !vq || !su || !sv || !out) return TANGO_EINVAL;
+    DotArgs a{};
+    a.src = src; a.dst = dst; a.n_edges = n_edges; a.u = uq; a.v = vq; a.ldu = ldu; a.ldv = ldv; a.H = h; a.D = d;
+    a.su = su; a.sv = sv; a.out = out; a.out_absmax = out_absmax;
+    // widest load for which every head starts on a VEC boundary of both operands
+    int vec = 1;
+    const bool single = (h == 1);
+    auto fits = [&](int v) {
+        return ldu % v == 0 && ldv % v == 0 && aligned(uq, v) && aligned(vq, v) &&
+               (single ? (round_up(d, v) <= ldu && round_up(d, v) <= ldv) : d % v == 0);
+    };
+    if (fits(16)) vec = 16; else if (fits(4)) vec = 4;
+    a.d_pad = (int)round_up(d, vec);  // single head: pad bytes are zero by the layout convention
+    a.G = pow2_ceil(a.d_pad / vec);
+    if (a.G > 32) a.G = 32;
+    int64_t blocks = ceil_div(ceil_div(n_edges, 32), 8);
+    const int64_t cap = (int64_t)kNumSMs * 16;
+    if (blocks > cap) blocks = cap;
+    if (vec == 16) sddmm_dot_kernel<16><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else if (vec == 4) sddmm_dot_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else sddmm_dot_kernel<1><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}
+
+template <int OP>
+static int launch_elem(const ElemArgs &a, bool vec4, cudaStream_t stream) {
+    const int64_t total = a.n_edges * ((a.dim + 3) / 4);
+    int64_t blocks = ceil_div(total, 256);
+    const int64_t cap = (int64_t)kNumSMs * 16;
+    if (blocks > cap) blocks = cap;
+    if (vec4) sddmm_elem_kernel<OP, true><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else sddmm_elem_kernel<OP, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}
+
+extern "C" int tango_sddmm_elementwise(int op, const int32_t *src, const int32_t *dst, int64_t n_edges,
+                                       const int8_t *uq, int64_t ldu, const int8_t *vq, int64_t ldv, int64_t dim,
+                                       const float *su, const float *sv, float *out, float *out_absmax,
+                                       tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (n_edges < 0 || dim < 1 || ldu < dim || ldv < dim || op < 0 || op > 3) return TANGO_EINVAL;
+    if (n_edges == 0) return TANGO_OK;
+    if (!src || !dst || !uq || !vq || !su || !sv || !out) return TANGO_EINVAL;
+    ElemArgs a{src, dst, n_edges, uq, vq, ldu, ldv, dim, su, sv, out, out_absmax};
+    const bool vec4 = ldu % 4 == 0 && ldv % 4 == 0 && aligned(uq, 4) && aligned(vq, 4) && aligned(out, 16) &&
+                      round_up(dim, 4) <= ldu && round_up(dim, 4) <= ldv;
+    switch (op) {
+        case TANGO_OP_ADD: return launch_elem<TANGO_OP_ADD>(a, vec4, stream);
+        case TANGO_OP_SUB: return launch_elem<TANGO_OP_SUB>(a, vec4, stream);
+        case TANGO_OP_MUL: return launch_elem<TANGO_OP_MUL>(a, vec4, stream);
+        default: return launch_elem<TANGO_OP_DIV>(a, vec4, stream);
+    }
+}
+
+extern "C" int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                                      int64_t n_rows, const int8_t *elq, const int8_t *erq, int h, const float *sl,
+                                      const float *sr, float slope, float *a, tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (n_rows < 0 || h < 1) return TANGO_EINVAL;
+    if (n_rows == 0) return TANGO_OK;
+    if (!indptr || !indices || !elq || !erq || !sl || !sr || !a) return TANGO_EINVAL;
+    const int64_t blocks = ceil_div(n_rows, 8);
+    gat_edge_softmax_kernel<<<(unsigned)blocks, 256, 0, stream>>>(indptr, indices, edge_ids, n_rows, elq, erq, h, sl,
+                                                                  sr, slope, a);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}

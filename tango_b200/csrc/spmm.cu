@@ -1,0 +1,338 @@
+// CSR SpMM over int8 node (or edge) features with exact int32 accumulation.
+//
+// One warp owns one output row (or one "unit" = slice of a long row).  Within the warp, G lanes cover one
+// neighbour's feature row with VEC-byte loads (G * VEC >= padded feature width) and 32/G neighbours are gathered per
+// step.  Neighbour ids are fetched 32 at a time with one coalesced load and handed out by shuffle.  Bytes are
+// sign-extended and added with dp4a against a one-hot (copy-u) or weight-carrying (u_mul_e) selector, so every
+// accumulator is an exact int32.  Rows longer than the plan's threshold are cut into units that add into an int32
+// scratch row with integer atomics (order independent => deterministic) and a second kernel finishes them.
+#include "common.cuh"
+
+namespace tango {
+
+struct SpmmArgs {
+    const int32_t *indptr;
+    const int32_t *indices;   // feature-row id per slot; NULL => the slot number itself
+    const int32_t *edge_ids;  // edge id per slot for the weight lookup; NULL => the slot number itself
+    int64_t n_rows;
+    int nseg;
+    const int8_t *feat;
+    int64_t ld;
+    int f;      // logical feature bytes per row
+    int f_pad;  // bytes the lanes may read (multiple of VEC, <= ld)
+    const int8_t *ew;  // [E, H] int8 edge weights (weighted modes)
+    int H, D;
+    const float *scales;  // [nseg]
+    const float *row_scale;
+    const float *bias;
+    int relu;
+    float *out;
+    int64_t ldo;
+    float *out_absmax;
+    const int32_t *units;
+    int64_t n_units;
+    const int32_t *heavy_rows;
+    int64_t n_heavy;
+    int32_t *ws;
+    int64_t ws_ld;
+    int split_threshold;
+    int G;  // lanes per neighbour (power of two)
+};
+
+enum { MODE_COPY = 0, MODE_WEIGHT_LANE = 1, MODE_WEIGHT_ELEM = 2 };
+
+template <int VEC> struct VecLoad;
+template <> struct VecLoad<16> {
+    uint32_t w[4];
+    __device__ __forceinline__ void load(const int8_t *p) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    }
+    __device__ __forceinline__ void zero() { w[0] = w[1] = w[2] = w[3] = 0; }
+};
+template <> struct VecLoad<4> {
+    uint32_t w[1];
+    __device__ __forceinline__ void load(const int8_t *p) { w[0] = __ldg(reinterpret_cast<const uint32_t *>(p)); }
+    __device__ __forceinline__ void zero() { w[0] = 0; }
+};
+template <> struct VecLoad<1> {
+    uint32_t w[1];
+    __device__ __forceinline__ void load(const int8_t *p) { w[0] = (uint32_t)(uint8_t)__ldg(p); }
+    __device__ __forceinline__ void zero() { w[0] = 0; }
+};
+
+template <int VEC, int MODE>
+__device__ __forceinline__ void accumulate(int (&acc)[VEC], const VecLoad<VEC> &v, uint32_t wsel,
+                                           const int8_t *wrow, int off, const SpmmArgs &a) {
+    if (VEC == 1) {
+        const int b = (int)(int8_t)(v.w[0] & 0xff);
+        if (MODE == MODE_COPY) acc[0] += b;
+        else acc[0] += b * (int)(int8_t)wsel;
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        const uint32_t word = v.w[i >> 2];
+        if (MODE == MODE_COPY) {
+            acc[i] = __dp4a((int)word, (int)(1u << (8 * (i & 3))), acc[i]);
+        } else if (MODE == MODE_WEIGHT_LANE) {
+            acc[i] = __dp4a((int)word, (int)(wsel << (8 * (i & 3))), acc[i]);
+        } else {
+            const int col = off + i;
+            const int wv = (wrow && col < a.f) ? (int)__ldg(wrow + col / a.D) : 0;
+            acc[i] += (int)(int8_t)((word >> (8 * (i & 3))) & 0xff) * wv;
+        }
+    }
+}
+
+// Sums the neighbours of slots [beg, end) into acc for the feature bytes [off, off + VEC) handled by this lane.
+// On return every lane of group 0 (lane < G) holds the full sum for its bytes.
+template <int VEC, int MODE>
+__device__ __forceinline__ void gather_segment(int (&acc)[VEC], int beg, int end, int off, bool active,
+                                               const SpmmArgs &a) {
+    const int lane = threadIdx.x & 31;
+    const int G = a.G, NB = 32 / G, grp = lane / G;
+    constexpr int U = 4;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0;
+    const int head = (MODE == MODE_WEIGHT_LANE) ? off / a.D : 0;
+    for (int j0 = beg; j0 < end; j0 += 32) {
+        const int j = j0 + lane;
+        int my_idx = -1, my_eid = 0;
+        if (j < end) {
+            my_idx = a.indices ? __ldg(a.indices + j) : j;
+            if (MODE != MODE_COPY) my_eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
+        }
+        const int steps = min(G, (end - j0 + NB - 1) / NB);
+        for (int s = 0; s < steps; s += U) {
+            VecLoad<VEC> v[U];
+            uint32_t wsel[U];
+            const int8_t *wrow[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int src_lane = ((s + u) * NB + grp) & 31;
+                const int idx = __shfl_sync(0xffffffffu, my_idx, src_lane);
+                int eid = 0;
+                if (MODE != MODE_COPY) eid = __shfl_sync(0xffffffffu, my_eid, src_lane);
+                const bool ok = active && (s + u) < steps && idx >= 0;
+                wsel[u] = 0; wrow[u] = nullptr;
+                if (ok) {
+                    v[u].load(a.feat + (int64_t)idx * a.ld + off);
+                    if (MODE == MODE_WEIGHT_LANE) wsel[u] = (uint32_t)(uint8_t)__ldg(a.ew + (int64_t)eid * a.H + head);
+                    if (MODE == MODE_WEIGHT_ELEM) wrow[u] = a.ew + (int64_t)eid * a.H;
+                } else {
+                    v[u].zero();
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) accumulate<VEC, MODE>(acc, v[u], wsel[u], wrow[u], off, a);
+        }
+    }
+    for (int o = G; o < 32; o <<= 1) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+    }
+}
+
+__device__ __forceinline__ float finish_value(float v, int64_t row, int col, const SpmmArgs &a) {
+    if (a.row_scale) v = __fmul_rn(v, __ldg(a.row_scale + row));
+    if (a.bias) v = __fadd_rn(v, __ldg(a.bias + col));
+    if (a.relu) v = fmaxf(v, 0.f);
+    return v;
+}
+
+template <int VEC, int MODE>
+__global__ void __launch_bounds__(256) spmm_kernel(const SpmmArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int sub = lane % a.G;
+    float amax = 0.f;
+    if (w < a.n_units) {
+        // ---- one slice of a long row: integer partial sums into scratch
+        const int4 u = __ldg(reinterpret_cast<const int4 *>(a.units) + w);  // (vrow, beg, end, slot)
+        for (int fb = 0; fb < a.f_pad; fb += 32 * VEC) {
+            const int off = fb + sub * VEC;
+            const bool active = off < a.f_pad;
+            int acc[VEC];
+            gather_segment<VEC, MODE>(acc, u.y, u.z, off, active, a);
+            if (active && lane < a.G) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i)
+                    if (off + i < a.f && acc[i] != 0) atomicAdd(a.ws + (int64_t)u.w * a.ws_ld + off + i, acc[i]);
+            }
+        }
+    } else if (w - a.n_units < a.n_rows) {
+        const int64_t row = w - a.n_units;
+        const int32_t *ip = a.indptr + row * a.nseg;
+        const int row_beg = __ldg(ip), row_end = __ldg(ip + a.nseg);
+        if (a.n_heavy > 0 && row_end - row_beg > a.split_threshold) return;  // finished by spmm_finalize_kernel
+        for (int fb = 0; fb < a.f_pad; fb += 32 * VEC) {
+            const int off = fb + sub * VEC;
+            const bool active = off < a.f_pad;
+            float facc[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) facc[i] = 0.f;
+            for (int k = 0; k < a.nseg; ++k) {
+                int acc[VEC];
+                gather_segment<VEC, MODE>(acc, __ldg(ip + k), __ldg(ip + k + 1), off, active, a);
+                const float sc = __ldg(a.scales + k);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) facc[i] = __fadd_rn(facc[i], __fmul_rn((float)acc[i], sc));
+            }
+            if (active && lane < a.G) {
+                float *o = a.out + row * a.ldo + off;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    facc[i] = finish_value(facc[i], row, min(off + i, a.f - 1), a);
+                    if (off + i < a.f) amax = fmaxf(amax, fabsf(facc[i]));
+                }
+                if (VEC == 16 && off + 16 <= a.f && (a.ldo & 3) == 0 &&
+                    (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        reinterpret_cast<float4 *>(o)[i] =
+                            make_float4(facc[4 * i], facc[4 * i + 1], facc[4 * i + 2], facc[4 * i + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i)
+                        if (off + i < a.f) o[i] = facc[i];
+                }
+            }
+        }
+    }
+    if (a.out_absmax) {
+        amax = warp_max(amax);
+        if (lane == 0 && amax > 0.f) {
+            const float s = __fdiv_rn(amax, 127.0f);
+            if (s > __ldcg(a.out_absmax)) atomic_max_nonneg(a.out_absmax, s);
+        }
+    }
+}
+
+// Finishes the rows that were cut into units: one thread per (heavy row, feature byte).
+__global__ void __launch_bounds__(256) spmm_finalize_kernel(const SpmmArgs a) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    float amax = 0.f;
+    if (t < a.n_heavy * a.f) {
+        const int64_t hs = t / a.f;
+        const int col = (int)(t - hs * a.f);
+        const int64_t row = __ldg(a.heavy_rows + hs);
+        float facc = 0.f;
+        for (int k = 0; k < a.nseg; ++k)
+            facc = __fadd_rn(facc, __fmul_rn((float)a.ws[(hs * a.nseg + k) * a.ws_ld + col], __ldg(a.scales + k)));
+        facc = finish_value(facc, row, col, a);
+        a.out[row * a.ldo + col] = facc;
+        amax = fabsf(facc);
+    }
+    if (a.out_absmax) {
+        amax = warp_max(amax);
+        if ((threadIdx.x & 31) == 0 && amax > 0.f) {
+            const float s = __fdiv_rn(amax, 127.0f);
+            if (s > __ldcg(a.out_absmax)) atomic_max_nonneg(a.out_absmax, s);
+        }
+    }
+}
+
+static int pow2_ceil(int x) {
+    int p = 1;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+template <int MODE>
+static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t stream) {
+    if (a.n_rows == 0 || a.f == 0) return TANGO_OK;
+    if (plan && plan->n_units > 0) {
+        if (!plan->units || !plan->heavy_rows || !plan->ws || plan->ws_ld < a.f || plan->n_heavy <= 0)
+            return TANGO_EINVAL;
+        if (!aligned(plan->units, 16)) return TANGO_EALIGN;
+        a.units = plan->units; a.n_units = plan->n_units; a.heavy_rows = plan->heavy_rows;
+        a.n_heavy = plan->n_heavy; a.ws = plan->ws; a.ws_ld = plan->ws_ld; a.split_threshold = plan->split_threshold;
+        TANGO_CUDA_TRY(cudaMemsetAsync(a.ws, 0, sizeof(int32_t) * (size_t)(a.n_heavy * a.nseg * a.ws_ld), stream));
+    }
+    if (MODE == MODE_WEIGHT_LANE && a.H == 1) a.D = 1 << 20;  // one head: every byte shares the weight
+    int vec = 1;
+    if (a.ld % 16 == 0 && aligned(a.feat, 16)) vec = 16;
+    else if (a.ld % 4 == 0 && aligned(a.feat, 4)) vec = 4;
+    // narrow rows: prefer one lane per neighbour over mostly idle 16-byte lanes
+    if (vec == 16 && a.f <= 4) vec = 4;
+    a.f_pad = (int)round_up(a.f, vec);
+    if (a.f_pad > a.ld) return TANGO_EINVAL;
+    a.G = pow2_ceil((a.f_pad + vec - 1) / vec);
+    if (a.G > 32) a.G = 32;
+    if (MODE == MODE_WEIGHT_LANE && (a.D % vec) != 0) {
+        // a lane's bytes must stay inside one head; fall back to narrower loads, else to the per-element mode
+        if (vec == 16 && a.D % 4 == 0 && a.ld % 4 == 0) {
+            vec = 4; a.f_pad = (int)round_up(a.f, 4); a.G = pow2_ceil(a.f_pad / 4); if (a.G > 32) a.G = 32;
+        }
+    }
+    const int64_t warps = a.n_units + a.n_rows;
+    const int64_t blocks = ceil_div(warps, 8);
+    if (blocks > 0x7fffffff) return TANGO_ESIZE;
+#define TANGO_SPMM_LAUNCH(V, M) spmm_kernel<V, M><<<(unsigned)blocks, 256, 0, stream>>>(a)
+    if (MODE == MODE_WEIGHT_LANE && (a.D % vec) != 0) {
+        if (vec == 16) TANGO_SPMM_LAUNCH(16, MODE_WEIGHT_ELEM);
+        else if (vec == 4) TANGO_SPMM_LAUNCH(4, MODE_WEIGHT_ELEM);
+        else TANGO_SPMM_LAUNCH(1, MODE_WEIGHT_LANE);  // VEC == 1: a lane holds one byte, always inside one head
+    } else {
+        if (vec == 16) TANGO_SPMM_LAUNCH(16, MODE);
+        else if (vec == 4) TANGO_SPMM_LAUNCH(4, MODE);
+        else TANGO_SPMM_LAUNCH(1, MODE);
+    }
+#undef TANGO_SPMM_LAUNCH
+    TANGO_LAUNCH_CHECK();
+    if (a.n_units > 0) {
+        const int64_t fb = ceil_div(a.n_heavy * a.f, 256);
+        spmm_finalize_kernel<<<(unsigned)fb, 256, 0, stream>>>(a);
+        TANGO_LAUNCH_CHECK();
+    }
+    return TANGO_OK;
+}
+
+}  // namespace tango
+
+using namespace tango;
+
+extern "C" int tango_spmm_copy_u(const int32_t *indptr, const int32_t *indices, int64_t n_rows, int nseg,
+                                 const int8_t *nq, int64_t ldn, int64_t f, const float *scales, const float *row_scale,
+                                 const float *bias, int relu, float *out, int64_t ldo, float *out_absmax,
+                                 const tango_spmm_plan *plan, tango_stream_t stream) {
+    if (n_rows < 0 || nseg < 1 || f < 0 || ldn < f || ldo < f || f > (1 << 20)) return TANGO_EINVAL;
+    if (n_rows == 0 || f == 0) return TANGO_OK;
+    if (!indptr || !indices || !nq || !scales || !out) return TANGO_EINVAL;
+    SpmmArgs a{};
+    a.indptr = indptr; a.indices = indices; a.edge_ids = nullptr; a.n_rows = n_rows; a.nseg = nseg;
+    a.feat = nq; a.ld = ldn; a.f = (int)f; a.ew = nullptr; a.H = 1; a.D = (int)f;
+    a.scales = scales; a.row_scale = row_scale; a.bias = bias; a.relu = relu;
+    a.out = out; a.ldo = ldo; a.out_absmax = out_absmax;
+    return launch_spmm<MODE_COPY>(a, plan, (cudaStream_t)stream);
+}
+
+extern "C" int tango_spmm_u_mul_e(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                                  int64_t n_rows, const int8_t *nq, int64_t ldn, int h, int d, const int8_t *eq,
+                                  const float *scale, float *out, int64_t ldo, const tango_spmm_plan *plan,
+                                  tango_stream_t stream) {
+    if (n_rows < 0 || h < 1 || d < 1) return TANGO_EINVAL;
+    const int64_t f = (int64_t)h * d;
+    if (ldn < f || ldo < f || f > (1 << 20)) return TANGO_EINVAL;
+    if (n_rows == 0) return TANGO_OK;
+    if (!indptr || !indices || !nq || !eq || !scale || !out) return TANGO_EINVAL;
+    SpmmArgs a{};
+    a.indptr = indptr; a.indices = indices; a.edge_ids = edge_ids; a.n_rows = n_rows; a.nseg = 1;
+    a.feat = nq; a.ld = ldn; a.f = (int)f; a.ew = eq; a.H = h; a.D = d;
+    a.scales = scale; a.out = out; a.ldo = ldo;
+    return launch_spmm<MODE_WEIGHT_LANE>(a, plan, (cudaStream_t)stream);
+}
+
+extern "C" int tango_spmm_incidence(const int32_t *indptr, const int32_t *edge_ids, int64_t n_rows, const int8_t *zq,
+                                    int64_t ldz, int64_t f, const float *scale, float *out, int64_t ldo,
+                                    const tango_spmm_plan *plan, tango_stream_t stream) {
+    if (n_rows < 0 || f < 0 || ldz < f || ldo < f || f > (1 << 20)) return TANGO_EINVAL;
+    if (n_rows == 0 || f == 0) return TANGO_OK;
+    if (!indptr || !zq || !scale || !out) return TANGO_EINVAL;
+    SpmmArgs a{};
+    a.indptr = indptr; a.indices = edge_ids; a.edge_ids = nullptr; a.n_rows = n_rows; a.nseg = 1;
+    a.feat = zq; a.ld = ldz; a.f = (int)f; a.H = 1; a.D = (int)f;
+    a.scales = scale; a.out = out; a.ldo = ldo;
+    return launch_spmm<MODE_COPY>(a, plan, (cudaStream_t)stream);
+}

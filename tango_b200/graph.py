@@ -1,0 +1,270 @@
+"""DGL-free graph container and seeded synthetic graph generator.
+
+`Graph` exposes the attributes the reference operators read after `graph_preprocess`
+(cuda/util.py:5-11 in the reference): `adj_csr`, `adj_csc` = (indptr, indices, edge_ids), `coo` = (src, dst) in
+edge-id order, `inc_in` / `inc_out` = [2, E] (node, edge id) pairs, and `num_nodes()`.  Indices are int32 (the
+reference uses DGL's int64; halving the index traffic matters for memory-bound kernels).
+
+`rmat_graph` builds the R-MAT graphs (a=0.57, b=c=0.19, d=0.05) that stand in for the public datasets the
+reference's scripts load.  It uses only wrapping int64 arithmetic, so the same seed gives the same graph on CPU and
+on GPU.
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+from typing import Optional, Tuple
+
+import torch
+
+_M64 = (1 << 64) - 1
+
+
+def _s64(x: int) -> int:
+    """Python int -> the signed 64-bit value with the same low 64 bits."""
+    x &= _M64
+    return x - (1 << 64) if x >= (1 << 63) else x
+
+
+_C1 = _s64(0xBF58476D1CE4E5B9)
+_C2 = _s64(0x94D049BB133111EB)
+_GOLD = _s64(0x9E3779B97F4A7C15)
+
+
+def _lsr(x: torch.Tensor, s: int) -> torch.Tensor:
+    return (x >> s) & ((1 << (64 - s)) - 1)
+
+
+def mix64(x: torch.Tensor) -> torch.Tensor:
+    """splitmix64 finaliser on int64 tensors (wrapping arithmetic)."""
+    x = (x ^ _lsr(x, 30)) * _C1
+    x = (x ^ _lsr(x, 27)) * _C2
+    return x ^ _lsr(x, 31)
+
+
+def _rmat_batch(n_nodes: int, start: int, count: int, seed: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    levels = max(1, math.ceil(math.log2(max(2, n_nodes))))
+    i = torch.arange(start, start + count, dtype=torch.int64, device=device)
+    base = mix64(i * _GOLD + _s64(seed * 0x2545F4914F6CDD1D + 0x1234567))
+    src = torch.zeros(count, dtype=torch.int64, device=device)
+    dst = torch.zeros(count, dtype=torch.int64, device=device)
+    ta, tb, tc = int(0.57 * (1 << 24)), int(0.76 * (1 << 24)), int(0.95 * (1 << 24))
+    for lvl in range(levels):
+        u = _lsr(mix64(base + _s64((lvl + 1) * 0xD6E8FEB86659FD93)), 40)  # 24 uniform bits
+        sbit = (u >= tb).to(torch.int64)                                   # quadrants c, d: source bit set
+        dbit = (((u >= ta) & (u < tb)) | (u >= tc)).to(torch.int64)       # quadrants b, d: destination bit set
+        src = (src << 1) | sbit
+        dst = (dst << 1) | dbit
+    return src, dst
+
+
+def rmat_edges(n_nodes: int, n_edges: int, seed: int, device="cpu") -> Tuple[torch.Tensor, torch.Tensor]:
+    """`n_edges` distinct directed non-loop edges (src, dst) of an R-MAT graph, sorted by (src, dst)."""
+    keys = torch.empty(0, dtype=torch.int64, device=device)
+    start = 0
+    while keys.numel() < n_edges:
+        need = n_edges - keys.numel()
+        count = max(1024, int(need * 1.5) + 1024)
+        s, d = _rmat_batch(n_nodes, start, count, seed, device)
+        start += count
+        ok = (s < n_nodes) & (d < n_nodes) & (s != d)
+        new = torch.unique(s[ok] * n_nodes + d[ok])
+        del s, d, ok
+        if keys.numel():
+            pos = torch.searchsorted(keys, new).clamp_(max=keys.numel() - 1)
+            new = new[keys[pos] != new]
+        if new.numel() > need:  # keep a pseudo-random, seed-determined subset of the last batch
+            order = torch.argsort(mix64(new ^ _s64(seed)))
+            new = new[order[:need]]
+        keys = torch.sort(torch.cat([keys, new]))[0]
+    return (keys // n_nodes).to(torch.int32), (keys % n_nodes).to(torch.int32)
+
+
+class Graph:
+    """Homogeneous directed graph held as int32 index tensors on one device."""
+
+    is_block = False
+
+    def __init__(self, src: torch.Tensor, dst: torch.Tensor, n_nodes: int):
+        assert src.shape == dst.shape and src.dim() == 1
+        self._src = src.to(torch.int32).contiguous()
+        self._dst = dst.to(torch.int32).contiguous()
+        self._n = int(n_nodes)
+        self.ndata = {}
+        self.edata = {}
+        self.srcdata = self.ndata
+        self.dstdata = self.ndata
+        self._csr = None
+        self._csc = None
+        self._plans = {}
+        self._deg = {}
+        self.n_classes = None
+
+    # ---- DGL-like surface used by the operators and the layers
+    @property
+    def device(self):
+        return self._src.device
+
+    def num_nodes(self) -> int:
+        return self._n
+
+    number_of_nodes = num_nodes
+
+    def num_edges(self) -> int:
+        return int(self._src.numel())
+
+    number_of_edges = num_edges
+
+    def number_of_dst_nodes(self) -> int:
+        return self._n
+
+    def edges(self):
+        return self._src, self._dst
+
+    def in_degrees(self) -> torch.Tensor:
+        if "in" not in self._deg:
+            self._deg["in"] = torch.bincount(self._dst.long(), minlength=self._n)
+        return self._deg["in"]
+
+    def out_degrees(self) -> torch.Tensor:
+        if "out" not in self._deg:
+            self._deg["out"] = torch.bincount(self._src.long(), minlength=self._n)
+        return self._deg["out"]
+
+    @contextlib.contextmanager
+    def local_scope(self):
+        yield self
+
+    def to(self, device) -> "Graph":
+        g = Graph(self._src.to(device), self._dst.to(device), self._n)
+        g.n_classes = self.n_classes
+        g.ndata = {k: v.to(device) for k, v in self.ndata.items()}
+        g.srcdata = g.dstdata = g.ndata
+        return g
+
+    # ---- sparse formats
+    def adj_sparse(self, fmt: str):
+        """(indptr, indices, edge_ids); 'csr' rows are sources, 'csc' rows are destinations.  Columns are sorted."""
+        if fmt == "coo":
+            return self._src, self._dst
+        rows, cols = (self._src, self._dst) if fmt == "csr" else (self._dst, self._src)
+        cached = self._csr if fmt == "csr" else self._csc
+        if cached is None:
+            key = rows.long() * self._n + cols.long()
+            key, perm = torch.sort(key, stable=True)
+            counts = torch.bincount(rows.long(), minlength=self._n)
+            indptr = torch.zeros(self._n + 1, dtype=torch.int64, device=self.device)
+            torch.cumsum(counts, 0, out=indptr[1:])
+            cached = (indptr.to(torch.int32), (key % self._n).to(torch.int32), perm.to(torch.int32))
+            if fmt == "csr":
+                self._csr = cached
+            else:
+                self._csc = cached
+        return cached
+
+    @property
+    def adj_csr(self):
+        return self.adj_sparse("csr")
+
+    @property
+    def adj_csc(self):
+        return self.adj_sparse("csc")
+
+    @property
+    def coo(self):
+        return self._src, self._dst
+
+    def _inc(self, fmt: str) -> torch.Tensor:
+        indptr, _, eids = self.adj_sparse(fmt)
+        nodes = torch.repeat_interleave(torch.arange(self._n, dtype=torch.int32, device=self.device),
+                                        (indptr[1:] - indptr[:-1]).long())
+        return torch.stack([nodes, eids])
+
+    @property
+    def inc_in(self):
+        return self._inc("csc")
+
+    @property
+    def inc_out(self):
+        return self._inc("csr")
+
+
+def add_self_loop(src: torch.Tensor, dst: torch.Tensor, n_nodes: int):
+    """Drops existing loops and appends one loop per node (dgl.remove_self_loop + add_self_loop,
+    evaluation/util.py:28 in the reference)."""
+    keep = src != dst
+    loop = torch.arange(n_nodes, dtype=src.dtype, device=src.device)
+    return torch.cat([src[keep], loop]), torch.cat([dst[keep], loop])
+
+
+def rmat_graph(n_nodes: int, n_edges: int, seed: int, device="cpu", self_loops: bool = True) -> Graph:
+    src, dst = rmat_edges(n_nodes, n_edges, seed, device)
+    if self_loops:
+        src, dst = add_self_loop(src, dst, n_nodes)
+    return Graph(src, dst, n_nodes)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Schedules for rows that are too long for one warp, and 1-D row partitions for multi-GPU training.
+# ----------------------------------------------------------------------------------------------------------------
+SPLIT_THRESHOLD = 4096
+UNIT_NNZ = 2048
+
+
+class SpmmSchedule:
+    """Device arrays consumed by the SpMM kernels: `units` [n_units, 4] = (segment row, begin, end, scratch slot)
+    for every slice of a row longer than the threshold, and `heavy_rows` = those rows."""
+
+    def __init__(self, indptr: torch.Tensor, nseg: int = 1, threshold: int = SPLIT_THRESHOLD, unit: int = UNIT_NNZ):
+        self.nseg = nseg
+        self.threshold = threshold
+        n_rows = (indptr.numel() - 1) // nseg
+        ip = indptr.long()
+        row_deg = ip[nseg::nseg] - ip[:-1:nseg][:n_rows] if nseg > 1 else ip[1:] - ip[:-1]
+        heavy = torch.nonzero(row_deg > threshold).flatten()
+        self.n_heavy = int(heavy.numel())
+        self.heavy_rows = heavy.to(torch.int32)
+        if self.n_heavy == 0:
+            self.units = torch.zeros((0, 4), dtype=torch.int32, device=indptr.device)
+            self.n_units = 0
+            return
+        # segment rows of the heavy rows, their scratch slots, and the slices of each
+        seg_rows = (heavy[:, None] * nseg + torch.arange(nseg, device=indptr.device)[None, :]).flatten()
+        slots = torch.arange(seg_rows.numel(), device=indptr.device)
+        beg, end = ip[seg_rows], ip[seg_rows + 1]
+        n_chunks = (end - beg + unit - 1) // unit
+        rep = torch.repeat_interleave(torch.arange(seg_rows.numel(), device=indptr.device), n_chunks)
+        first = torch.cumsum(n_chunks, 0) - n_chunks
+        k = torch.arange(rep.numel(), device=indptr.device) - first[rep]
+        ub = beg[rep] + k * unit
+        ue = torch.minimum(ub + unit, end[rep])
+        units = torch.stack([seg_rows[rep], ub, ue, slots[rep]], dim=1)
+        # longest slices first
+        self.units = units.to(torch.int32).contiguous()
+        self.n_units = int(self.units.shape[0])
+
+
+class RowPartition:
+    """Rank `rank`'s block of rows [r0, r1) of a CSR/CSC whose column ids stay global.  `indptr` has
+    n_local * world + 1 entries: row v owns `world` consecutive segments, segment k holding the columns that live on
+    rank k (columns are sorted, so segments are contiguous)."""
+
+    def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, edge_ids: Optional[torch.Tensor], n_nodes: int,
+                 rank: int, world: int):
+        self.world, self.rank = world, rank
+        self.shard_rows = (n_nodes + world - 1) // world
+        self.r0 = min(n_nodes, rank * self.shard_rows)
+        self.r1 = min(n_nodes, self.r0 + self.shard_rows)
+        self.n_local = self.r1 - self.r0
+        ip = indptr.long()
+        lo, hi = int(ip[self.r0]), int(ip[self.r1])
+        self.indices = indices[lo:hi].contiguous()
+        self.edge_ids = None if edge_ids is None else edge_ids[lo:hi].contiguous()
+        rows = torch.repeat_interleave(torch.arange(self.n_local, device=indptr.device),
+                                       (ip[self.r0 + 1:self.r1 + 1] - ip[self.r0:self.r1]))
+        key = rows * (self.shard_rows * world) + self.indices.long()
+        bounds = (torch.arange(self.n_local, device=indptr.device)[:, None] * (self.shard_rows * world)
+                  + torch.arange(world, device=indptr.device)[None, :] * self.shard_rows).flatten()
+        seg = torch.searchsorted(key, bounds)
+        self.indptr = torch.cat([seg, torch.tensor([hi - lo], device=indptr.device)]).to(torch.int32)
+        self.schedule = SpmmSchedule(self.indptr, nseg=world)

@@ -1,0 +1,470 @@
+"""Python wrappers with the names and signatures of the reference's cuda/kernels.py, backed by the prebuilt
+sm_100a library instead of a runtime JIT of CUTLASS sources (cuda/kernels.py:10-16 in the reference).
+
+`cuda_kernels` mirrors the reference's pybind module (cuda/src/cuda.cpp:182-204): scripts call
+`cuda_kernels.get_scale(t)` directly.  The free functions below mirror cuda/kernels.py:19-178.
+
+Differences a caller can observe:
+  * graph index tensors are int32;
+  * int8 tensors whose row width is not a multiple of 16 bytes are returned as views of zero-padded storage
+    (same shape, row stride rounded up to 16) so that every kernel can use 128-bit accesses and TMA;
+  * `quantize`/`QGEMM_forward` accept `mode`/`seed`/`call` for the rounding mode (defaults reproduce the
+    reference: nearest for `quantize`, truncation for the fused forward).
+"""
+from __future__ import annotations
+
+import ctypes
+import types
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_TRUNC, SpmmPlan, check, lib
+from .graph import SpmmSchedule
+
+__all__ = ["cuda_kernels", "quantize", "mySDDMM_int8", "QGEMM_forward", "QGEMM_backward", "transpose_quant",
+           "multi_cusparse_SPMM", "incidence_SPMM", "csr_SPMM", "multi_cusparse_SPMV", "infer_broadcast_shape",
+           "ROUND_TRUNC", "ROUND_NEAREST", "ROUND_STOCHASTIC", "device_status", "alloc_int8"]
+
+
+# --------------------------------------------------------------------------------------------------- plumbing
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+def _matrix(t: torch.Tensor):
+    """(tensor, rows, cols, ld): `t` seen as a row-major [rows, cols] matrix with leading dimension ld (elements)."""
+    rows = t.shape[0] if t.dim() else 1
+    cols = t.numel() // rows if rows else 0
+    if t.dim() <= 1:
+        t = t.contiguous()
+        return t, 1, t.numel(), max(t.numel(), 1)
+    if t.is_contiguous():
+        return t, rows, cols, max(cols, 1)
+    if rows > 0 and t[0].is_contiguous() and t.stride(0) >= cols:
+        return t, rows, cols, t.stride(0)
+    t = t.contiguous()
+    return t, rows, cols, max(cols, 1)
+
+
+def alloc_int8(shape, device, align: int = 16) -> torch.Tensor:
+    """int8 tensor of `shape` whose rows (dim 0) are padded to a multiple of `align` bytes: 16 for GEMM operands and
+    gathered feature rows (TMA and 128-bit loads), 4 is enough for per-head edge or node scalars."""
+    shape = tuple(shape)
+    if len(shape) < 2:
+        return torch.empty(shape, dtype=torch.int8, device=device)
+    rows, cols = shape[0], 1
+    for s in shape[1:]:
+        cols *= s
+    ld = _round_up(max(cols, 1), align)
+    store = torch.empty((rows, ld), dtype=torch.int8, device=device)
+    if ld == cols:
+        return store.view(shape)
+    v = store[:, :cols]
+    return v.unflatten(1, shape[1:]) if len(shape) > 2 else v
+
+
+_status = {}
+
+
+def device_status(device=None, reset: bool = False) -> int:
+    """Value of the per-device status word written by kernels with bounded waits (0 = no timeout).  Synchronises."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    t = _status.get(dev)
+    if t is None:
+        return 0
+    v = int(t.item())
+    if reset:
+        t.zero_()
+    return v
+
+
+def _status_word(device) -> torch.Tensor:
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    t = _status.get(dev)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[dev] = t
+    return t
+
+
+_call_counter = [0]
+
+
+def next_call() -> int:
+    """Monotonic per-process counter that keys the stochastic-rounding stream of successive calls."""
+    _call_counter[0] += 1
+    return _call_counter[0]
+
+
+def set_call_counter(v: int) -> None:
+    _call_counter[0] = int(v)
+
+
+def infer_broadcast_shape(op, ushape, vshape):
+    """Trailing-shape broadcast used by the SDDMM wrapper (dgl.sparse.infer_broadcast_shape in the reference,
+    cuda/kernels.py:3,49-50): NumPy broadcast, with the last dimension collapsed to 1 for 'dot'."""
+    ushape, vshape = tuple(ushape), tuple(vshape)
+    if op == "dot" and ushape[-1] != vshape[-1]:
+        raise ValueError("dot needs equal feature sizes")
+    n = max(len(ushape), len(vshape))
+    u = (1,) * (n - len(ushape)) + ushape
+    v = (1,) * (n - len(vshape)) + vshape
+    out = []
+    for a, b in zip(u, v):
+        if a != b and a != 1 and b != 1:
+            raise ValueError(f"cannot broadcast {ushape} with {vshape}")
+        out.append(max(a, b))
+    if op == "dot":
+        out[-1] = 1
+    return tuple(out)
+
+
+# --------------------------------------------------------------------------------------------------- native module
+def _get_scale(t: torch.Tensor, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    assert t.is_cuda and t.dtype == torch.float32
+    t, rows, cols, ld = _matrix(t)
+    scale = torch.empty(1, dtype=torch.float32, device=t.device)
+    with torch.cuda.device(t.device):
+        check(lib.tango_absmax_scale(_p(t), rows, cols, ld, _p(row_scale), _p(scale), _stream()), "get_scale")
+    return scale
+
+
+def _quantize_into(out: torch.Tensor, t: torch.Tensor, scale: torch.Tensor, mode: int = ROUND_NEAREST, seed: int = 0,
+                   call: int = 0, row_scale: Optional[torch.Tensor] = None) -> None:
+    assert t.is_cuda and out.is_cuda and out.dtype == torch.int8 and t.dtype == torch.float32
+    assert out.shape == t.shape
+    t, rows, cols, ldx = _matrix(t)
+    o2, orows, ocols, ldq = _matrix(out)
+    assert o2.data_ptr() == out.data_ptr(), "output int8 tensor must be row-strided, not arbitrary-strided"
+    with torch.cuda.device(t.device):
+        check(lib.tango_quantize(_p(t), rows, cols, ldx, _p(row_scale), _p(scale), _p(out), ldq, mode, seed, call,
+                                 _stream()), "quantize")
+
+
+def _transpose_quant(data: torch.Tensor, scale: torch.Tensor, nrow: int, ncol: int) -> torch.Tensor:
+    data = data.contiguous()
+    out = torch.empty((ncol, nrow), dtype=torch.int8, device=data.device)
+    with torch.cuda.device(data.device):
+        check(lib.tango_quantize_transpose(_p(data), nrow, ncol, _p(scale), _p(out), _stream()), "transpose_quant")
+    return out
+
+
+def _qgemm_forward(Y, X, X_q, W, W_q, bias, scaleY, scaleX, scaleW, mode=ROUND_TRUNC, seed=0, call=0):
+    X, m, k, ldx = _matrix(X)
+    W, n, k2, ldw = _matrix(W)
+    assert k == k2
+    _, _, _, ldxq = _matrix(X_q)
+    _, _, _, ldwq = _matrix(W_q)
+    _, _, _, ldy = _matrix(Y)
+    st = _status_word(X.device)
+    with torch.cuda.device(X.device):
+        check(lib.tango_qgemm_forward(_p(X), ldx, _p(W), ldw, m, n, k, _p(scaleX), _p(scaleW), _p(X_q), ldxq, _p(W_q),
+                                      ldwq, _p(bias), _p(Y), ldy, _p(scaleY), mode, seed, call, _p(st), _stream()),
+              "QGEMM_forward")
+
+
+def _qgemm_nt(Y, X_q, W_q, scaleX, scaleW, bias=None, scaleY=None):
+    _, m, k, ldx = _matrix(X_q)
+    _, n, _, ldw = _matrix(W_q)
+    _, _, _, ldy = _matrix(Y)
+    st = _status_word(X_q.device)
+    with torch.cuda.device(X_q.device):
+        check(lib.tango_qgemm_nt(_p(X_q), ldx, _p(W_q), ldw, m, n, k, _p(scaleX), _p(scaleW), _p(bias), _p(Y), ldy,
+                                 _p(scaleY), _p(st), _stream()), "qgemm_nt")
+
+
+def _qgemm_gradX(dX, dY_q, W_q, scaledY, scaleW):
+    _, m, n, lddy = _matrix(dY_q)
+    _, n2, k, ldw = _matrix(W_q)
+    assert n == n2
+    _, _, _, lddx = _matrix(dX)
+    st = _status_word(dX.device)
+    with torch.cuda.device(dX.device):
+        check(lib.tango_qgemm_dx(_p(dY_q), lddy, _p(W_q), ldw, m, n, k, _p(scaledY), _p(scaleW), _p(dX), lddx, _p(st),
+                                 _stream()), "QGEMM_backward_gradX")
+
+
+def _qgemm_gradW(dW, dY_q, X_q, scaledY, scaleX):
+    _, m, n, lddy = _matrix(dY_q)
+    _, m2, k, ldx = _matrix(X_q)
+    assert m == m2
+    _, _, _, lddw = _matrix(dW)
+    nbytes = lib.tango_qgemm_dw_workspace_bytes(n, k)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dW.device)
+    st = _status_word(dW.device)
+    with torch.cuda.device(dW.device):
+        check(lib.tango_qgemm_dw(_p(dY_q), lddy, _p(X_q), ldx, m, n, k, _p(scaledY), _p(scaleX), _p(dW), lddw, _p(ws),
+                                 nbytes, _p(st), _stream()), "QGEMM_backward_gradW")
+
+
+def _make_plan(sched: Optional[SpmmSchedule], f: int, device):
+    """ctypes plan + the tensors that must stay alive for the call."""
+    if sched is None or sched.n_units == 0:
+        return None, ()
+    ws_ld = _round_up(f, 16)
+    ws = torch.empty((sched.n_heavy * sched.nseg, ws_ld), dtype=torch.int32, device=device)
+    plan = SpmmPlan(sched.units.data_ptr(), sched.n_units, sched.heavy_rows.data_ptr(), sched.n_heavy, ws.data_ptr(),
+                    ws_ld, sched.threshold)
+    return ctypes.byref(plan), (plan, ws)
+
+
+def _csr_spmm(out, indptr, indices, U, scaleU, sched=None, nseg=1, row_scale=None, bias=None, relu=False,
+              out_absmax=None):
+    U, _, f, ldn = _matrix(U)
+    n_rows = (indptr.numel() - 1) // nseg
+    _, _, _, ldo = _matrix(out)
+    plan, keep = _make_plan(sched, f, U.device)
+    with torch.cuda.device(U.device):
+        check(lib.tango_spmm_copy_u(_p(indptr), _p(indices), n_rows, nseg, _p(U), ldn, f, _p(scaleU), _p(row_scale),
+                                    _p(bias), int(relu), _p(out), ldo, _p(out_absmax), plan, _stream()), "csr_SPMM")
+    del keep
+
+
+def _u_mul_e_spmm(indptr, indices, edge_ids, N, E, scale, sched=None):
+    """N int8 [Nn, H, D]; E int8 [nnz or E, H] (edge-id order when edge_ids is given, CSR-slot order otherwise)."""
+    assert N.dim() == 3
+    nn, h, d = N.shape
+    N, _, f, ldn = _matrix(N)
+    E = E.contiguous()
+    n_rows = indptr.numel() - 1
+    out = torch.empty((n_rows, h, d), dtype=torch.float32, device=N.device)
+    plan, keep = _make_plan(sched, f, N.device)
+    with torch.cuda.device(N.device):
+        check(lib.tango_spmm_u_mul_e(_p(indptr), _p(indices), _p(edge_ids), n_rows, _p(N), ldn, h, d, _p(E), _p(scale),
+                                     _p(out), f, plan, _stream()), "multi_cusparse_SPMM")
+    del keep
+    return out
+
+
+def _incidence_spmm(out, indptr, edge_ids, E, scale, sched=None):
+    E, _, f, ldz = _matrix(E)
+    n_rows = indptr.numel() - 1
+    _, _, _, ldo = _matrix(out)
+    plan, keep = _make_plan(sched, f, E.device)
+    with torch.cuda.device(E.device):
+        check(lib.tango_spmm_incidence(_p(indptr), _p(edge_ids), n_rows, _p(E), ldz, f, _p(scale), _p(out), ldo, plan,
+                                       _stream()), "incidence_SPMM")
+    del keep
+
+
+def _sddmm(op: str, out, scaleOut, src, dst, U, V, scaleU, scaleV):
+    n_edges = src.numel()
+    with torch.cuda.device(U.device):
+        if op == "dot":
+            h, d = U.shape[-2], U.shape[-1]
+            U2, _, _, ldu = _matrix(U)
+            V2, _, _, ldv = _matrix(V)
+            check(lib.tango_sddmm_dot(_p(src), _p(dst), n_edges, _p(U2), ldu, _p(V2), ldv, h, d, _p(scaleU),
+                                      _p(scaleV), _p(out), _p(scaleOut), _stream()), "mySDDMM_int8(dot)")
+        elif op in _lib.OPS:
+            U2, _, dim, ldu = _matrix(U)
+            V2, _, dimv, ldv = _matrix(V)
+            assert dim == dimv, "element-wise SDDMM needs equal feature shapes"
+            check(lib.tango_sddmm_elementwise(_lib.OPS[op], _p(src), _p(dst), n_edges, _p(U2), ldu, _p(V2), ldv, dim,
+                                              _p(scaleU), _p(scaleV), _p(out), _p(scaleOut), _stream()),
+                  f"mySDDMM_int8({op})")
+        else:
+            raise ValueError(f"{op} op not supported")
+
+
+def _qgemm_generic(kind: str, A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    """QgemmNT/NN/TN of the reference's legacy cuBLAS path (cuda/src/Qgemm_impl.cu:107-125): quantise both fp32
+    operands (nearest) and multiply.  Thin aliases of the tcgen05 GEMMs, kept for API completeness."""
+    sa, sb = _get_scale(A), _get_scale(B)
+    Aq, Bq = alloc_int8(A.shape, A.device), alloc_int8(B.shape, B.device)
+    _quantize_into(Aq, A, sa)
+    _quantize_into(Bq, B, sb)
+    if kind == "NT":      # A[M,K] . B[N,K]^T
+        out = torch.empty((A.shape[0], B.shape[0]), dtype=torch.float32, device=A.device)
+        _qgemm_nt(out, Aq, Bq, sa, sb)
+    elif kind == "NN":    # A[M,N] . B[N,K]
+        out = torch.empty((A.shape[0], B.shape[1]), dtype=torch.float32, device=A.device)
+        _qgemm_gradX(out, Aq, Bq, sa, sb)
+    else:                 # A[M,N]^T . B[M,K]
+        out = torch.empty((A.shape[1], B.shape[1]), dtype=torch.float32, device=A.device)
+        _qgemm_gradW(out, Aq, Bq, sa, sb)
+    return out
+
+
+def _spmv_stub(*args, **kwargs):
+    raise NotImplementedError("multi_cusparse_SPMV is an unfinished stub in the reference (cuda/src/SPMM.cu:196-257)")
+
+
+cuda_kernels = types.SimpleNamespace(
+    QGEMM_forward=_qgemm_forward,
+    quantize=lambda out, t, scale: _quantize_into(out, t, scale),
+    get_scale=_get_scale,
+    transpose_quant=_transpose_quant,
+    QgemmNT=lambda A, B: _qgemm_generic("NT", A, B),
+    QgemmTN=lambda A, B: _qgemm_generic("TN", A, B),
+    QgemmNN=lambda A, B: _qgemm_generic("NN", A, B),
+    QGEMM_backward_gradX=_qgemm_gradX,
+    QGEMM_backward_gradW=_qgemm_gradW,
+    csr_SPMM=lambda out, indptr, indices, U, scaleU: _csr_spmm(out, indptr, indices, U, scaleU),
+    multi_cusparse_SPMM=lambda indptr, indices, N, E_T, scale: _u_mul_e_spmm(
+        indptr, indices, None, N, E_T.reshape(E_T.shape[0], -1).t().contiguous(), scale),
+    incidence_SPMM=lambda out, src, dst, E, scale: _incidence_from_coo(out, src, dst, E, scale),
+    multi_cusparse_SPMV=_spmv_stub,
+    mySDDMM_int8=_sddmm,
+)
+
+
+def _incidence_from_coo(out, nodes, edge_ids, E, scale):
+    """Reference signature (cuda/src/SPMM.cu:259-303): COO rows = node ids (sorted, coalesced), cols = edge ids."""
+    n = out.shape[0]
+    counts = torch.bincount(nodes.long(), minlength=n)
+    indptr = torch.zeros(n + 1, dtype=torch.int64, device=nodes.device)
+    torch.cumsum(counts, 0, out=indptr[1:])
+    _incidence_spmm(out, indptr.to(torch.int32), edge_ids.to(torch.int32).contiguous(), E, scale)
+
+
+# --------------------------------------------------------------------------------------------------- wrappers
+def _schedule(g, reverse: bool) -> Optional[SpmmSchedule]:
+    plans = getattr(g, "_plans", None)
+    if plans is None:
+        return None
+    key = "csr" if reverse else "csc"
+    if key not in plans:
+        indptr = (g.adj_csr if reverse else g.adj_csc)[0]
+        plans[key] = SpmmSchedule(indptr)
+    return plans[key]
+
+
+def quantize(t: torch.Tensor, scale: torch.Tensor = None, mode: int = ROUND_NEAREST, seed: int = 0,
+             call: Optional[int] = None, align: int = 16):
+    """Quantize the input tensor to 8-bit (cuda/kernels.py:19-30).  Returns (int8 tensor, scale)."""
+    assert t.is_cuda, "tensor must be on GPU"
+    if scale is None:
+        scale = cuda_kernels.get_scale(t)
+    out = alloc_int8(t.shape, t.device, align)
+    if mode == ROUND_STOCHASTIC and call is None:
+        call = next_call()
+    _quantize_into(out, t, scale, mode, seed, call or 0)
+    return out, scale
+
+
+def mySDDMM_int8(g, op, U, V, scaleU, scaleV, isReduce, reverse=False):
+    """cuda/kernels.py:33-59."""
+    if reverse:
+        dst, src = g.coo
+    else:
+        src, dst = g.coo
+    assert src.is_cuda and dst.is_cuda and U.is_cuda and V.is_cuda and scaleU.is_cuda and scaleV.is_cuda
+    UV_unsqueezed = False
+    if len(U.shape) == 2 and len(V.shape) == 2:
+        U = U.unsqueeze(1)
+        V = V.unsqueeze(1)
+        UV_unsqueezed = True
+    out_shape = (src.size(0),) + infer_broadcast_shape(op, U.shape[1:], V.shape[1:])
+    out = torch.empty(out_shape, dtype=torch.float32, device=src.device)
+    scale = torch.zeros((1,), dtype=torch.float32, device=src.device) if isReduce else torch.Tensor()
+    cuda_kernels.mySDDMM_int8(op, out, scale, src, dst, U, V, scaleU, scaleV)
+    if UV_unsqueezed:
+        out = out.squeeze(1)
+    return out, scale
+
+
+def QGEMM_forward(x, x_, scaleX, w, w_, scaleW, bias=None, isReduce=False, mode: int = ROUND_TRUNC, seed: int = 0,
+                  call: Optional[int] = None):
+    """cuda/kernels.py:79-94.  x_ / w_ receive the quantized operands (allocate them with `alloc_int8`)."""
+    assert x.is_cuda and w.is_cuda and (bias is None or bias.is_cuda)
+    assert x.size(1) == w.size(1), "x and w must have the same number of columns"
+    out_fp = torch.empty((x.size(0), w.size(0)), dtype=torch.float32, device=x.device)
+    scale_out = torch.zeros_like(scaleX) if isReduce else torch.Tensor()
+    bias = torch.Tensor() if bias is None else bias
+    if mode == ROUND_STOCHASTIC and call is None:
+        call = next_call()
+        next_call()  # the weight draws from call + 1
+    cuda_kernels.QGEMM_forward(out_fp, x, x_, w, w_, bias, scale_out, scaleX, scaleW, mode, seed, call or 0)
+    return (out_fp, scale_out) if isReduce else out_fp
+
+
+def QGEMM_backward(dY, X, W, scaledY, scaleX, scaleW, X_need=True, W_need=True):
+    """cuda/kernels.py:97-111."""
+    assert scaledY.is_cuda and dY.is_cuda
+    dX, dW = None, None
+    if X_need:
+        assert W.is_cuda and scaleW.is_cuda
+        dX = torch.empty(X.shape, dtype=torch.float32, device=X.device)
+        cuda_kernels.QGEMM_backward_gradX(dX, dY, W, scaledY, scaleW)
+    if W_need:
+        assert X.is_cuda and scaleX.is_cuda
+        dW = torch.empty(W.shape, dtype=torch.float32, device=X.device)
+        cuda_kernels.QGEMM_backward_gradW(dW, dY, X, scaledY, scaleX)
+    return dX, dW
+
+
+def transpose_quant(data, scale):
+    """cuda/kernels.py:114-119: fp32 [E,H,D] -> int8 [H,D,E]."""
+    assert data.ndim == 3
+    nrow = data.size(0)
+    ncol = data.numel() // nrow
+    data_ = cuda_kernels.transpose_quant(data, scale, nrow, ncol)
+    return data_.reshape((data.size(1), data.size(2), nrow))
+
+
+def multi_cusparse_SPMM(g, N, E_T, scale, reverse=False):
+    """cuda/kernels.py:122-136.  E_T is int8 [H, 1, E] in edge-id order, as produced by `transpose_quant`; the
+    per-slot permutation by edge_ids that the reference performs with index_select happens inside the kernel."""
+    assert E_T.ndim == 3 and N.ndim == 3, "E and N must be 3D tensors"
+    assert E_T.size(1) == 1, "Cannot broadcast E"
+    indptr, indices, edge_ids = g.adj_csr if reverse else g.adj_csc
+    E = E_T.reshape(E_T.shape[0], -1).t().contiguous()  # [E, H]
+    return _u_mul_e_spmm(indptr, indices, edge_ids, N, E, scale, _schedule(g, reverse))
+
+
+def spmm_u_mul_e_int8(g, N, E, scale, reverse=False):
+    """Same product with the edge weights given as int8 [E, H] in edge-id order (no transposed copy)."""
+    indptr, indices, edge_ids = g.adj_csr if reverse else g.adj_csc
+    return _u_mul_e_spmm(indptr, indices, edge_ids, N, E.reshape(E.shape[0], -1), scale, _schedule(g, reverse))
+
+
+def incidence_SPMM(g, E, scaleE, reverse=False):
+    """cuda/kernels.py:139-152: sums int8 edge features into their destination (or source, if reverse) nodes."""
+    assert E.is_cuda and scaleE.is_cuda
+    indptr, _, edge_ids = g.adj_csr if reverse else g.adj_csc
+    out_shape = (g.num_nodes(),) + E.shape[1:]
+    dim = E.numel() // E.size(0)
+    out = torch.empty((g.num_nodes(), dim), dtype=torch.float32, device=E.device)
+    _incidence_spmm(out, indptr, edge_ids, E, scaleE, _schedule(g, reverse))
+    return out.view(out_shape)
+
+
+def csr_SPMM(g, N, scaleN, reverse=False, row_scale=None, bias=None, relu=False, out_absmax=None):
+    """cuda/kernels.py:154-165; the keyword arguments fuse out = act(out * row_scale[:,None] + bias)."""
+    indptr, indices, _ = g.adj_csr if reverse else g.adj_csc
+    out_shape = (g.num_nodes(),) + N.shape[1:]
+    dim = N.numel() // N.size(0)
+    out = torch.empty((g.num_nodes(), dim), dtype=torch.float32, device=N.device)
+    _csr_spmm(out, indptr, indices, N, scaleN, _schedule(g, reverse), 1, row_scale, bias, relu, out_absmax)
+    return out.view(out_shape)
+
+
+def multi_cusparse_SPMV(g, N_T, E_T, scale, reverse=False):
+    """cuda/kernels.py:167-178 forwards to multi_cusparse_SPMM in the reference; same here."""
+    return multi_cusparse_SPMM(g, N_T, E_T, scale, reverse)
+
+
+def gat_edge_softmax(g, elq, erq, sl, sr, slope: float = 0.2):
+    """Fused u_add_v -> LeakyReLU -> edge softmax over incoming edges; returns fp32 [E, H] in edge-id order."""
+    indptr, indices, edge_ids = g.adj_csc
+    h = elq.shape[1]
+    elq = elq.reshape(elq.shape[0], -1).contiguous()
+    erq = erq.reshape(erq.shape[0], -1).contiguous()
+    a = torch.empty((g.num_edges(), h), dtype=torch.float32, device=elq.device)
+    with torch.cuda.device(elq.device):
+        check(lib.tango_gat_edge_softmax(_p(indptr), _p(indices), _p(edge_ids), g.num_nodes(), _p(elq), _p(erq), h,
+                                         _p(sl), _p(sr), float(slope), _p(a), _stream()), "gat_edge_softmax")
+    return a

@@ -1,0 +1,326 @@
+"""Parity of every CUDA primitive against the CPU oracle, through the C ABI (ctypes) on a B200.
+
+Integer paths (quantized bytes, int32 accumulators and therefore every dequantized fp32 value, which is a single
+rounded product of an exact integer) must be bit-exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import tango_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def _scale_t(s):
+    return torch.tensor([float(s)], dtype=torch.float32, device="cuda")
+
+
+def _graph(n, e, seed, loops=True):
+    from tango_b200.graph import rmat_graph
+    g = rmat_graph(n, e, seed, device="cuda", self_loops=loops)
+    return g
+
+
+def _np_graph(g):
+    csr = [t.cpu().numpy().astype(np.int64) for t in g.adj_csr]
+    csc = [t.cpu().numpy().astype(np.int64) for t in g.adj_csc]
+    src, dst = [t.cpu().numpy().astype(np.int64) for t in g.coo]
+    return csr, csc, src, dst
+
+
+# ------------------------------------------------------------------------------------------------ quantisation
+@pytest.mark.parametrize("shape", [(1,), (7,), (4096,), (33, 41), (128, 602), (257, 256), (5, 3, 16), (1000, 4, 1)])
+def test_absmax_scale(cuda, shape):
+    from tango_b200 import kernels as K
+    x = np.random.default_rng(1).standard_normal(shape).astype(np.float32)
+    s = K.cuda_kernels.get_scale(_dev(x))
+    assert s.cpu().numpy()[0] == O.absmax_scale(x)
+
+
+def test_absmax_zero_and_empty(cuda):
+    from tango_b200 import kernels as K
+    assert K.cuda_kernels.get_scale(torch.zeros(100, device="cuda")).item() == 0.0
+    assert K.cuda_kernels.get_scale(torch.zeros((0, 8), device="cuda")).item() == 0.0
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("shape,align", [((64, 64), 16), ((33, 41), 16), ((128, 602), 16), ((1000, 4, 1), 1),
+                                         ((19, 3), 16), ((4099,), 16), ((37, 4), 1), ((50, 2, 24), 16)])
+def test_quantize_bit_exact(cuda, mode, shape, align):
+    from tango_b200 import kernels as K
+    rng = np.random.default_rng(7)
+    x = (rng.standard_normal(shape) * 3).astype(np.float32)
+    s = O.absmax_scale(x)
+    q, st = K.quantize(_dev(x), None, mode=mode, seed=1234, call=5, align=align)
+    assert st.item() == s
+    ref = O.quantize(x, s, mode, seed=1234, call=5)
+    got = q.cpu().numpy()
+    assert got.shape == ref.shape
+    np.testing.assert_array_equal(got, ref)
+    if q.dim() >= 2 and q.stride(0) != q[0].numel():   # padded storage: the pad bytes must be zero
+        store = torch.as_strided(q, (q.shape[0], q.stride(0)), (q.stride(0), 1))
+        assert int(store[:, q[0].numel():].abs().sum().item()) == 0
+
+
+def test_quantize_zero_scale_and_given_scale(cuda):
+    from tango_b200 import kernels as K
+    q, s = K.quantize(torch.zeros((8, 16), device="cuda"))
+    assert s.item() == 0 and int(q.abs().sum()) == 0
+    x = np.linspace(-4, 4, 64, dtype=np.float32).reshape(4, 16)
+    q, _ = K.quantize(_dev(x), _scale_t(0.01))           # saturates: clamp to +-127
+    np.testing.assert_array_equal(q.cpu().numpy(), O.quantize(x, np.float32(0.01)))
+    assert q.max().item() == 127 and q.min().item() == -127
+
+
+def test_quantize_row_scale(cuda):
+    from tango_b200 import kernels as K
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((100, 48)).astype(np.float32)
+    rs = rng.random(100).astype(np.float32)
+    xs = (x * rs[:, None]).astype(np.float32)
+    s = K._get_scale(_dev(x), _dev(rs))
+    assert s.item() == O.absmax_scale(xs)
+    out = K.alloc_int8(x.shape, "cuda")
+    K._quantize_into(out, _dev(x), s, 1, 0, 0, _dev(rs))
+    np.testing.assert_array_equal(out.cpu().numpy(), O.quantize(xs, O.absmax_scale(xs)))
+
+
+def test_stochastic_rounding_is_unbiased_and_seeded(cuda):
+    from tango_b200 import kernels as K
+    x = torch.full((1 << 16,), 0.3, device="cuda")
+    x[0] = 1.0                                          # scale = 1/127 -> 0.3 maps to 38.1
+    a, _ = K.quantize(x, None, mode=2, seed=9, call=1)
+    b, _ = K.quantize(x, None, mode=2, seed=9, call=1)
+    c, _ = K.quantize(x, None, mode=2, seed=9, call=2)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    mean = a[1:].float().mean().item()
+    assert abs(mean - 38.1) < 0.02
+    assert set(a[1:].unique().tolist()) == {38, 39}
+
+
+def test_transpose_quant(cuda):
+    from tango_b200 import kernels as K
+    rng = np.random.default_rng(11)
+    e = rng.random((1000, 4, 1)).astype(np.float32)
+    s = O.absmax_scale(e)
+    got = K.transpose_quant(_dev(e), _scale_t(s)).cpu().numpy()
+    np.testing.assert_array_equal(got, O.transpose_quant(e, s))
+    e2 = rng.standard_normal((77, 3, 5)).astype(np.float32)
+    s2 = O.absmax_scale(e2)
+    np.testing.assert_array_equal(K.transpose_quant(_dev(e2), _scale_t(s2)).cpu().numpy(), O.transpose_quant(e2, s2))
+
+
+# ------------------------------------------------------------------------------------------------ SpMM
+@pytest.mark.parametrize("f", [4, 16, 41, 128, 256, 602])
+def test_spmm_copy_u(cuda, f):
+    from tango_b200 import kernels as K
+    g = _graph(500, 6000, 3)
+    (csr, csc, src, dst) = _np_graph(g)
+    rng = np.random.default_rng(f)
+    nq = rng.integers(-127, 128, (500, f), dtype=np.int8)
+    nq_t = K.alloc_int8((500, f), "cuda"); nq_t.copy_(_dev(nq))
+    if nq_t.stride(0) != f:
+        torch.as_strided(nq_t, (500, nq_t.stride(0) - f), (nq_t.stride(0), 1), f).zero_()
+    s = np.float32(0.0371)
+    for reverse, (indptr, indices, _) in ((False, csc), (True, csr)):
+        out = K.csr_SPMM(g, nq_t, _scale_t(s), reverse).cpu().numpy()
+        np.testing.assert_array_equal(out, O.spmm_copy_u(indptr, indices, nq, s))
+
+
+def test_spmm_copy_u_unaligned_contiguous(cuda):
+    """API-level input: contiguous int8 with a row width that is not a multiple of 4 or 16."""
+    from tango_b200 import kernels as K
+    g = _graph(300, 2500, 5)
+    (_, csc, _, _) = _np_graph(g)
+    nq = np.random.default_rng(0).integers(-127, 128, (300, 41), dtype=np.int8)
+    out = K.csr_SPMM(g, _dev(nq), _scale_t(0.5)).cpu().numpy()
+    np.testing.assert_array_equal(out, O.spmm_copy_u(csc[0], csc[1], nq, np.float32(0.5)))
+
+
+def test_spmm_long_rows_use_units(cuda):
+    """A star graph: one row far above the split threshold, the rest of degree 1 (plus empty rows)."""
+    from tango_b200 import kernels as K
+    from tango_b200.graph import Graph
+    n = 20000
+    src = torch.arange(1, n - 5, dtype=torch.int32)
+    dst = torch.zeros_like(src)
+    extra_s = torch.arange(0, 3000, dtype=torch.int32)
+    extra_d = torch.full_like(extra_s, 7)
+    g = Graph(torch.cat([src, extra_s, dst[:50]]), torch.cat([dst, extra_d, src[:50]]), n).to("cuda")
+    sched = K._schedule(g, False)
+    assert sched.n_heavy == 1 and sched.n_units >= 9
+    (_, csc, _, _) = _np_graph(g)
+    nq = np.random.default_rng(2).integers(-127, 128, (n, 64), dtype=np.int8)
+    out = K.csr_SPMM(g, _dev(nq), _scale_t(0.25)).cpu().numpy()
+    np.testing.assert_array_equal(out, O.spmm_copy_u(csc[0], csc[1], nq, np.float32(0.25)))
+    out2 = K.csr_SPMM(g, _dev(nq), _scale_t(0.25)).cpu().numpy()      # scratch is re-zeroed per call
+    np.testing.assert_array_equal(out, out2)
+
+
+def test_spmm_fused_epilogue(cuda):
+    from tango_b200 import kernels as K
+    g = _graph(400, 5000, 8)
+    (_, csc, _, _) = _np_graph(g)
+    rng = np.random.default_rng(4)
+    nq = rng.integers(-127, 128, (400, 32), dtype=np.int8)
+    rs = rng.random(400).astype(np.float32)
+    bias = rng.standard_normal(32).astype(np.float32)
+    s = np.float32(0.01)
+    amax = torch.zeros(1, device="cuda")
+    out = K.csr_SPMM(g, _dev(nq), _scale_t(s), False, _dev(rs), _dev(bias), True, amax).cpu().numpy()
+    ref = O.spmm_copy_u(csc[0], csc[1], nq, s)
+    ref = np.maximum((ref * rs[:, None]).astype(np.float32) + bias[None, :], 0).astype(np.float32)
+    np.testing.assert_array_equal(out, ref)
+    assert amax.item() == O.absmax_scale(ref)
+
+
+@pytest.mark.parametrize("h,d", [(4, 64), (4, 32), (1, 41), (2, 24), (8, 1), (3, 5)])
+def test_spmm_u_mul_e(cuda, h, d):
+    from tango_b200 import kernels as K
+    g = _graph(300, 4000, 13)
+    (csr, csc, src, dst) = _np_graph(g)
+    E = g.num_edges()
+    rng = np.random.default_rng(h * 100 + d)
+    nq = rng.integers(-127, 128, (300, h, d), dtype=np.int8)
+    eq = rng.integers(-127, 128, (E, h), dtype=np.int8)
+    nq_t = K.alloc_int8((300, h, d), "cuda"); nq_t.copy_(_dev(nq))
+    ld = nq_t.stride(0)
+    if ld != h * d:
+        torch.as_strided(nq_t, (300, ld - h * d), (ld, 1), h * d).zero_()
+    s = np.float32(0.003)
+    for reverse, (indptr, indices, eids) in ((False, csc), (True, csr)):
+        out = K.spmm_u_mul_e_int8(g, nq_t, _dev(eq), _scale_t(s), reverse).cpu().numpy()
+        np.testing.assert_array_equal(out, O.spmm_u_mul_e(indptr, indices, eids, nq, eq, s))
+    # reference-shaped call: E_T [H,1,E] as produced by transpose_quant
+    e_t = _dev(np.ascontiguousarray(eq.T.reshape(h, 1, E)))
+    out = K.multi_cusparse_SPMM(g, nq_t, e_t, _scale_t(s)).cpu().numpy()
+    np.testing.assert_array_equal(out, O.spmm_u_mul_e(csc[0], csc[1], csc[2], nq, eq, s))
+
+
+@pytest.mark.parametrize("dim", [1, 4, 16, 32])
+def test_incidence_spmm(cuda, dim):
+    from tango_b200 import kernels as K
+    g = _graph(300, 4000, 17)
+    (csr, csc, src, dst) = _np_graph(g)
+    E = g.num_edges()
+    zq = np.random.default_rng(dim).integers(-127, 128, (E, dim), dtype=np.int8)
+    s = np.float32(0.02)
+    out_in = K.incidence_SPMM(g, _dev(zq), _scale_t(s)).cpu().numpy()
+    out_out = K.incidence_SPMM(g, _dev(zq), _scale_t(s), True).cpu().numpy()
+    np.testing.assert_array_equal(out_in, O.spmm_incidence(csc[0], csc[2], zq, s))
+    np.testing.assert_array_equal(out_out, O.spmm_incidence(csr[0], csr[2], zq, s))
+    # the same sums straight from the definition: node v collects the edges whose dst (src) is v
+    acc = np.zeros((300, dim), dtype=np.int64)
+    np.add.at(acc, dst, zq.astype(np.int64))
+    np.testing.assert_array_equal(out_in, (acc.astype(np.float32) * s).astype(np.float32))
+    # reference-shaped native call with explicit COO (node, edge id) pairs
+    inc = g.inc_in
+    out = torch.empty((300, dim), device="cuda")
+    K.cuda_kernels.incidence_SPMM(out, inc[0], inc[1], _dev(zq), _scale_t(s))
+    np.testing.assert_array_equal(out.cpu().numpy(), out_in)
+
+
+def test_spmm_segmented_per_shard_scales(cuda):
+    """Row-partitioned form: nseg segments per row, one scale per source shard."""
+    from tango_b200 import kernels as K
+    from tango_b200.graph import RowPartition
+    g = _graph(1000, 20000, 19)
+    (_, csc, _, _) = _np_graph(g)
+    world = 4
+    nq = np.random.default_rng(5).integers(-127, 128, (1000, 64), dtype=np.int8)
+    scales = np.array([0.01, 0.02, 0.005, 0.04], dtype=np.float32)
+    ref = O.spmm_copy_u(csc[0], csc[1], nq, scales, shard_rows=250)
+    for rank in range(world):
+        part = RowPartition(g.adj_csc[0], g.adj_csc[1], None, 1000, rank, world)
+        out = torch.empty((part.n_local, 64), device="cuda")
+        K._csr_spmm(out, part.indptr, part.indices, _dev(nq), _dev(scales), part.schedule, world)
+        np.testing.assert_array_equal(out.cpu().numpy(), ref[part.r0:part.r1])
+
+
+# ------------------------------------------------------------------------------------------------ SDDMM
+@pytest.mark.parametrize("h,d", [(1, 128), (4, 64), (4, 32), (1, 41), (2, 24), (3, 5), (1, 256)])
+def test_sddmm_dot(cuda, h, d):
+    from tango_b200 import kernels as K
+    g = _graph(300, 4000, 23)
+    (_, _, src, dst) = _np_graph(g)
+    rng = np.random.default_rng(d)
+    uq = rng.integers(-127, 128, (300, h, d), dtype=np.int8)
+    vq = rng.integers(-127, 128, (300, h, d), dtype=np.int8)
+    u_t = K.alloc_int8(uq.shape, "cuda"); u_t.copy_(_dev(uq))
+    v_t = K.alloc_int8(vq.shape, "cuda"); v_t.copy_(_dev(vq))
+    for t in (u_t, v_t):
+        if t.stride(0) != h * d:
+            torch.as_strided(t, (300, t.stride(0) - h * d), (t.stride(0), 1), h * d).zero_()
+    su, sv = np.float32(0.01), np.float32(0.03)
+    out, sc = K.mySDDMM_int8(g, "dot", u_t, v_t, _scale_t(su), _scale_t(sv), True)
+    ref = O.sddmm_dot(src, dst, uq, vq, su, sv)
+    assert out.shape == (g.num_edges(), h, 1)
+    np.testing.assert_array_equal(out.cpu().numpy()[..., 0], ref)
+    assert sc.item() == O.absmax_scale(ref)
+    out_r, _ = K.mySDDMM_int8(g, "dot", u_t, v_t, _scale_t(su), _scale_t(sv), False, reverse=True)
+    np.testing.assert_array_equal(out_r.cpu().numpy()[..., 0], O.sddmm_dot(dst, src, uq, vq, su, sv))
+
+
+def test_sddmm_recipe_fixture(cuda):
+    """The 3-node / 4-edge input recipe the reference keeps under #ifdef TEST (cuda/src/SDDMM.cu:230-257)."""
+    from tango_b200 import kernels as K
+    from tango_b200.graph import Graph
+    for dim in (16, 64, 100):
+        src, dst, u, v, su, sv = O.recipe_sddmm_inputs(dim)
+        g = Graph(torch.from_numpy(src), torch.from_numpy(dst), 3).to("cuda")
+        out, _ = K.mySDDMM_int8(g, "add", _dev(u), _dev(v), _scale_t(su), _scale_t(sv), False)
+        np.testing.assert_array_equal(out.cpu().numpy().reshape(4, -1), O.sddmm_elementwise("add", src, dst, u, v, su, sv))
+        out, _ = K.mySDDMM_int8(g, "dot", _dev(u), _dev(v), _scale_t(su), _scale_t(sv), False)
+        np.testing.assert_array_equal(out.cpu().numpy().reshape(4, -1), O.sddmm_dot(src, dst, u, v, su, sv))
+
+
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "div"])
+@pytest.mark.parametrize("shape", [(4, 1), (1, 16), (3, 5), (1, 41)])
+def test_sddmm_elementwise(cuda, op, shape):
+    from tango_b200 import kernels as K
+    g = _graph(300, 4000, 29)
+    (_, _, src, dst) = _np_graph(g)
+    rng = np.random.default_rng(1)
+    uq = rng.integers(-127, 128, (300,) + shape, dtype=np.int8)
+    vq = rng.integers(1, 128, (300,) + shape, dtype=np.int8)        # non-zero divisor
+    su, sv = np.float32(0.01), np.float32(0.03)
+    out, sc = K.mySDDMM_int8(g, op, _dev(uq), _dev(vq), _scale_t(su), _scale_t(sv), True)
+    ref = O.sddmm_elementwise(op, src, dst, uq, vq, su, sv)
+    np.testing.assert_array_equal(out.cpu().numpy().reshape(ref.shape), ref)
+    assert sc.item() == O.absmax_scale(ref)
+
+
+def test_gat_edge_softmax(cuda):
+    from tango_b200 import kernels as K
+    g = _graph(200, 3000, 31)
+    (_, csc, src, dst) = _np_graph(g)
+    rng = np.random.default_rng(2)
+    el = rng.integers(-127, 128, (200, 4), dtype=np.int8)
+    er = rng.integers(-127, 128, (200, 4), dtype=np.int8)
+    sl, sr = np.float32(0.02), np.float32(0.015)
+    a = K.gat_edge_softmax(g, _dev(el), _dev(er), _scale_t(sl), _scale_t(sr), 0.2).cpu().numpy()
+    z = O.leaky_relu(O.sddmm_elementwise("add", src, dst, el, er, sl, sr), 0.2)
+    ref = O.edge_softmax(csc[0], csc[2], z)
+    np.testing.assert_allclose(a, ref, rtol=1e-4, atol=1e-6)   # fp32 exp: tolerance, not bit-exact
+    sums = np.zeros((200, 4)); np.add.at(sums, dst, a)
+    np.testing.assert_allclose(sums, 1.0, rtol=1e-5)
+
+
+# ------------------------------------------------------------------------------------------------ empty inputs
+def test_empty_graph_and_rows(cuda):
+    from tango_b200 import kernels as K
+    from tango_b200.graph import Graph
+    g = Graph(torch.zeros(0, dtype=torch.int32), torch.zeros(0, dtype=torch.int32), 10).to("cuda")
+    nq = torch.ones((10, 16), dtype=torch.int8, device="cuda")
+    out = K.csr_SPMM(g, nq, _scale_t(1.0))
+    assert out.shape == (10, 16) and float(out.abs().sum()) == 0.0
+    o, _ = K.mySDDMM_int8(g, "dot", nq, nq, _scale_t(1.0), _scale_t(1.0), False)
+    assert o.shape == (0, 1)
