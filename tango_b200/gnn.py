@@ -1,0 +1,206 @@
+"""The evaluation models of the reference (QGraphConv / GCN from evaluation/test_gcn.py:40-175, QGATConv / GAT from
+evaluation/test_gat.py:30-224) re-hosted on the DGL-free `Graph`, built only from the quantized operators of this
+package.  They are the callers of the hot path: the epoch benchmark and the end-to-end parity tests run them.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.autograd.function import Function, once_differentiable
+
+from . import config, kernels
+from .QLinear import QLinear, Qlinear_func, Qlinear_func_reduce
+from .SDDMM import sddmm_u_add_v
+from .SPMM import spmm_copy_u, spmm_u_mul_e
+
+
+def _norm(deg: torch.Tensor, both: bool) -> torch.Tensor:
+    d = deg.float().clamp(min=1)
+    return torch.pow(d, -0.5) if both else 1.0 / d
+
+
+class QGraphConv(nn.Module):
+    """Graph convolution with int8 GEMM and int8 aggregation (evaluation/test_gcn.py:40-139).  As in the reference,
+    the linear layer runs first when it shrinks the features (and hands its output scale to the aggregation), else
+    the aggregation runs first."""
+
+    def __init__(self, in_feats, out_feats, norm="both", weight=True, bias=True, activation=None,
+                 allow_zero_in_degree=False):
+        super().__init__()
+        if norm not in ("none", "both", "right", "left"):
+            raise ValueError(f'Invalid norm value "{norm}"')
+        self._in_feats, self._out_feats, self._norm = in_feats, out_feats, norm
+        self._allow_zero_in_degree = allow_zero_in_degree
+        self.weight = nn.Parameter(torch.empty(out_feats, in_feats)) if weight else None
+        self.bias = nn.Parameter(torch.empty(out_feats)) if bias else None
+        self._activation = activation
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        if self.weight is not None:
+            nn.init.xavier_uniform_(self.weight)
+        if self.bias is not None:
+            nn.init.zeros_(self.bias)
+
+    def forward(self, graph, feat):
+        if not self._allow_zero_in_degree and bool((graph.in_degrees() == 0).any()):
+            raise RuntimeError("There are 0-in-degree nodes in the graph; add self loops first")
+        feat_src = feat
+        if self._norm in ("left", "both"):
+            feat_src = feat_src * _norm(graph.out_degrees(), self._norm == "both").unsqueeze(1)
+        if self._in_feats > self._out_feats:
+            if self.weight is not None:
+                feat_src, s = Qlinear_func_reduce.apply(feat_src, self.weight)
+                rst = spmm_copy_u.apply(graph, feat_src, s)
+            else:
+                rst = spmm_copy_u.apply(graph, feat_src)
+        else:
+            rst = spmm_copy_u.apply(graph, feat_src)
+            if self.weight is not None:
+                rst = Qlinear_func.apply(rst, self.weight)
+        if self._norm in ("right", "both"):
+            rst = rst * _norm(graph.in_degrees(), self._norm == "both").unsqueeze(1)
+        if self.bias is not None:
+            rst = rst + self.bias
+        if self._activation is not None:
+            rst = self._activation(rst)
+        return rst
+
+
+class GCN(nn.Module):
+    """Stack of QGraphConv layers (evaluation/test_gcn.py:143-175): in -> hidden (x n_layers) -> classes."""
+
+    def __init__(self, g, in_feats, n_hidden, n_classes, n_layers, activation=F.relu, dropout=0.0):
+        super().__init__()
+        self.g = g
+        self.layers = nn.ModuleList()
+        self.layers.append(QGraphConv(in_feats, n_hidden, activation=activation))
+        for _ in range(n_layers - 1):
+            self.layers.append(QGraphConv(n_hidden, n_hidden, activation=activation))
+        self.layers.append(QGraphConv(n_hidden, n_classes))
+        self.dropout = nn.Dropout(p=dropout)
+
+    def forward(self, features):
+        h = features
+        for i, layer in enumerate(self.layers):
+            if i != 0:
+                h = self.dropout(h)
+            h = layer(self.g, h)
+        return h
+
+
+# ---------------------------------------------------------------------------------------------------- GAT
+class _edge_softmax_fn(Function):
+    """Softmax of edge scores over the incoming edges of every destination, per head (the reference calls
+    dgl.ops.edge_softmax, evaluation/test_gat.py:146).  fp32, as in the reference."""
+
+    @staticmethod
+    def forward(ctx, g, e):
+        _, dst = g.coo
+        shape = e.shape
+        e2 = e.reshape(shape[0], -1)
+        n = g.num_nodes()
+        idx = dst.long().unsqueeze(1).expand_as(e2)
+        m = torch.full((n, e2.shape[1]), float("-inf"), device=e.device).scatter_reduce(0, idx, e2, "amax")
+        ex = torch.exp(e2 - m[dst.long()])
+        s = torch.zeros((n, e2.shape[1]), device=e.device).index_add_(0, dst.long(), ex)
+        a = ex / s[dst.long()]
+        ctx.save_for_backward(a)
+        ctx.g = g
+        return a.reshape(shape)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, da):
+        (a,) = ctx.saved_tensors
+        _, dst = ctx.g.coo
+        da2 = da.reshape(a.shape)
+        t = a * da2
+        acc = torch.zeros((ctx.g.num_nodes(), a.shape[1]), device=a.device).index_add_(0, dst.long(), t)
+        return None, (t - a * acc[dst.long()]).reshape(da.shape)
+
+
+def edge_softmax(g, e):
+    return _edge_softmax_fn.apply(g, e)
+
+
+class QGATConv(nn.Module):
+    """Graph attention layer on the quantized operators (evaluation/test_gat.py:30-169): QLinear projection,
+    int8 u_add_v edge logits, LeakyReLU, edge softmax (fp32), int8 u_mul_e aggregation."""
+
+    def __init__(self, in_feats, out_feats, num_heads, feat_drop=0.0, attn_drop=0.0, negative_slope=0.2,
+                 residual=False, activation=None, allow_zero_in_degree=False, bias=True):
+        super().__init__()
+        self._num_heads, self._in_feats, self._out_feats = num_heads, in_feats, out_feats
+        self._allow_zero_in_degree = allow_zero_in_degree
+        self.fc = QLinear(in_feats, out_feats * num_heads, bias=False)
+        self.attn_l = nn.Parameter(torch.empty(1, num_heads, out_feats))
+        self.attn_r = nn.Parameter(torch.empty(1, num_heads, out_feats))
+        self.feat_drop = nn.Dropout(feat_drop)
+        self.attn_drop = nn.Dropout(attn_drop)
+        self.leaky_relu = nn.LeakyReLU(negative_slope)
+        self.bias = nn.Parameter(torch.empty(num_heads * out_feats)) if bias else None
+        if residual:
+            self.res_fc = (QLinear(in_feats, num_heads * out_feats, bias=False)
+                           if in_feats != out_feats * num_heads else nn.Identity())
+        else:
+            self.res_fc = None
+        self.activation = activation
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        gain = nn.init.calculate_gain("relu")
+        nn.init.xavier_normal_(self.fc.weight, gain=gain)
+        nn.init.xavier_normal_(self.attn_l, gain=gain)
+        nn.init.xavier_normal_(self.attn_r, gain=gain)
+        if self.bias is not None:
+            nn.init.constant_(self.bias, 0)
+        if isinstance(self.res_fc, QLinear):
+            nn.init.xavier_normal_(self.res_fc.weight, gain=gain)
+
+    def forward(self, graph, feat, get_attention=False):
+        if not self._allow_zero_in_degree and bool((graph.in_degrees() == 0).any()):
+            raise RuntimeError("There are 0-in-degree nodes in the graph.")
+        prefix = feat.shape[:-1]
+        h = self.feat_drop(feat).contiguous()
+        ft = self.fc(h).view(*prefix, self._num_heads, self._out_feats)
+        el = (ft * self.attn_l).sum(dim=-1).unsqueeze(-1)
+        er = (ft * self.attn_r).sum(dim=-1).unsqueeze(-1)
+        e = self.leaky_relu(sddmm_u_add_v.apply(graph, el, er))
+        a = self.attn_drop(edge_softmax(graph, e))
+        rst = spmm_u_mul_e.apply(graph, ft, a)
+        if self.res_fc is not None:
+            rst = rst + self.res_fc(h).view(*prefix, -1, self._out_feats)
+        if self.bias is not None:
+            rst = rst + self.bias.view(*((1,) * len(prefix)), self._num_heads, self._out_feats)
+        if self.activation:
+            rst = self.activation(rst)
+        return (rst, a) if get_attention else rst
+
+
+class GAT(nn.Module):
+    """evaluation/test_gat.py:172-224."""
+
+    def __init__(self, g, num_layers, in_dim, num_hidden, num_classes, heads, activation=F.elu, feat_drop=0.0,
+                 attn_drop=0.0, negative_slope=0.2, residual=False):
+        super().__init__()
+        self.g, self.num_layers = g, num_layers
+        self.gat_layers = nn.ModuleList()
+        if num_layers > 1:
+            self.gat_layers.append(QGATConv(in_dim, num_hidden, heads[0], feat_drop, attn_drop, negative_slope,
+                                            False, activation))
+            for l in range(1, num_layers - 1):
+                self.gat_layers.append(QGATConv(num_hidden * heads[l - 1], num_hidden, heads[l], feat_drop, attn_drop,
+                                                negative_slope, residual, activation))
+            self.gat_layers.append(QGATConv(num_hidden * heads[-2], num_classes, heads[-1], feat_drop, attn_drop,
+                                            negative_slope, residual, None))
+        else:
+            self.gat_layers.append(QGATConv(in_dim, num_classes, heads[0], feat_drop, attn_drop, negative_slope,
+                                            residual, None))
+
+    def forward(self, inputs):
+        h = inputs
+        for l in range(self.num_layers - 1):
+            h = self.gat_layers[l](self.g, h).flatten(1)
+        return self.gat_layers[-1](self.g, h).mean(1)

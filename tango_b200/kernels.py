@@ -37,6 +37,14 @@ def _p(t: Optional[torch.Tensor]):
     return None if t is None or t.numel() == 0 else t.data_ptr()
 
 
+def _pi(t: torch.Tensor):
+    """Pointer of a mandatory index array; an empty one (graph without edges) still needs a valid address."""
+    if t.numel() == 0:
+        t = torch.zeros(1, dtype=torch.int32, device=t.device)
+        _pi.keep = t
+    return t.data_ptr()
+
+
 def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
@@ -227,7 +235,7 @@ def _csr_spmm(out, indptr, indices, U, scaleU, sched=None, nseg=1, row_scale=Non
     _, _, _, ldo = _matrix(out)
     plan, keep = _make_plan(sched, f, U.device)
     with torch.cuda.device(U.device):
-        check(lib.tango_spmm_copy_u(_p(indptr), _p(indices), n_rows, nseg, _p(U), ldn, f, _p(scaleU), _p(row_scale),
+        check(lib.tango_spmm_copy_u(_p(indptr), _pi(indices), n_rows, nseg, _p(U), ldn, f, _p(scaleU), _p(row_scale),
                                     _p(bias), int(relu), _p(out), ldo, _p(out_absmax), plan, _stream()), "csr_SPMM")
     del keep
 
@@ -242,7 +250,7 @@ def _u_mul_e_spmm(indptr, indices, edge_ids, N, E, scale, sched=None):
     out = torch.empty((n_rows, h, d), dtype=torch.float32, device=N.device)
     plan, keep = _make_plan(sched, f, N.device)
     with torch.cuda.device(N.device):
-        check(lib.tango_spmm_u_mul_e(_p(indptr), _p(indices), _p(edge_ids), n_rows, _p(N), ldn, h, d, _p(E), _p(scale),
+        check(lib.tango_spmm_u_mul_e(_p(indptr), _pi(indices), _p(edge_ids), n_rows, _p(N), ldn, h, d, _p(E), _p(scale),
                                      _p(out), f, plan, _stream()), "multi_cusparse_SPMM")
     del keep
     return out
