@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized GCN training epoch (the workload BASELINE.json's metric is quoted on).
+
+    python bench.py --gpus N --steps K --warmup W            # this library, N GPUs (torchrun for N > 1)
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's fp32 formulation on the host cores
+
+Workload "gcn_c5": 2-layer GCN 602 -> 256 -> 41 (norm='both', ReLU) on a seeded R-MAT graph with 232,965 nodes and
+114,615,892 directed edges including one self loop per node; features fp32 N(0,1), uniform random labels.  One
+step = forward + mean cross-entropy over all nodes + backward + Adam update: one full-graph training epoch.  The
+synthetic graph stands in for the Reddit graph the reference's scripts load; nothing of that dataset is used.
+
+Prints ONE JSON line (rank 0).  `value` is the epoch time in ms with the inputs resident in HBM; `e2e` is the same
+epoch with the features and labels copied from pinned host memory and the loss read back inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (nodes, directed non-loop edges, in_feats, hidden, classes, graph seed)
+    "gcn_c5": (232_965, 114_615_892 - 232_965, 602, 256, 41, 20245),
+    "gcn_c1": (19_717, 88_648, 500, 16, 3, 20241),
+}
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            p = [x.strip() for x in ln.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1])); mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, p[5:9]):
+                if v.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_graph(name: str, device):
+    from tango_b200.graph import rmat_graph
+    n, e, *_rest, seed = WORKLOADS[name]
+    return rmat_graph(n, e, seed, device=device)
+
+
+def make_inputs(name: str, lo: int, hi: int, pin: bool):
+    """Seeded features / labels for node rows [lo, hi) on the host (generated per row block so that a partition sees
+    the same values as the single-GPU run)."""
+    import torch
+    n, _, in_feats, _, classes, _ = WORKLOADS[name]
+    gen = torch.Generator().manual_seed(3)
+    feats = torch.randn((n, in_feats), generator=gen)[lo:hi].contiguous()
+    gen = torch.Generator().manual_seed(5)
+    labels = torch.randint(0, classes, (n,), generator=gen)[lo:hi].contiguous()
+    if pin:
+        feats, labels = feats.pin_memory(), labels.pin_memory()
+    return feats, labels
+
+
+# ----------------------------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    """The reference's fp32 DGL/PyTorch formulation of the epoch on the host cores (restated without DGL in
+    oracle/fp32_baseline.py), full workload, all host threads."""
+    import torch
+    import torch.nn.functional as F
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import fp32_baseline as B
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    name = args.workload
+    n, _, in_feats, hidden, classes, _ = WORKLOADS[name]
+    dev = "cuda" if torch.cuda.is_available() else "cpu"   # the synthetic graph is only *generated* on the GPU
+    g = build_graph(name, dev)
+    csc = [t.cpu() for t in g.adj_csc]
+    csr = [t.cpu() for t in g.adj_csr]
+    ind, outd = g.in_degrees().cpu(), g.out_degrees().cpu()
+    n_edges = g.num_edges()
+    del g
+    a, a_t = B.csr_matrix(csc[0], csc[1], n), B.csr_matrix(csr[0], csr[1], n)
+    torch.manual_seed(6)
+    w1 = torch.nn.init.xavier_uniform_(torch.empty(hidden, in_feats))
+    w2 = torch.nn.init.xavier_uniform_(torch.empty(classes, hidden))
+    model = B.GCNfp32(a, a_t, outd, ind, [w1, w2], [torch.zeros(hidden), torch.zeros(classes)])
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2, weight_decay=5e-4)
+    feats, labels = make_inputs(name, 0, n, False)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        loss = F.cross_entropy(model(feats), labels)
+        loss.backward()
+        opt.step()
+        return float(loss)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    ms = (time.perf_counter() - t0) * 1e3 / max(1, args.steps)
+    line = {
+        "impl": "reference", "metric": "gcn_epoch_ms", "value": ms, "unit": "ms", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "nodes": n, "edges": n_edges, "layers": f"{in_feats}-{hidden}-{classes}",
+                   "timing": "host wall clock, inputs larger than L2"},
+        "cpu_baseline": {"value": ms, "unit": "ms", "cores": cores, "kind": "port",
+                         "sample": "full epoch (all nodes, all edges), fp32 torch CPU formulation"},
+        "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------- this library
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    import tango_b200 as T
+    from tango_b200 import kernels as K
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    name = args.workload
+    n, _, in_feats, hidden, classes, _ = WORKLOADS[name]
+    T.config.set_rounding(args.rounding, seed=1234)
+    g = build_graph(name, dev)
+    n_edges = g.num_edges()
+    torch.manual_seed(6)
+    if world == 1:
+        from tango_b200.gnn import GCN
+        T.graph_preprocess(g)
+        model = GCN(g, in_feats, hidden, classes, 1).to(dev)
+        lo, hi = 0, n
+    else:
+        from tango_b200.dist import DistGCN, DistGraph, allreduce_grads
+        dg = DistGraph(g, rank, world)
+        del g
+        torch.cuda.empty_cache()
+        model = DistGCN(dg, in_feats, hidden, classes, 1).to(dev)
+        lo, hi = dg.r0, dg.r1
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2, weight_decay=5e-4)
+    h_feats, h_labels = make_inputs(name, lo, hi, True)
+    d_feats, d_labels = h_feats.to(dev), h_labels.to(dev)
+
+    def step(feats, labels):
+        opt.zero_grad(set_to_none=True)
+        logits = model(feats)
+        loss = F.cross_entropy(logits, labels, reduction="sum") / n
+        loss.backward()
+        if world > 1:
+            allreduce_grads(model)
+        opt.step()
+        return loss
+
+    def step_e2e():
+        f = h_feats.to(dev, non_blocking=True)
+        l = h_labels.to(dev, non_blocking=True)
+        return float(step(f, l))      # .item(): device -> host read of the loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms) / steps
+
+    for _ in range(max(3, args.warmup)):
+        step(d_feats, d_labels)
+    K.launch_counter[0] = 0
+    step(d_feats, d_labels)
+    launches = K.launch_counter[0]
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda: step(d_feats, d_labels), args.steps)
+    ms_e2e = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    loss = float(step(d_feats, d_labels))
+    if world > 1:
+        lt = torch.tensor([loss], device=dev)
+        dist.all_reduce(lt)
+        loss = float(lt)
+    status = K.device_status()
+
+    # dominant kernel on its own: the layer-1 aggregation (int8 features of width `hidden`) on this rank's rows
+    peaks, peak_kind = _peaks()
+    roof = None
+    if world == 1:
+        x = torch.randn((n, hidden), device=dev)
+        q, s = K.quantize(x)
+        for _ in range(3):
+            K.csr_SPMM(g, q, s)
+        torch.cuda.synchronize()
+        reps = 10
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            K.csr_SPMM(g, q, s)
+        e1.record()
+        torch.cuda.synchronize()
+        k_ms = e0.elapsed_time(e1) / reps
+        alg = n * hidden + 4 * n_edges + 4 * (n + 1) + 4 * n * hidden      # features + CSR + fp32 output, once each
+        touched = n_edges * hidden + 4 * n_edges + 4 * (n + 1) + 4 * n * hidden
+        ach = alg / (k_ms * 1e-3) / 1e9
+        roof = {"kernel": "spmm_kernel<16,copy_u> F=256 (layer-1 aggregation)", "bound": "hbm", "achieved": ach,
+                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                "peak_source": peak_kind, "kernel_ms": k_ms, "algorithmic_bytes": alg,
+                "gathered_bytes_per_s_GB": touched / (k_ms * 1e-3) / 1e9,
+                "note": "gathers of E*F bytes are served by L2; see DESIGN.md"}
+
+    cpu_base = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        cpu_base = _cpu_baseline(name, g, model)
+
+    if rank == 0:
+        line = {
+            "metric": "gcn_epoch_ms", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+            "config": {"workload": name, "nodes": n, "edges": n_edges, "layers": f"{in_feats}-{hidden}-{classes}",
+                       "rounding": args.rounding, "parallelism": f"row-partition x{world}",
+                       "timing": "CUDA events, inputs larger than L2 (no flush)"},
+            "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": (h_feats.numel() * 4 + h_labels.numel() * 8),
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
+            "clocks": clocks, "loss": loss, "status_word": status,
+        }
+        if roof:
+            line["roofline"] = roof
+        if cpu_base:
+            line["cpu_baseline"] = cpu_base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _cpu_baseline(name, g, model):
+    """One fp32 epoch (forward + loss + backward + Adam) of the reference's DGL/PyTorch formulation on the host
+    cores, same graph, same initial weights: 1 warm-up + 1 timed epoch."""
+    import torch
+    import torch.nn.functional as F
+    from oracle import fp32_baseline as B
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n = g.num_nodes()
+    csc, csr = g.adj_csc, g.adj_csr
+    a, a_t = B.csr_matrix(csc[0], csc[1], n), B.csr_matrix(csr[0], csr[1], n)
+    ws = [l.weight for l in model.layers]
+    bs = [l.bias for l in model.layers]
+    ref = B.GCNfp32(a, a_t, g.out_degrees(), g.in_degrees(), ws, bs)
+    opt = torch.optim.Adam(ref.parameters(), lr=1e-2, weight_decay=5e-4)
+    feats, labels = make_inputs(name, 0, n, False)
+    times = []
+    for _ in range(2):
+        t0 = time.perf_counter()
+        opt.zero_grad(set_to_none=True)
+        loss = F.cross_entropy(ref(feats), labels)
+        loss.backward()
+        opt.step()
+        times.append((time.perf_counter() - t0) * 1e3)
+    return {"value": times[-1], "unit": "ms", "cores": cores, "kind": "port",
+            "sample": "one full epoch (all nodes and edges) after one warm-up epoch; fp32 torch CPU formulation"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gcn_c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--rounding", default="reference", choices=["reference", "nearest", "stochastic"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -94,8 +94,14 @@ def absmax_scale(x: np.ndarray) -> np.float32:
 
 
 def inv_scale(scale) -> np.float32:
+    """1/scale as one fp32 division; 0 when scale is 0 or so small (subnormal) that the reciprocal overflows -- a
+    tensor whose absmax is below ~4e-37 quantizes to all zeros instead of producing inf * 0 = NaN."""
     s = F32(scale)
-    return F32(0) if s == 0 else F32(F32(1.0) / s)
+    if s == 0:
+        return F32(0)
+    with np.errstate(over="ignore"):
+        inv = F32(F32(1.0) / s)
+    return inv if np.isfinite(inv) else F32(0)
 
 
 def quantize(x: np.ndarray, scale, mode: int = ROUND_NEAREST, seed: int = 0,

@@ -54,7 +54,12 @@ __device__ __forceinline__ void block_absmax_to_scale(float thread_max, float *s
     }
 }
 
-__device__ __forceinline__ float inv_scale(float s) { return s == 0.f ? 0.f : __fdiv_rn(1.0f, s); }
+// 1/s; 0 when s is 0 or so small (subnormal) that the reciprocal overflows, so such tensors quantize to zeros.
+__device__ __forceinline__ float inv_scale(float s) {
+    if (s == 0.f) return 0.f;
+    const float inv = __fdiv_rn(1.0f, s);
+    return isinf(inv) ? 0.f : inv;
+}
 
 // sign-extended byte i (0..3) of a packed word, added into acc: dp4a with a one-hot selector.
 template <int I>

@@ -1,0 +1,137 @@
+"""1-D row-partitioned full-graph training over the GPUs of one node (one process per GPU, torch.distributed).
+
+The reference is single-GPU only.  Here rank r owns a contiguous block of nodes: their feature rows, the CSC rows of
+the adjacency (forward aggregation) and the CSR rows (backward aggregation), both with global column ids.  The only
+data-path exchange is one all-gather per aggregation of the int8-quantized feature shard plus its fp32 scale; the
+aggregation kernel then applies the scale of the shard each neighbour came from.  Weight gradients are summed with
+an all-reduce after the backward pass.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.autograd.function import Function, once_differentiable
+
+from . import config
+from .graph import Graph, RowPartition
+
+
+def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_rows: int, group=None):
+    """Gathers every rank's int8 shard ([<= shard_rows, ld], same ld everywhere) and scale.
+
+    Returns (q_all [world * shard_rows, ld], scales [world]); rank k's rows start at k * shard_rows.  Works on any
+    backend (NCCL on GPUs, gloo on CPU)."""
+    world = dist.get_world_size(group)
+    ld = q_local.shape[1]
+    q_all = torch.empty((world * shard_rows, ld), dtype=torch.int8, device=q_local.device)
+    if q_local.shape[0] == shard_rows and q_local.is_contiguous():
+        send = q_local
+    else:
+        send = torch.zeros((shard_rows, ld), dtype=torch.int8, device=q_local.device)
+        send[:q_local.shape[0]] = q_local
+    dist.all_gather_into_tensor(q_all, send, group=group)
+    scales = torch.empty(world, dtype=torch.float32, device=s_local.device)
+    dist.all_gather_into_tensor(scales, s_local.reshape(1).contiguous(), group=group)
+    return q_all, scales
+
+
+class DistGraph:
+    """Rank-local view of a graph that every rank holds (or can rebuild from the same seed)."""
+
+    def __init__(self, g: Graph, rank: int, world: int):
+        n = g.num_nodes()
+        self.rank, self.world, self.n_total = rank, world, n
+        csc, csr = g.adj_csc, g.adj_csr
+        self.fwd = RowPartition(csc[0], csc[1], None, n, rank, world)
+        self.bwd = RowPartition(csr[0], csr[1], None, n, rank, world)
+        self.shard_rows, self.r0, self.r1, self.n_local = self.fwd.shard_rows, self.fwd.r0, self.fwd.r1, self.fwd.n_local
+        self.in_norm = g.in_degrees()[self.r0:self.r1].float().clamp(min=1).pow(-0.5).contiguous()
+        self.out_norm = g.out_degrees()[self.r0:self.r1].float().clamp(min=1).pow(-0.5).contiguous()
+
+
+def _padded_storage(q: torch.Tensor) -> torch.Tensor:
+    """The [rows, ld] storage behind an int8 tensor returned by kernels.quantize."""
+    ld = q.stride(0)
+    return torch.as_strided(q, (q.shape[0], ld), (ld, 1))
+
+
+class dist_spmm_copy_u(Function):
+    """spmm_copy_u over a row partition: quantize the local shard, all-gather int8 shards + scales, aggregate the
+    local rows.  Backward does the same on the transposed partition."""
+
+    @staticmethod
+    def forward(ctx, dg: DistGraph, x_local, scale_local=None):
+        ctx.dg = dg
+        return _aggregate(dg, dg.fwd, x_local, scale_local)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dz):
+        dg = ctx.dg
+        dn = _aggregate(dg, dg.bwd, dz.contiguous(), None) if ctx.needs_input_grad[1] else None
+        return None, dn, None
+
+
+def _aggregate(dg: DistGraph, part: RowPartition, x_local: torch.Tensor, scale_local: Optional[torch.Tensor]):
+    from . import kernels as K
+    q, s = K.quantize(x_local, scale_local, mode=config.mode_for("quantize"), seed=config.seed())
+    q_all, scales = all_gather_quantized(_padded_storage(q), s, dg.shard_rows)
+    f = x_local.shape[1]
+    out = torch.empty((dg.n_local, f), dtype=torch.float32, device=x_local.device)
+    K._csr_spmm(out, part.indptr, part.indices, q_all[:, :f] if q_all.shape[1] != f else q_all, scales,
+                part.schedule, dg.world)
+    return out
+
+
+class DistQGraphConv(nn.Module):
+    """QGraphConv (norm='both') on a row partition."""
+
+    def __init__(self, in_feats, out_feats, activation=None):
+        super().__init__()
+        self._in_feats, self._out_feats, self._activation = in_feats, out_feats, activation
+        self.weight = nn.Parameter(torch.empty(out_feats, in_feats))
+        self.bias = nn.Parameter(torch.zeros(out_feats))
+        nn.init.xavier_uniform_(self.weight)
+
+    def forward(self, dg: DistGraph, feat_local):
+        from .QLinear import Qlinear_func, Qlinear_func_reduce
+        h = feat_local * dg.out_norm.unsqueeze(1)
+        if self._in_feats > self._out_feats:
+            h, s = Qlinear_func_reduce.apply(h, self.weight)
+            rst = dist_spmm_copy_u.apply(dg, h, s)
+        else:
+            rst = Qlinear_func.apply(dist_spmm_copy_u.apply(dg, h), self.weight)
+        rst = rst * dg.in_norm.unsqueeze(1) + self.bias
+        return self._activation(rst) if self._activation is not None else rst
+
+
+class DistGCN(nn.Module):
+    def __init__(self, dg: DistGraph, in_feats, n_hidden, n_classes, n_layers=1, activation=F.relu):
+        super().__init__()
+        self.dg = dg
+        dims = [in_feats] + [n_hidden] * n_layers + [n_classes]
+        self.layers = nn.ModuleList(
+            DistQGraphConv(dims[i], dims[i + 1], activation if i < len(dims) - 2 else None) for i in range(len(dims) - 1))
+
+    def forward(self, feat_local):
+        h = feat_local
+        for layer in self.layers:
+            h = layer(self.dg, h)
+        return h
+
+
+def allreduce_grads(module: nn.Module, group=None) -> None:
+    """Sums the parameter gradients over the ranks (each rank holds the contribution of its rows)."""
+    grads = [p.grad for p in module.parameters() if p.grad is not None]
+    if not grads:
+        return
+    flat = torch.cat([g.reshape(-1) for g in grads])
+    dist.all_reduce(flat, group=group)
+    off = 0
+    for g in grads:
+        g.copy_(flat[off:off + g.numel()].view_as(g))
+        off += g.numel()

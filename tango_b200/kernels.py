@@ -107,6 +107,7 @@ def _status_word(device) -> torch.Tensor:
     return t
 
 
+launch_counter = [0]  # kernels of this library launched so far (benchmarks report it per step)
 _call_counter = [0]
 
 
@@ -146,6 +147,7 @@ def _get_scale(t: torch.Tensor, row_scale: Optional[torch.Tensor] = None) -> tor
     scale = torch.empty(1, dtype=torch.float32, device=t.device)
     with torch.cuda.device(t.device):
         check(lib.tango_absmax_scale(_p(t), rows, cols, ld, _p(row_scale), _p(scale), _stream()), "get_scale")
+    launch_counter[0] += 1
     return scale
 
 
@@ -159,6 +161,7 @@ def _quantize_into(out: torch.Tensor, t: torch.Tensor, scale: torch.Tensor, mode
     with torch.cuda.device(t.device):
         check(lib.tango_quantize(_p(t), rows, cols, ldx, _p(row_scale), _p(scale), _p(out), ldq, mode, seed, call,
                                  _stream()), "quantize")
+    launch_counter[0] += 1
 
 
 def _transpose_quant(data: torch.Tensor, scale: torch.Tensor, nrow: int, ncol: int) -> torch.Tensor:
@@ -166,6 +169,7 @@ def _transpose_quant(data: torch.Tensor, scale: torch.Tensor, nrow: int, ncol: i
     out = torch.empty((ncol, nrow), dtype=torch.int8, device=data.device)
     with torch.cuda.device(data.device):
         check(lib.tango_quantize_transpose(_p(data), nrow, ncol, _p(scale), _p(out), _stream()), "transpose_quant")
+    launch_counter[0] += 1
     return out
 
 
@@ -181,6 +185,7 @@ def _qgemm_forward(Y, X, X_q, W, W_q, bias, scaleY, scaleX, scaleW, mode=ROUND_T
         check(lib.tango_qgemm_forward(_p(X), ldx, _p(W), ldw, m, n, k, _p(scaleX), _p(scaleW), _p(X_q), ldxq, _p(W_q),
                                       ldwq, _p(bias), _p(Y), ldy, _p(scaleY), mode, seed, call, _p(st), _stream()),
               "QGEMM_forward")
+    launch_counter[0] += 3
 
 
 def _qgemm_nt(Y, X_q, W_q, scaleX, scaleW, bias=None, scaleY=None):
@@ -191,6 +196,7 @@ def _qgemm_nt(Y, X_q, W_q, scaleX, scaleW, bias=None, scaleY=None):
     with torch.cuda.device(X_q.device):
         check(lib.tango_qgemm_nt(_p(X_q), ldx, _p(W_q), ldw, m, n, k, _p(scaleX), _p(scaleW), _p(bias), _p(Y), ldy,
                                  _p(scaleY), _p(st), _stream()), "qgemm_nt")
+    launch_counter[0] += 1
 
 
 def _qgemm_gradX(dX, dY_q, W_q, scaledY, scaleW):
@@ -202,6 +208,7 @@ def _qgemm_gradX(dX, dY_q, W_q, scaledY, scaleW):
     with torch.cuda.device(dX.device):
         check(lib.tango_qgemm_dx(_p(dY_q), lddy, _p(W_q), ldw, m, n, k, _p(scaledY), _p(scaleW), _p(dX), lddx, _p(st),
                                  _stream()), "QGEMM_backward_gradX")
+    launch_counter[0] += 1
 
 
 def _qgemm_gradW(dW, dY_q, X_q, scaledY, scaleX):
@@ -215,6 +222,7 @@ def _qgemm_gradW(dW, dY_q, X_q, scaledY, scaleX):
     with torch.cuda.device(dW.device):
         check(lib.tango_qgemm_dw(_p(dY_q), lddy, _p(X_q), ldx, m, n, k, _p(scaledY), _p(scaleX), _p(dW), lddw, _p(ws),
                                  nbytes, _p(st), _stream()), "QGEMM_backward_gradW")
+    launch_counter[0] += 2
 
 
 def _make_plan(sched: Optional[SpmmSchedule], f: int, device):
@@ -237,6 +245,7 @@ def _csr_spmm(out, indptr, indices, U, scaleU, sched=None, nseg=1, row_scale=Non
     with torch.cuda.device(U.device):
         check(lib.tango_spmm_copy_u(_p(indptr), _pi(indices), n_rows, nseg, _p(U), ldn, f, _p(scaleU), _p(row_scale),
                                     _p(bias), int(relu), _p(out), ldo, _p(out_absmax), plan, _stream()), "csr_SPMM")
+    launch_counter[0] += 1 + (plan is not None)
     del keep
 
 
@@ -245,13 +254,14 @@ def _u_mul_e_spmm(indptr, indices, edge_ids, N, E, scale, sched=None):
     assert N.dim() == 3
     nn, h, d = N.shape
     N, _, f, ldn = _matrix(N)
-    E = E.contiguous()
+    E = E.contiguous() if E.numel() else torch.zeros(1, dtype=torch.int8, device=N.device)
     n_rows = indptr.numel() - 1
     out = torch.empty((n_rows, h, d), dtype=torch.float32, device=N.device)
     plan, keep = _make_plan(sched, f, N.device)
     with torch.cuda.device(N.device):
         check(lib.tango_spmm_u_mul_e(_p(indptr), _pi(indices), _p(edge_ids), n_rows, _p(N), ldn, h, d, _p(E), _p(scale),
                                      _p(out), f, plan, _stream()), "multi_cusparse_SPMM")
+    launch_counter[0] += 1 + (plan is not None)
     del keep
     return out
 
@@ -264,11 +274,13 @@ def _incidence_spmm(out, indptr, edge_ids, E, scale, sched=None):
     with torch.cuda.device(E.device):
         check(lib.tango_spmm_incidence(_p(indptr), _p(edge_ids), n_rows, _p(E), ldz, f, _p(scale), _p(out), ldo, plan,
                                        _stream()), "incidence_SPMM")
+    launch_counter[0] += 1 + (plan is not None)
     del keep
 
 
 def _sddmm(op: str, out, scaleOut, src, dst, U, V, scaleU, scaleV):
     n_edges = src.numel()
+    launch_counter[0] += 1
     with torch.cuda.device(U.device):
         if op == "dot":
             h, d = U.shape[-2], U.shape[-1]
@@ -475,4 +487,5 @@ def gat_edge_softmax(g, elq, erq, sl, sr, slope: float = 0.2):
     with torch.cuda.device(elq.device):
         check(lib.tango_gat_edge_softmax(_p(indptr), _p(indices), _p(edge_ids), g.num_nodes(), _p(elq), _p(erq), h,
                                          _p(sl), _p(sr), float(slope), _p(a), _stream()), "gat_edge_softmax")
+    launch_counter[0] += 1
     return a

@@ -1,0 +1,54 @@
+"""The C-ABI library loads without a GPU and exports every symbol that include/tango_b200.h declares; argument
+validation that happens before any CUDA call returns the documented error codes."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "tango_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tango_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    from tango_b200 import _lib
+    names = _declared()
+    assert len(names) >= 17
+    for name in names:
+        assert hasattr(_lib.lib, name), f"{name} declared in tango_b200.h but not exported"
+    assert set(_lib.EXPORTED) == set(names), "ctypes signature table out of sync with the header"
+
+
+def test_version_and_strerror():
+    from tango_b200 import _lib
+    assert _lib.lib.tango_version() >= 100
+    assert _lib.lib.tango_strerror(0) == b"ok"
+    assert b"invalid" in _lib.lib.tango_strerror(-1)
+    assert b"unknown" in _lib.lib.tango_strerror(-99)
+
+
+def test_argument_validation_without_gpu():
+    from tango_b200 import _lib
+    L = _lib.lib
+    assert L.tango_quantize(None, -1, 4, 4, None, None, None, 4, 1, 0, 0, None) == -1          # negative rows
+    assert L.tango_quantize(None, 4, 4, 4, None, None, None, 4, 7, 0, 0, None) == -1           # bad mode
+    assert L.tango_quantize(None, 4, 8, 4, None, None, None, 8, 1, 0, 0, None) == -1           # ld < cols
+    assert L.tango_sddmm_elementwise(9, None, None, 1, None, 4, None, 4, 4, None, None, None, None, None) == -1
+    assert L.tango_spmm_copy_u(None, None, 4, 0, None, 16, 16, None, None, None, 0, None, 16, None, None, None) == -1
+    assert L.tango_qgemm_nt(None, 16, None, 16, 8, 8, 0, None, None, None, None, 8, None, None, None) == -1
+    assert L.tango_qgemm_dw_workspace_bytes(256, 602) == 256 * 604 * 4
+    # empty problems succeed without touching the device
+    assert L.tango_sddmm_dot(None, None, 0, None, 16, None, 16, 1, 16, None, None, None, None, None) == 0
+    assert L.tango_spmm_incidence(None, None, 0, None, 4, 4, None, None, 4, None, None) == 0
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "tango_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in src, f"{f} mentions the oracle"

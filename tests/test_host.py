@@ -1,0 +1,166 @@
+"""Host-side logic that needs no GPU: graph generator and index bundles, long-row schedules, row partitions, shape
+helpers, rounding-mode switch, and the 2-rank all-gather path over gloo."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import tango_oracle as O
+from tango_b200 import config
+from tango_b200.graph import Graph, RowPartition, SpmmSchedule, add_self_loop, rmat_edges, rmat_graph
+from tango_b200.kernels import alloc_int8, infer_broadcast_shape
+
+
+def test_rmat_is_seeded_distinct_and_loop_free():
+    s1, d1 = rmat_edges(1000, 8000, 5)
+    s2, d2 = rmat_edges(1000, 8000, 5)
+    s3, _ = rmat_edges(1000, 8000, 6)
+    assert torch.equal(s1, s2) and torch.equal(d1, d2) and not torch.equal(s1, s3)
+    assert s1.numel() == 8000 and int((s1 == d1).sum()) == 0
+    key = s1.long() * 1000 + d1.long()
+    assert key.unique().numel() == 8000 and int(s1.max()) < 1000 and int(d1.max()) < 1000
+    deg = torch.bincount(s1.long(), minlength=1000)
+    assert deg.max() > 8 * deg.float().mean()            # power-law skew
+
+
+def test_graph_index_bundles():
+    g = rmat_graph(500, 4000, 3)
+    src, dst = g.coo
+    assert g.num_edges() == 4500 and int(g.in_degrees().min()) >= 1      # one self loop per node
+    for fmt, rows, cols in (("csr", src, dst), ("csc", dst, src)):
+        indptr, indices, eids = g.adj_sparse(fmt)
+        assert indptr.dtype == torch.int32 and int(indptr[-1]) == 4500
+        assert torch.equal(cols[eids.long()], indices)
+        r = torch.repeat_interleave(torch.arange(500), (indptr[1:] - indptr[:-1]).long())
+        assert torch.equal(rows[eids.long()].long(), r)
+        for v in (0, 7, 499):                                            # columns sorted inside a row
+            seg = indices[indptr[v]:indptr[v + 1]]
+            assert torch.equal(seg, seg.sort()[0])
+    inc = g.inc_in
+    assert inc.shape == (2, 4500) and torch.equal(dst[inc[1].long()], inc[0])
+    assert torch.equal(src[g.inc_out[1].long()], g.inc_out[0])
+
+
+def test_add_self_loop_replaces_existing_loops():
+    s = torch.tensor([0, 1, 2, 2], dtype=torch.int32)
+    d = torch.tensor([0, 2, 2, 1], dtype=torch.int32)
+    s2, d2 = add_self_loop(s, d, 3)
+    assert s2.tolist() == [1, 2, 0, 1, 2] and d2.tolist() == [2, 1, 0, 1, 2]
+
+
+@pytest.mark.parametrize("nseg", [1, 3])
+def test_schedule_covers_long_rows_exactly_once(nseg):
+    g = rmat_graph(2000, 60000, 9)
+    indptr, indices, _ = g.adj_csc
+    if nseg > 1:
+        part = RowPartition(indptr, indices, None, 2000, 0, nseg)
+        indptr = part.indptr
+    s = SpmmSchedule(indptr, nseg=nseg, threshold=100, unit=64)
+    ip = indptr.long()
+    n_rows = (ip.numel() - 1) // nseg
+    deg = ip[nseg::nseg] - ip[:-1:nseg]
+    assert s.n_heavy == int((deg > 100).sum()) and s.n_heavy > 0
+    cov = torch.zeros(int(ip[-1]), dtype=torch.int32)
+    for vrow, b, e, slot in s.units.tolist():
+        assert 0 < e - b <= 64 and ip[vrow] <= b and e <= ip[vrow + 1]
+        assert s.heavy_rows[slot // nseg] == vrow // nseg and slot % nseg == vrow % nseg
+        cov[b:e] += 1
+    assert int(cov.max()) == 1 and int(cov.sum()) == int(deg[s.heavy_rows.long()].sum())
+    assert n_rows * nseg + 1 == ip.numel()
+
+
+def test_row_partition_segments():
+    g = rmat_graph(1003, 20000, 4)
+    indptr, indices, _ = g.adj_csc
+    world = 4
+    seen = 0
+    for r in range(world):
+        p = RowPartition(indptr, indices, None, 1003, r, world)
+        assert p.shard_rows == 251 and p.indptr.numel() == p.n_local * world + 1
+        ip = p.indptr.long()
+        for v in (0, p.n_local // 2, p.n_local - 1):
+            for k in range(world):
+                seg = p.indices[ip[v * world + k]:ip[v * world + k + 1]]
+                assert bool(((seg // p.shard_rows) == k).all())
+        seen += p.indices.numel()
+    assert seen == g.num_edges()
+
+
+def test_alloc_int8_padding_and_broadcast_shapes():
+    t = alloc_int8((10, 41), "cpu")
+    assert t.shape == (10, 41) and t.stride() == (48, 1)
+    t = alloc_int8((10, 4, 64), "cpu")
+    assert t.is_contiguous()
+    t = alloc_int8((10, 2, 24), "cpu")
+    assert t.shape == (10, 2, 24) and t.stride() == (48, 24, 1)
+    assert alloc_int8((7, 4), "cpu", align=1).is_contiguous()
+    assert infer_broadcast_shape("dot", (4, 64), (4, 64)) == (4, 1)
+    assert infer_broadcast_shape("add", (4, 1), (4, 1)) == (4, 1)
+    assert infer_broadcast_shape("mul", (4, 16), (1, 16)) == (4, 16)
+    with pytest.raises(ValueError):
+        infer_broadcast_shape("add", (4, 3), (4, 5))
+
+
+def test_rounding_switch():
+    from tango_b200._lib import ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_TRUNC
+    config.set_rounding("reference")
+    assert config.mode_for("gemm_fwd") == ROUND_TRUNC and config.mode_for("quantize") == ROUND_NEAREST
+    config.set_rounding("stochastic", seed=9)
+    assert config.mode_for("gemm_fwd") == ROUND_STOCHASTIC and config.seed() == 9
+    config.set_rounding("reference")
+    with pytest.raises(ValueError):
+        config.set_rounding("bogus")
+
+
+# ------------------------------------------------------------------------------------------- 2 ranks over gloo
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from tango_b200.dist import all_gather_quantized
+    n, f = 301, 24                                       # ragged: the last shard is shorter
+    g = rmat_graph(n, 5000, 21)
+    indptr, indices, _ = g.adj_csc
+    part = RowPartition(indptr, indices, None, n, rank, world)
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((n, f)).astype(np.float32) * (1 + np.arange(n)[:, None] / 100)
+    x_loc = x[part.r0:part.r1]
+    s_loc = O.absmax_scale(x_loc)
+    q_loc = torch.zeros((part.n_local, 32), dtype=torch.int8)          # padded rows, as the quantizer writes them
+    q_loc[:, :f] = torch.from_numpy(O.quantize(x_loc, s_loc))
+    q_all, scales = all_gather_quantized(q_loc, torch.tensor([s_loc]), part.shard_rows)
+    assert q_all.shape == (world * part.shard_rows, 32)
+    out = O.spmm_copy_u(part.indptr.numpy().astype(np.int64)[::world], part.indices.numpy().astype(np.int64),
+                        q_all[:, :f].numpy(), scales.numpy(), shard_rows=part.shard_rows)
+    np.save(os.path.join(out_dir, f"out{rank}.npy"), out)
+    np.save(os.path.join(out_dir, f"scales{rank}.npy"), scales.numpy())
+    dist.destroy_process_group()
+
+
+def test_two_rank_gather_and_aggregate(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    n, f = 301, 24
+    g = rmat_graph(n, 5000, 21)
+    indptr, indices, _ = [t.numpy().astype(np.int64) for t in g.adj_csc]
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((n, f)).astype(np.float32) * (1 + np.arange(n)[:, None] / 100)
+    shard = (n + world - 1) // world
+    scales = np.array([O.absmax_scale(x[k * shard:(k + 1) * shard]) for k in range(world)], dtype=np.float32)
+    q = np.concatenate([O.quantize(x[k * shard:(k + 1) * shard], scales[k]) for k in range(world)])
+    ref = O.spmm_copy_u(indptr, indices, q, scales, shard_rows=shard)
+    got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
+    np.testing.assert_array_equal(np.load(tmp_path / "scales0.npy"), scales)
+    np.testing.assert_array_equal(got, ref)
+    # and the per-shard-scale result stays within the stated tolerance of the fp32 aggregation
+    a = np.zeros((n, f)); rows = np.repeat(np.arange(n), np.diff(indptr)); np.add.at(a, rows, x[indices])
+    assert np.abs(got - a).max() / np.abs(a).max() < 1e-2
