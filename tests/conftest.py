@@ -11,7 +11,11 @@ if ROOT not in sys.path:
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA device (run with -m gpu on a B200)")
     # make sure the prebuilt library exists before any test imports the package (nvcc cross-compiles without a GPU)
-    from tango_b200 import build
+    # the build script is loaded by path: importing the package itself needs an up-to-date library
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_tango_build", os.path.join(ROOT, "tango_b200", "build.py"))
+    build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(build)
     build.build()
 
 
