@@ -109,6 +109,26 @@ int tango_qgemm_dw(const int8_t *dyq, int64_t lddy, const int8_t *xq, int64_t ld
                    const float *sdy, const float *sx, float *dw, int64_t lddw, void *workspace,
                    int64_t workspace_bytes, int *status, tango_stream_t stream);
 
+/* Weight gradient for callers that have no device memory to lend and must not allocate any: same result as
+ * tango_qgemm_dw, but the split-K scratch is a fixed 4 MiB array that lives inside the library image, so no
+ * workspace argument exists and no cudaMalloc / cudaFree (nor any allocating library routine) is called.  This has
+ * no counterpart in the reference.  It is meant for hosts where allocation is off the table at call time: a
+ * runtime that has handed all device memory to its own pool and gives plug-ins no allocator handle, or a
+ * latency-sensitive loop that cannot tolerate the implicit device-wide synchronisation of cudaMalloc/cudaFree.
+ * Limits and rules:
+ *   - n * round_up(k, 4) must not exceed tango_qgemm_dw_noalloc_max_elems() (1,048,576 int32); larger problems
+ *     return TANGO_ESIZE and must use tango_qgemm_dw with caller memory;
+ *   - every GPU that loads the library holds the 4 MiB until the process exits;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device, under a
+ *     mutex); make that first call before starting any stream capture;
+ *   - all calls on a device share the one array: it still holds the previous call's partial sums, each call clears
+ *     the part it uses first, and two calls that overlap on the GPU (different streams) race -- serialise them. */
+int tango_qgemm_dw_noalloc(const int8_t *dyq, int64_t lddy, const int8_t *xq, int64_t ldx, int64_t m, int64_t n,
+                           int64_t k, const float *sdy, const float *sx, float *dw, int64_t lddw, int *status,
+                           tango_stream_t stream);
+/* Capacity of the built-in scratch of tango_qgemm_dw_noalloc in int32 elements. */
+int64_t tango_qgemm_dw_noalloc_max_elems(void);
+
 /* ---------------------------------------------------------------- SpMM (CSR, int8 features, int32 accumulation) */
 
 /* Optional schedule for rows too long for one warp.  A row whose degree exceeds `split_threshold` is cut into

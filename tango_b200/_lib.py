@@ -1,6 +1,6 @@
 """ctypes binding of libtango_b200.so (the C ABI declared in include/tango_b200.h).
 
-The library is prebuilt in-tree (python -m tango_b200.build); there is no fallback implementation: if the shared
+The library is prebuilt in-tree (python tango_b200/build.py); there is no fallback implementation: if the shared
 object is missing, importing this module raises.
 """
 from __future__ import annotations
@@ -32,7 +32,7 @@ class SpmmPlan(Structure):
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build the CUDA library first with `python -m tango_b200.build` "
+        f"{LIB_PATH} is missing: build the CUDA library first with `python tango_b200/build.py` "
         "(there is no CPU or PyTorch fallback for these operators)")
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -51,6 +51,8 @@ _SIGS = {
                              c_int64, P, c_int, c_uint64, c_uint64, P, P], c_int),
     "tango_qgemm_dx": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, P], c_int),
     "tango_qgemm_dw": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, c_int64, P, P], c_int),
+    "tango_qgemm_dw_noalloc": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, P], c_int),
+    "tango_qgemm_dw_noalloc_max_elems": ([], c_int64),
     "tango_spmm_copy_u": ([P, P, c_int64, c_int, P, c_int64, c_int64, P, P, P, c_int, P, c_int64, P,
                            POINTER(SpmmPlan), P], c_int),
     "tango_spmm_u_mul_e": ([P, P, P, c_int64, P, c_int64, c_int, c_int, P, P, P, c_int64, POINTER(SpmmPlan), P], c_int),
@@ -60,6 +62,8 @@ _SIGS = {
     "tango_gat_edge_softmax": ([P, P, P, c_int64, P, P, c_int, P, P, c_float, P, P], c_int),
 }
 for _name, (_args, _res) in _SIGS.items():
+    if not hasattr(lib, _name):
+        raise ImportError(f"{LIB_PATH} is stale (no symbol {_name}): rebuild it with `python tango_b200/build.py`")
     _fn = getattr(lib, _name)
     _fn.argtypes = _args
     _fn.restype = _res

@@ -15,6 +15,8 @@
 // memory and returns.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace tango {
@@ -461,4 +463,49 @@ extern "C" int tango_qgemm_dw(const int8_t *dyq, int64_t lddy, const int8_t *xq,
     dequant_ws_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const int32_t *)workspace, ldws, n, k, sdy, sx, dw, lddw);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ no-allocation dW
+// Scratch for tango_qgemm_dw_noalloc: a fixed array inside the library image instead of caller-provided memory.
+// Every GPU that loads the library keeps these 4 MiB until the process exits.
+namespace tango {
+constexpr int64_t kStaticDwScratchElems = 1 << 20;  // int32 elements: n * round_up(k, 4) must not exceed this
+static __device__ __align__(256) int32_t g_dw_scratch[kStaticDwScratchElems];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_dw_scratch_mutex;
+static void *g_dw_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_dw_scratch on the current device.  In host code the array's name is only a handle, so the
+// address is looked up once per device (with that device current) and cached.
+static int dw_scratch_address(void **out) {
+    int dev = -1;
+    TANGO_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return TANGO_ESIZE;
+    std::lock_guard<std::mutex> lock(g_dw_scratch_mutex);
+    if (!g_dw_scratch_ptr[dev]) {
+        void *p = nullptr;
+        TANGO_CUDA_TRY(cudaGetSymbolAddress(&p, g_dw_scratch));
+        if (!p) return TANGO_ECUDA;
+        g_dw_scratch_ptr[dev] = p;
+    }
+    *out = g_dw_scratch_ptr[dev];
+    return TANGO_OK;
+}
+}  // namespace tango
+
+extern "C" int64_t tango_qgemm_dw_noalloc_max_elems(void) { return tango::kStaticDwScratchElems; }
+
+extern "C" int tango_qgemm_dw_noalloc(const int8_t *dyq, int64_t lddy, const int8_t *xq, int64_t ldx, int64_t m,
+                                      int64_t n, int64_t k, const float *sdy, const float *sx, float *dw,
+                                      int64_t lddw, int *status, tango_stream_t stream) {
+    if (n < 0 || k < 0) return TANGO_EINVAL;
+    const int64_t need = tango_qgemm_dw_workspace_bytes(n, k);
+    if (need > tango::kStaticDwScratchElems * (int64_t)sizeof(int32_t)) return TANGO_ESIZE;
+    void *scratch = nullptr;
+    const int rc = tango::dw_scratch_address(&scratch);
+    if (rc) return rc;
+    // The regular entry point clears the part of the scratch it uses before accumulating into it.
+    return tango_qgemm_dw(dyq, lddy, xq, ldx, m, n, k, sdy, sx, dw, lddw, scratch,
+                          tango::kStaticDwScratchElems * (int64_t)sizeof(int32_t), status, stream);
 }
