@@ -334,6 +334,41 @@ def _cpu_baseline(name, g, model):
             "sample": "one full epoch (all nodes and edges) after one warm-up epoch; fp32 torch CPU formulation"}
 
 
+def run_case(args):
+    """Small single-kernel cases for profiler captures (a few launches, well under 1 GB on the device)."""
+    import torch
+    import tango_b200 as T
+    from tango_b200 import kernels as K
+    from tango_b200.graph import rmat_graph
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    if args.case.startswith("spmm"):
+        f = int(args.case.split("_f")[1])
+        n, e = 232_965, 20_000_000
+        g = rmat_graph(n, e, 7, device=dev)
+        T.graph_preprocess(g)
+        q, s = K.quantize(torch.randn((n, f), device=dev))
+        for _ in range(3):
+            out = K.csr_SPMM(g, q, s)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "nodes": n, "edges": g.num_edges(), "f": f,
+                          "checksum": float(out.double().sum())}))
+    elif args.case == "gemm":
+        m, k, n = 65_536, 602, 256
+        x, w, dy = torch.randn((m, k), device=dev), torch.randn((n, k), device=dev) * 0.04, torch.randn((m, n), device=dev)
+        sx, sw = K.cuda_kernels.get_scale(x), K.cuda_kernels.get_scale(w)
+        xq, wq = K.alloc_int8(x.shape, dev), K.alloc_int8(w.shape, dev)
+        for _ in range(3):
+            y = K.QGEMM_forward(x, xq, sx, w, wq, sw)
+            dyq, sdy = K.quantize(dy)
+            dx, dw = K.QGEMM_backward(dyq, xq, wq, sdy, sx, sw)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "m": m, "k": k, "n": n, "status": K.device_status(),
+                          "checksum": float(y.double().sum() + dx.double().sum() + dw.double().sum())}))
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -343,8 +378,11 @@ def main():
     ap.add_argument("--workload", default="gcn_c5", choices=sorted(WORKLOADS))
     ap.add_argument("--rounding", default="reference", choices=["reference", "nearest", "stochastic"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, gemm) and exit")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
