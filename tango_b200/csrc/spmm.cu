@@ -61,9 +61,10 @@ template <> struct VecLoad<1> {
     __device__ __forceinline__ void zero() { w[0] = 0; }
 };
 
+// Adds one byte of one neighbour (VEC == 1) or, for the per-element weight mode, VEC bytes with their own weights.
 template <int VEC, int MODE>
-__device__ __forceinline__ void accumulate(int (&acc)[VEC], const VecLoad<VEC> &v, uint32_t wsel,
-                                           const int8_t *wrow, int off, const SpmmArgs &a) {
+__device__ __forceinline__ void accumulate_one(int (&acc)[VEC], const VecLoad<VEC> &v, uint32_t wsel,
+                                               const int8_t *wrow, int off, const SpmmArgs &a) {
     if (VEC == 1) {
         const int b = (int)(int8_t)(v.w[0] & 0xff);
         if (MODE == MODE_COPY) acc[0] += b;
@@ -73,30 +74,83 @@ __device__ __forceinline__ void accumulate(int (&acc)[VEC], const VecLoad<VEC> &
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
         const uint32_t word = v.w[i >> 2];
-        if (MODE == MODE_COPY) {
-            acc[i] = __dp4a((int)word, (int)(1u << (8 * (i & 3))), acc[i]);
-        } else if (MODE == MODE_WEIGHT_LANE) {
-            acc[i] = __dp4a((int)word, (int)(wsel << (8 * (i & 3))), acc[i]);
-        } else {
-            const int col = off + i;
-            const int wv = (wrow && col < a.f) ? (int)__ldg(wrow + col / a.D) : 0;
-            acc[i] += (int)(int8_t)((word >> (8 * (i & 3))) & 0xff) * wv;
-        }
+        const int col = off + i;
+        const int wv = (wrow && col < a.f) ? (int)__ldg(wrow + col / a.D) : 0;
+        acc[i] += (int)(int8_t)((word >> (8 * (i & 3))) & 0xff) * wv;
+    }
+}
+
+// Adds four neighbours at once.  The same word of the four rows is byte-transposed with 8 PRMTs so that each result
+// word holds one feature of the four neighbours; one 4-way dp4a against (1,1,1,1) -- or against the four neighbours'
+// int8 weights -- then adds all four into the int32 accumulator: 12 instructions per 16 gathered bytes.
+template <int VEC>
+__device__ __forceinline__ void accumulate_four(int (&acc)[VEC], const VecLoad<VEC> (&v)[4], uint32_t wvec) {
+#pragma unroll
+    for (int wp = 0; wp < VEC / 4; ++wp) {
+        const uint32_t a = v[0].w[wp], b = v[1].w[wp], c = v[2].w[wp], d = v[3].w[wp];
+        const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
+        const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);
+        acc[4 * wp + 0] = __dp4a((int)__byte_perm(t0, t1, 0x5410), (int)wvec, acc[4 * wp + 0]);
+        acc[4 * wp + 1] = __dp4a((int)__byte_perm(t0, t1, 0x7632), (int)wvec, acc[4 * wp + 1]);
+        acc[4 * wp + 2] = __dp4a((int)__byte_perm(t2, t3, 0x5410), (int)wvec, acc[4 * wp + 2]);
+        acc[4 * wp + 3] = __dp4a((int)__byte_perm(t2, t3, 0x7632), (int)wvec, acc[4 * wp + 3]);
     }
 }
 
 // Sums the neighbours of slots [beg, end) into acc for the feature bytes [off, off + VEC) handled by this lane.
-// On return every lane of group 0 (lane < G) holds the full sum for its bytes.
+// On return every lane of group 0 (lane < G) holds the full sum for its bytes.  Lanes whose bytes lie beyond the
+// feature width run the same instruction stream on the row's first bytes (their sums are never stored), so the hot
+// loop over full batches of 32 neighbours carries no predicates at all.
 template <int VEC, int MODE>
 __device__ __forceinline__ void gather_segment(int (&acc)[VEC], int beg, int end, int off, bool active,
                                                const SpmmArgs &a) {
     const int lane = threadIdx.x & 31;
     const int G = a.G, NB = 32 / G, grp = lane / G;
     constexpr int U = 4;
+    constexpr bool kFour = (VEC >= 4) && (MODE != MODE_WEIGHT_ELEM);
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = 0;
-    const int head = (MODE == MODE_WEIGHT_LANE) ? off / a.D : 0;
-    for (int j0 = beg; j0 < end; j0 += 32) {
+    const int ld_off = active ? off : 0;
+    const int head = (MODE == MODE_WEIGHT_LANE) ? ld_off / a.D : 0;
+    const int8_t *base = a.feat + ld_off;
+    const int8_t *wbase = (MODE == MODE_WEIGHT_LANE) ? a.ew + head : a.ew;
+    const int64_t ld = a.ld;
+    const int H = a.H;
+    int j0 = beg;
+    if (kFour && G >= U) {
+        // ---- full batches: every shuffled index is valid, four loads in flight per lane, no predicates.
+        // The indices of the next batch are fetched while the current one is processed.
+        int nxt_idx = 0, nxt_eid = 0;
+        if (j0 + 32 <= end) {
+            nxt_idx = a.indices ? __ldg(a.indices + j0 + lane) : j0 + lane;
+            if (MODE != MODE_COPY) nxt_eid = a.edge_ids ? __ldg(a.edge_ids + j0 + lane) : j0 + lane;
+        }
+        for (; j0 + 32 <= end; j0 += 32) {
+            const int my_idx = nxt_idx, my_eid = nxt_eid;
+            if (j0 + 64 <= end) {
+                nxt_idx = a.indices ? __ldg(a.indices + j0 + 32 + lane) : j0 + 32 + lane;
+                if (MODE != MODE_COPY) nxt_eid = a.edge_ids ? __ldg(a.edge_ids + j0 + 32 + lane) : j0 + 32 + lane;
+            }
+            for (int s = 0; s < G; s += U) {
+                VecLoad<VEC> v[U];
+                uint32_t wvec = 0x01010101u;
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int src_lane = (s + u) * NB + grp;
+                    const int idx = __shfl_sync(0xffffffffu, my_idx, src_lane);
+                    v[u].load(base + (int64_t)idx * ld);
+                    if (MODE == MODE_WEIGHT_LANE) {
+                        const int eid = __shfl_sync(0xffffffffu, my_eid, src_lane);
+                        const uint32_t wb = (uint32_t)(uint8_t)__ldg(wbase + (int64_t)eid * H);
+                        wvec = (u == 0) ? wb : (wvec | (wb << (8 * u)));
+                    }
+                }
+                accumulate_four<VEC>(acc, v, wvec);
+            }
+        }
+    }
+    // ---- ragged tail (and every batch of the narrow or per-element-weight configurations): predicated
+    for (; j0 < end; j0 += 32) {
         const int j = j0 + lane;
         int my_idx = -1, my_eid = 0;
         if (j < end) {
@@ -111,21 +165,27 @@ __device__ __forceinline__ void gather_segment(int (&acc)[VEC], int beg, int end
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int src_lane = ((s + u) * NB + grp) & 31;
-                const int idx = __shfl_sync(0xffffffffu, my_idx, src_lane);
+                int idx = __shfl_sync(0xffffffffu, my_idx, src_lane);
                 int eid = 0;
                 if (MODE != MODE_COPY) eid = __shfl_sync(0xffffffffu, my_eid, src_lane);
-                const bool ok = active && (s + u) < steps && idx >= 0;
+                if (s + u >= steps) idx = -1;
                 wsel[u] = 0; wrow[u] = nullptr;
-                if (ok) {
-                    v[u].load(a.feat + (int64_t)idx * a.ld + off);
-                    if (MODE == MODE_WEIGHT_LANE) wsel[u] = (uint32_t)(uint8_t)__ldg(a.ew + (int64_t)eid * a.H + head);
-                    if (MODE == MODE_WEIGHT_ELEM) wrow[u] = a.ew + (int64_t)eid * a.H;
+                if (idx >= 0) {
+                    v[u].load(base + (int64_t)idx * ld);
+                    if (MODE == MODE_WEIGHT_LANE) wsel[u] = (uint32_t)(uint8_t)__ldg(wbase + (int64_t)eid * H);
+                    if (MODE == MODE_WEIGHT_ELEM) wrow[u] = a.ew + (int64_t)eid * H;
                 } else {
                     v[u].zero();
                 }
             }
+            if (kFour) {
+                uint32_t wvec = 0x01010101u;
+                if (MODE == MODE_WEIGHT_LANE) wvec = wsel[0] | (wsel[1] << 8) | (wsel[2] << 16) | (wsel[3] << 24);
+                accumulate_four<VEC>(acc, v, wvec);
+            } else {
 #pragma unroll
-            for (int u = 0; u < U; ++u) accumulate<VEC, MODE>(acc, v[u], wsel[u], wrow[u], off, a);
+                for (int u = 0; u < U; ++u) accumulate_one<VEC, MODE>(acc, v[u], wsel[u], wrow[u], ld_off, a);
+            }
         }
     }
     for (int o = G; o < 32; o <<= 1) {
@@ -142,7 +202,13 @@ __device__ __forceinline__ float finish_value(float v, int64_t row, int col, con
 }
 
 template <int VEC, int MODE>
-__global__ void __launch_bounds__(256) spmm_kernel(const SpmmArgs a) {
+#ifndef SPMM_THREADS
+#define SPMM_THREADS 128
+#endif
+#ifndef SPMM_MINB
+#define SPMM_MINB 8
+#endif
+__global__ void __launch_bounds__(SPMM_THREADS, SPMM_MINB) spmm_kernel(const SpmmArgs a) {
     const int lane = threadIdx.x & 31;
     const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int sub = lane % a.G;
@@ -267,9 +333,9 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
         }
     }
     const int64_t warps = a.n_units + a.n_rows;
-    const int64_t blocks = ceil_div(warps, 8);
+    const int64_t blocks = ceil_div(warps, SPMM_THREADS / 32);
     if (blocks > 0x7fffffff) return TANGO_ESIZE;
-#define TANGO_SPMM_LAUNCH(V, M) spmm_kernel<V, M><<<(unsigned)blocks, 256, 0, stream>>>(a)
+#define TANGO_SPMM_LAUNCH(V, M) spmm_kernel<V, M><<<(unsigned)blocks, SPMM_THREADS, 0, stream>>>(a)
     if (MODE == MODE_WEIGHT_LANE && (a.D % vec) != 0) {
         if (vec == 16) TANGO_SPMM_LAUNCH(16, MODE_WEIGHT_ELEM);
         else if (vec == 4) TANGO_SPMM_LAUNCH(4, MODE_WEIGHT_ELEM);
