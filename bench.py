@@ -205,7 +205,7 @@ def run_ours(args):
     def step(feats, labels):
         opt.zero_grad(set_to_none=True)
         logits = model(feats)
-        loss = F.cross_entropy(logits, labels, reduction="sum") / n
+        loss = F.cross_entropy(logits, labels, reduction="none").sum() / n
         loss.backward()
         if world > 1:
             allreduce_grads(model)

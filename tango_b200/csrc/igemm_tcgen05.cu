@@ -226,8 +226,14 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
+        // Each warp drains the 32 accumulator rows it may read, 32 columns at a time: TMEM -> registers (one row per
+        // lane) -> dequantise -> a padded shared-memory tile -> registers (8 lanes per row) -> 128-bit coalesced
+        // global stores (or coalesced int32 atomics for the split-K mode).  The tile reuses pipeline-stage memory,
+        // which is idle once the accumulator barrier has fired.
         const int q = warp & 3;  // the 32-lane quarter of tensor memory this warp may read
         const int row = m0 + q * 32 + lane;
+        constexpr int kTileLd = 36;  // words per staged row: 16-byte aligned, conflict-free for 128-bit accesses
+        uint32_t *tile = reinterpret_cast<uint32_t *>(smem_raw + (smem_base - smem_u32(smem_raw))) + q * 32 * kTileLd;
         bool ok = n_iter > 0;
         if (ok) ok = mbar_wait(smem_u32(&bar_acc), 0u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -236,37 +242,61 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float sc = 0.f;
             if (p.mode == 0) sc = __fmul_rn(__ldg(p.sa), __ldg(p.sb));
-            for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
-                uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+            const bool vec_ok = p.mode == 0 ? ((p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0)
+                                            : false;
+            for (int c0 = 0; c0 < p.n_tile; c0 += 32) {
                 const int col0 = n0 + c0;
-                if (row < p.M && col0 < p.N) {
-                    if (p.mode == 0) {
-                        float v[16];
+                const int width = min(32, p.n_tile - c0);  // 32, or 16 for the last chunk
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            v[i] = __fmul_rn((float)(int)r[i], sc);
-                            if (p.bias && col0 + i < p.N) v[i] = __fadd_rn(v[i], __ldg(p.bias + col0 + i));
-                            if (col0 + i < p.N) amax = fmaxf(amax, fabsf(v[i]));
+                for (int half = 0; half < 2; ++half) {
+                    if (half * 16 < width) {  // warp-uniform
+                        uint32_t r[16];
+                        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c0 + half * 16), r);
+                        if (p.mode == 0) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const int col = col0 + half * 16 + i;
+                                float v = __fmul_rn((float)(int)r[i], sc);
+                                if (p.bias && col < p.N) v = __fadd_rn(v, __ldg(p.bias + col));
+                                if (col < p.N && row < p.M) amax = fmaxf(amax, fabsf(v));
+                                r[i] = __float_as_uint(v);
+                            }
                         }
-                        float *o = p.out + (int64_t)row * p.ldo + col0;
-                        if (col0 + 16 <= p.N && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                reinterpret_cast<float4 *>(o)[i] =
-                                    make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                if (col0 + i < p.N) o[i] = v[i];
-                        }
-                    } else {
-                        int32_t *o = p.ws + (int64_t)row * p.ldws + col0;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            if (col0 + i < p.N && r[i] != 0) atomicAdd(o + i, (int)r[i]);
+                        for (int i = 0; i < 4; ++i)
+                            *reinterpret_cast<uint4 *>(tile + lane * kTileLd + half * 16 + 4 * i) =
+                                make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
                     }
                 }
+                __syncwarp();
+                if (p.mode == 0 && vec_ok) {
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3), cv = (lane & 7) * 4;
+                        const int grow = m0 + q * 32 + rr, gcol = col0 + cv;
+                        if (grow < p.M && cv < width && gcol < p.N) {
+                            const uint4 t = *reinterpret_cast<const uint4 *>(tile + rr * kTileLd + cv);
+                            float *o = p.out + (int64_t)grow * p.ldo + gcol;
+                            if (gcol + 4 <= p.N) {
+                                *reinterpret_cast<uint4 *>(o) = t;
+                            } else {
+                                const uint32_t e[4] = {t.x, t.y, t.z, t.w};
+                                for (int i = 0; i < 4 && gcol + i < p.N; ++i) o[i] = __uint_as_float(e[i]);
+                            }
+                        }
+                    }
+                } else {
+                    // one staged row per step, one column per lane: 128-byte coalesced scalar stores / atomics
+                    for (int rr = 0; rr < 32; ++rr) {
+                        const int grow = m0 + q * 32 + rr, gcol = col0 + lane;
+                        if (grow < p.M && lane < width && gcol < p.N) {
+                            const uint32_t t = tile[rr * kTileLd + lane];
+                            if (p.mode == 0) p.out[(int64_t)grow * p.ldo + gcol] = __uint_as_float(t);
+                            else if (t != 0) atomicAdd(p.ws + (int64_t)grow * p.ldws + gcol, (int)t);
+                        }
+                    }
+                }
+                __syncwarp();
             }
         }
         if (p.absmax && p.mode == 0) {

@@ -24,27 +24,34 @@ struct Philox {
 };
 
 // ---------------------------------------------------------------------------------------------- absmax
-template <bool VEC4>
+// LW = floats per load (4, 2 or 1): rows must start on an LW-float boundary (base aligned, ld % LW == 0); the columns
+// past the last full vector of a row are read one by one.
+template <int LW>
 __global__ void __launch_bounds__(256) absmax_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
                                                      int64_t ld, const float *__restrict__ row_scale,
                                                      float *__restrict__ scale) {
     float m = 0.f;
-    if (VEC4) {
-        // cols % 4 == 0, ld % 4 == 0, base 16-byte aligned
-        const int64_t c4 = cols >> 2, total = rows * c4;
-        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-             i += (int64_t)gridDim.x * blockDim.x) {
-            const int64_t r = i / c4, c = (i - r * c4) << 2;
+    const int64_t cv = cols / LW, total = rows * cv;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cv, c = (i - r * cv) * LW;
+        float t;
+        if (LW == 4) {
             const float4 v = __ldcs(reinterpret_cast<const float4 *>(x + r * ld + c));
-            float t = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-            if (row_scale) t = __fmul_rn(t, fabsf(__ldg(row_scale + r)));
-            m = fmaxf(m, t);
+            t = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        } else if (LW == 2) {
+            const float2 v = __ldcs(reinterpret_cast<const float2 *>(x + r * ld + c));
+            t = fmaxf(fabsf(v.x), fabsf(v.y));
+        } else {
+            t = fabsf(x[r * ld + c]);
         }
-    } else {
-        const int64_t total = rows * cols;
-        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+        if (row_scale) t = __fmul_rn(t, fabsf(__ldg(row_scale + r)));
+        m = fmaxf(m, t);
+    }
+    const int64_t rem = cols - cv * LW;  // < LW columns per row left over
+    if (rem > 0) {
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < rows * rem;
              i += (int64_t)gridDim.x * blockDim.x) {
-            const int64_t r = i / cols, c = i - r * cols;
+            const int64_t r = i / rem, c = cv * LW + (i - r * rem);
             float t = fabsf(x[r * ld + c]);
             if (row_scale) t = __fmul_rn(t, fabsf(__ldg(row_scale + r)));
             m = fmaxf(m, t);
@@ -63,8 +70,8 @@ __device__ __forceinline__ int round_to_i8(float t, int mode, float u) {
     return (int)r;
 }
 
-// One thread produces 16 consecutive output bytes of one row (a 128-bit store).
-template <bool VEC4>
+// One thread produces 16 consecutive output bytes of one row (a 128-bit store).  LW = floats per input load.
+template <int LW>
 __global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
                                                        int64_t ldx, const float *__restrict__ row_scale,
                                                        const float *__restrict__ scale, int8_t *__restrict__ q,
@@ -77,11 +84,17 @@ __global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__
         const int64_t r = i / groups, c0 = (i - r * groups) << 4;
         const float rs = row_scale ? __ldg(row_scale + r) : 1.f;
         float v[16];
-        if (VEC4 && c0 + 16 <= cols) {
+        if (LW == 4 && c0 + 16 <= cols) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const float4 t = __ldcs(reinterpret_cast<const float4 *>(x + r * ldx + c0 + 4 * k));
                 v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
+            }
+        } else if (LW == 2 && c0 + 16 <= cols) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float2 t = __ldcs(reinterpret_cast<const float2 *>(x + r * ldx + c0 + 2 * k));
+                v[2 * k] = t.x; v[2 * k + 1] = t.y;
             }
         } else {
 #pragma unroll
@@ -208,14 +221,11 @@ extern "C" int tango_absmax_scale(const float *x, int64_t rows, int64_t cols, in
     if (ld == cols && !row_scale) {  // contiguous: treat as one long row so the vector path applies to any shape
         cols = rows * cols; rows = 1; ld = cols;
     }
-    const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && aligned(x, 16);
-    if (vec) {
-        const int grid = stream_grid(rows * (cols / 4), 256, 8);
-        absmax_kernel<true><<<grid, 256, 0, stream>>>(x, rows, cols, ld, row_scale, scale);
-    } else {
-        const int grid = stream_grid(rows * cols, 256, 8);
-        absmax_kernel<false><<<grid, 256, 0, stream>>>(x, rows, cols, ld, row_scale, scale);
-    }
+    const int lw = (aligned(x, 16) && (rows == 1 || ld % 4 == 0)) ? 4 : (aligned(x, 8) && (rows == 1 || ld % 2 == 0)) ? 2 : 1;
+    const int grid = stream_grid(rows * ceil_div(cols, lw), 256, 16);
+    if (lw == 4) absmax_kernel<4><<<grid, 256, 0, stream>>>(x, rows, cols, ld, row_scale, scale);
+    else if (lw == 2) absmax_kernel<2><<<grid, 256, 0, stream>>>(x, rows, cols, ld, row_scale, scale);
+    else absmax_kernel<1><<<grid, 256, 0, stream>>>(x, rows, cols, ld, row_scale, scale);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
 }
@@ -231,12 +241,14 @@ extern "C" int tango_quantize(const float *x, int64_t rows, int64_t cols, int64_
         cols = rows * cols; rows = 1; ldx = ldq = cols;
     }
     if ((ldq % 16 == 0 || rows == 1) && aligned(q, 16)) {
-        const bool vec = (ldx % 4 == 0 || rows == 1) && aligned(x, 16);
-        const int grid = stream_grid(rows * ceil_div(ldq, 16), 256, 8);
-        if (vec)
-            quantize_kernel<true><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+        const int lw = (aligned(x, 16) && (rows == 1 || ldx % 4 == 0)) ? 4 : (aligned(x, 8) && (rows == 1 || ldx % 2 == 0)) ? 2 : 1;
+        const int grid = stream_grid(rows * ceil_div(ldq, 16), 256, 16);
+        if (lw == 4)
+            quantize_kernel<4><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+        else if (lw == 2)
+            quantize_kernel<2><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
         else
-            quantize_kernel<false><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+            quantize_kernel<1><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
     } else {
         const int grid = stream_grid(rows * ldq, 256, 8);
         quantize_scalar_kernel<<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);

@@ -20,14 +20,75 @@ def _norm(deg: torch.Tensor, both: bool) -> torch.Tensor:
     return torch.pow(d, -0.5) if both else 1.0 / d
 
 
+def _cached_norm(graph, which: str) -> torch.Tensor:
+    """deg^-1/2 (degrees clamped to >= 1) as a contiguous fp32 vector, computed once per graph."""
+    cache = graph.ndata.setdefault("_tango_norm", {})
+    if which not in cache:
+        deg = graph.in_degrees() if which == "in" else graph.out_degrees()
+        cache[which] = _norm(deg, True).contiguous()
+    return cache[which]
+
+
+class _gcn_conv_fused(Function):
+    """One "multiply first" graph convolution (in_feats > out_feats, norm='both') as a single autograd node:
+
+        out = act( (A . Q(Q(X * d_out^-1/2) W^T)) * d_in^-1/2 + b )
+
+    Same arithmetic, operation for operation, as the unfused composition in QGraphConv.forward (bit-identical
+    results), but the element-wise passes of the reference's layer (evaluation/test_gcn.py:86-94,123-137) are folded
+    into the kernels next to them: the left norm into the absmax/quantize of X, the right norm + bias + ReLU into the
+    aggregation's epilogue, and the right norm of the backward pass into the quantizer of the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, g, X, W, b, out_norm, in_norm, relu):
+        from .kernels import alloc_int8, next_call
+        mode_f, mode_q, seed = config.mode_for("gemm_fwd"), config.mode_for("quantize"), config.seed()
+        call = next_call() if mode_f == kernels.ROUND_STOCHASTIC else 0
+        if mode_f == kernels.ROUND_STOCHASTIC:
+            next_call()
+        X = X.contiguous()
+        sX = kernels._get_scale(X, out_norm)
+        sW = kernels._get_scale(W)
+        Xq, Wq = alloc_int8(X.shape, X.device), alloc_int8(W.shape, X.device)
+        kernels._quantize_into(Xq, X, sX, mode_f, seed, call, out_norm)
+        kernels._quantize_into(Wq, W.contiguous(), sW, mode_f, seed, call + 1)
+        H = torch.empty((X.shape[0], W.shape[0]), dtype=torch.float32, device=X.device)
+        sH = torch.zeros(1, dtype=torch.float32, device=X.device)
+        kernels._qgemm_nt(H, Xq, Wq, sX, sW, None, sH)
+        Hq, _ = kernels.quantize(H, sH, mode=mode_q, seed=seed)
+        out = kernels.csr_SPMM(g, Hq, sH, False, in_norm, b, relu)
+        ctx.g, ctx.relu, ctx.has_bias = g, relu, b is not None
+        ctx.save_for_backward(Xq, sX, Wq, sW, out_norm, in_norm, out if relu else None)
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_out):
+        Xq, sX, Wq, sW, out_norm, in_norm, out = ctx.saved_tensors
+        mode_q, seed = config.mode_for("quantize"), config.seed()
+        g1 = torch.where(out > 0, d_out, torch.zeros((), device=d_out.device)) if ctx.relu else d_out.contiguous()
+        db = g1.sum(0) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
+        sdZ = kernels._get_scale(g1, in_norm)
+        dZq = kernels.alloc_int8(g1.shape, g1.device)
+        call = kernels.next_call() if mode_q == kernels.ROUND_STOCHASTIC else 0
+        kernels._quantize_into(dZq, g1, sdZ, mode_q, seed, call, in_norm)
+        dH = kernels.csr_SPMM(ctx.g, dZq, sdZ, True)
+        dHq, sdH = kernels.quantize(dH, mode=mode_q, seed=seed)
+        dX, dW = kernels.QGEMM_backward(dHq, Xq, Wq, sdH, sX, sW, ctx.needs_input_grad[1], ctx.needs_input_grad[2])
+        if dX is not None:
+            dX = dX * out_norm.unsqueeze(1)
+        return None, dX, dW, db, None, None, None
+
+
 class QGraphConv(nn.Module):
     """Graph convolution with int8 GEMM and int8 aggregation (evaluation/test_gcn.py:40-139).  As in the reference,
     the linear layer runs first when it shrinks the features (and hands its output scale to the aggregation), else
     the aggregation runs first."""
 
     def __init__(self, in_feats, out_feats, norm="both", weight=True, bias=True, activation=None,
-                 allow_zero_in_degree=False):
+                 allow_zero_in_degree=False, fused=True):
         super().__init__()
+        self._fused = fused
         if norm not in ("none", "both", "right", "left"):
             raise ValueError(f'Invalid norm value "{norm}"')
         self._in_feats, self._out_feats, self._norm = in_feats, out_feats, norm
@@ -46,6 +107,14 @@ class QGraphConv(nn.Module):
     def forward(self, graph, feat):
         if not self._allow_zero_in_degree and bool((graph.in_degrees() == 0).any()):
             raise RuntimeError("There are 0-in-degree nodes in the graph; add self loops first")
+        if (self._fused and self._norm == "both" and self.weight is not None and self._in_feats > self._out_feats
+                and feat.dim() == 2):
+            relu = self._activation in (F.relu, torch.relu)
+            rst = _gcn_conv_fused.apply(graph, feat, self.weight, self.bias, _cached_norm(graph, "out"),
+                                        _cached_norm(graph, "in"), relu)
+            if self._activation is not None and not relu:
+                rst = self._activation(rst)
+            return rst
         feat_src = feat
         if self._norm in ("left", "both"):
             feat_src = feat_src * _norm(graph.out_degrees(), self._norm == "both").unsqueeze(1)
@@ -71,14 +140,14 @@ class QGraphConv(nn.Module):
 class GCN(nn.Module):
     """Stack of QGraphConv layers (evaluation/test_gcn.py:143-175): in -> hidden (x n_layers) -> classes."""
 
-    def __init__(self, g, in_feats, n_hidden, n_classes, n_layers, activation=F.relu, dropout=0.0):
+    def __init__(self, g, in_feats, n_hidden, n_classes, n_layers, activation=F.relu, dropout=0.0, fused=True):
         super().__init__()
         self.g = g
         self.layers = nn.ModuleList()
-        self.layers.append(QGraphConv(in_feats, n_hidden, activation=activation))
+        self.layers.append(QGraphConv(in_feats, n_hidden, activation=activation, fused=fused))
         for _ in range(n_layers - 1):
-            self.layers.append(QGraphConv(n_hidden, n_hidden, activation=activation))
-        self.layers.append(QGraphConv(n_hidden, n_classes))
+            self.layers.append(QGraphConv(n_hidden, n_hidden, activation=activation, fused=fused))
+        self.layers.append(QGraphConv(n_hidden, n_classes, fused=fused))
         self.dropout = nn.Dropout(p=dropout)
 
     def forward(self, features):

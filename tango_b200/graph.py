@@ -138,7 +138,7 @@ class Graph:
     def to(self, device) -> "Graph":
         g = Graph(self._src.to(device), self._dst.to(device), self._n)
         g.n_classes = self.n_classes
-        g.ndata = {k: v.to(device) for k, v in self.ndata.items()}
+        g.ndata = {k: v.to(device) for k, v in self.ndata.items() if torch.is_tensor(v)}
         g.srcdata = g.dstdata = g.ndata
         return g
 

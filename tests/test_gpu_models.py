@@ -1,0 +1,162 @@
+"""Model-level parity on the GPU: the quantized GCN layer chain against the CPU oracle chain (bit-exact forward,
+1e-3 gradients), fused vs unfused layer (bit-identical), GAT layer against its fp32 formulation, autograd
+operators against fp32 autograd within quantisation error."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import fp32_baseline as B
+from oracle import tango_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(n=1500, e=20000, seed=3):
+    import tango_b200 as T
+    from tango_b200.graph import rmat_graph
+    g = rmat_graph(n, e, seed, device="cuda")
+    T.graph_preprocess(g)
+    return g
+
+
+def _oracle_gcn_layer(g, x, w, b, relu):
+    """The layer of evaluation/test_gcn.py:86-137 ("multiply first" branch) with the oracle primitives."""
+    csc = [t.cpu().numpy().astype(np.int64) for t in g.adj_csc]
+    on = g.out_degrees().float().clamp(min=1).pow(-0.5).cpu().numpy()
+    inn = g.in_degrees().float().clamp(min=1).pow(-0.5).cpu().numpy()
+    xs = (x * on[:, None]).astype(np.float32)
+    h, *_rest, sh = O.qgemm_forward(xs, w, reduce_out=True)
+    agg = O.spmm_copy_u(csc[0], csc[1], O.quantize(h, sh), sh)
+    out = ((agg * inn[:, None]).astype(np.float32) + b[None, :]).astype(np.float32)
+    return np.maximum(out, 0) if relu else out
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_gcn_layer_forward_bit_exact_vs_oracle(cuda, fused):
+    from tango_b200.gnn import QGraphConv
+    g = _setup()
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((g.num_nodes(), 100)).astype(np.float32)
+    layer = QGraphConv(100, 32, activation=F.relu, fused=fused).cuda()
+    with torch.no_grad():
+        layer.bias.copy_(torch.from_numpy(rng.standard_normal(32).astype(np.float32)))
+    out = layer(g, torch.from_numpy(x).cuda())
+    ref = _oracle_gcn_layer(g, x, layer.weight.detach().cpu().numpy(), layer.bias.detach().cpu().numpy(), True)
+    np.testing.assert_array_equal(out.detach().cpu().numpy(), ref)
+
+
+def test_fused_and_unfused_gcn_are_bit_identical(cuda):
+    from tango_b200.gnn import GCN
+    g = _setup(2000, 30000, 5)
+    torch.manual_seed(1)
+    x = torch.randn(g.num_nodes(), 602, device="cuda", requires_grad=True)
+    y = torch.randint(0, 7, (g.num_nodes(),), device="cuda")
+    res = []
+    for fused in (True, False):
+        torch.manual_seed(2)
+        m = GCN(g, 602, 64, 7, 1, fused=fused).cuda()
+        xi = x.detach().clone().requires_grad_(True)
+        loss = F.cross_entropy(m(xi), y)
+        loss.backward()
+        res.append((loss.item(), xi.grad.clone(), [p.grad.clone() for p in m.parameters()]))
+    assert res[0][0] == res[1][0]
+    assert torch.equal(res[0][1], res[1][1])
+    for a, b in zip(res[0][2], res[1][2]):
+        assert torch.equal(a, b)
+
+
+def test_gcn_training_step_close_to_fp32(cuda):
+    """Loss and gradients of the int8 model stay within quantisation error of the fp32 formulation."""
+    from tango_b200.gnn import GCN
+    g = _setup(3000, 60000, 7)
+    n = g.num_nodes()
+    torch.manual_seed(3)
+    x = torch.randn(n, 128, device="cuda")
+    y = torch.randint(0, 5, (n,), device="cuda")
+    m = GCN(g, 128, 32, 5, 1).cuda()
+    loss = F.cross_entropy(m(x), y)
+    loss.backward()
+    csc, csr = g.adj_csc, g.adj_csr
+    ref = B.GCNfp32(B.csr_matrix(csc[0], csc[1], n), B.csr_matrix(csr[0], csr[1], n), g.out_degrees(), g.in_degrees(),
+                    [l.weight for l in m.layers], [l.bias for l in m.layers])
+    rloss = F.cross_entropy(ref(x.cpu()), y.cpu())
+    rloss.backward()
+    assert abs(loss.item() - rloss.item()) / rloss.item() < 1e-2
+    for l, w in zip(m.layers, ref.weights):
+        err = (l.weight.grad.cpu() - w.grad).abs().max() / w.grad.abs().max()
+        assert err < 0.1, err
+
+
+def test_operator_gradients_vs_fp32(cuda):
+    import tango_b200 as T
+    g = _setup(800, 9000, 11)
+    n, e = g.num_nodes(), g.num_edges()
+    src, dst = [t.long() for t in g.coo]
+    torch.manual_seed(0)
+    # QLinear
+    x = torch.randn(n, 64, device="cuda", requires_grad=True)
+    lin = T.QLinear(64, 48).cuda()
+    y = lin(x)
+    y.square().sum().backward()
+    xr = x.detach().clone().requires_grad_(True)
+    yr = F.linear(xr, lin.weight.detach(), lin.bias.detach())
+    yr.square().sum().backward()
+    assert (y - yr).abs().max() / yr.abs().max() < 0.05
+    assert (x.grad - xr.grad).abs().max() / xr.grad.abs().max() < 0.1
+    # spmm_u_mul_e and sddmm_u_dot_v against dense-gather fp32 formulas
+    h = torch.randn(n, 4, 16, device="cuda", requires_grad=True)
+    a = torch.rand(e, 4, 1, device="cuda", requires_grad=True)
+    out = T.spmm_u_mul_e.apply(g, h, a)
+    ref = torch.zeros(n, 4, 16, device="cuda").index_add_(0, dst, h[src] * a)
+    assert (out - ref).abs().max() / ref.abs().max() < 0.05
+    out.sum().backward()
+    ref_dh = torch.zeros(n, 4, 16, device="cuda").index_add_(0, src, a.detach().expand(e, 4, 16).contiguous())
+    assert (h.grad - ref_dh).abs().max() / ref_dh.abs().max() < 0.05
+    ref_da = h.detach()[src].sum(-1, keepdim=True)
+    assert (a.grad - ref_da).abs().max() / ref_da.abs().max() < 0.05
+    u = torch.randn(n, 4, 16, device="cuda", requires_grad=True)
+    v = torch.randn(n, 4, 16, device="cuda", requires_grad=True)
+    s = T.sddmm_u_dot_v.apply(g, u, v)
+    sref = (u[src] * v[dst]).sum(-1, keepdim=True)
+    assert (s - sref).abs().max() / sref.abs().max() < 0.05
+    s.sum().backward()
+    ref_du = torch.zeros(n, 4, 16, device="cuda").index_add_(0, src, v.detach()[dst])
+    assert (u.grad - ref_du).abs().max() / ref_du.abs().max() < 0.05
+    # sddmm_u_add_v backward = incidence sums
+    el = torch.randn(n, 4, 1, device="cuda", requires_grad=True)
+    er = torch.randn(n, 4, 1, device="cuda", requires_grad=True)
+    z = T.sddmm_u_add_v.apply(g, el, er)
+    w = torch.randn_like(z)
+    (z * w).sum().backward()
+    ref_del = torch.zeros(n, 4, 1, device="cuda").index_add_(0, src, w)
+    assert (el.grad - ref_del).abs().max() / ref_del.abs().max() < 0.05
+
+
+def test_gat_layer_close_to_fp32(cuda):
+    from tango_b200.gnn import GAT
+    g = _setup(1000, 15000, 13)
+    n = g.num_nodes()
+    src, dst = [t.long() for t in g.coo]
+    torch.manual_seed(5)
+    x = torch.randn(n, 64, device="cuda")
+    y = torch.randint(0, 6, (n,), device="cuda")
+    m = GAT(g, 2, 64, 16, 6, [4, 1]).cuda()
+    logits = m(x)
+    loss = F.cross_entropy(logits, y)
+    loss.backward()
+    assert torch.isfinite(loss) and all(torch.isfinite(p.grad).all() for p in m.parameters())
+
+    def ref_layer(layer, h, act):
+        ft = F.linear(h, layer.fc.weight).view(n, layer._num_heads, layer._out_feats)
+        el = (ft * layer.attn_l).sum(-1, keepdim=True)
+        er = (ft * layer.attn_r).sum(-1, keepdim=True)
+        e = F.leaky_relu(el[src] + er[dst], 0.2)
+        a = B.edge_softmax(dst.cpu(), e.cpu(), n).cuda()
+        out = torch.zeros_like(ft).index_add_(0, dst, ft[src] * a) + layer.bias.view(1, layer._num_heads, -1)
+        return act(out) if act else out
+
+    with torch.no_grad():
+        h1 = ref_layer(m.gat_layers[0], x, F.elu).flatten(1)
+        ref = ref_layer(m.gat_layers[1], h1, None).mean(1)
+    assert (logits - ref).abs().max() / ref.abs().max() < 0.1
