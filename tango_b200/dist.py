@@ -17,7 +17,7 @@ import torch.nn.functional as F
 from torch.autograd.function import Function, once_differentiable
 
 from . import config
-from .graph import Graph, RowPartition
+from .graph import Graph, RowPartition, balanced_bounds, uniform_bounds
 
 
 def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_rows: int, group=None):
@@ -42,12 +42,17 @@ def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_row
 class DistGraph:
     """Rank-local view of a graph that every rank holds (or can rebuild from the same seed)."""
 
-    def __init__(self, g: Graph, rank: int, world: int):
+    def __init__(self, g: Graph, rank: int, world: int, balance: str = "nnz"):
+        """balance='nnz': contiguous blocks with equal in-degree + out-degree (forward and backward aggregation cost);
+        balance='rows': equal row counts."""
         n = g.num_nodes()
         self.rank, self.world, self.n_total = rank, world, n
         csc, csr = g.adj_csc, g.adj_csr
-        self.fwd = RowPartition(csc[0], csc[1], None, n, rank, world)
-        self.bwd = RowPartition(csr[0], csr[1], None, n, rank, world)
+        bounds = (balanced_bounds(g.in_degrees() + g.out_degrees(), world) if balance == "nnz"
+                  else uniform_bounds(n, world))
+        self.bounds = bounds
+        self.fwd = RowPartition(csc[0], csc[1], None, n, rank, world, bounds)
+        self.bwd = RowPartition(csr[0], csr[1], None, n, rank, world, bounds)
         self.shard_rows, self.r0, self.r1, self.n_local = self.fwd.shard_rows, self.fwd.r0, self.fwd.r1, self.fwd.n_local
         self.in_norm = g.in_degrees()[self.r0:self.r1].float().clamp(min=1).pow(-0.5).contiguous()
         self.out_norm = g.out_degrees()[self.r0:self.r1].float().clamp(min=1).pow(-0.5).contiguous()
@@ -76,15 +81,66 @@ class dist_spmm_copy_u(Function):
         return None, dn, None
 
 
-def _aggregate(dg: DistGraph, part: RowPartition, x_local: torch.Tensor, scale_local: Optional[torch.Tensor]):
+def _aggregate(dg: DistGraph, part: RowPartition, x_local: torch.Tensor, scale_local: Optional[torch.Tensor],
+               row_scale=None, bias=None, relu=False, in_row_scale=None):
+    """Quantize the local rows (optionally times in_row_scale[r]) with the local scale, all-gather the int8 shards
+    and scales, aggregate this rank's rows; row_scale / bias / relu go to the aggregation's epilogue."""
     from . import kernels as K
-    q, s = K.quantize(x_local, scale_local, mode=config.mode_for("quantize"), seed=config.seed())
-    q_all, scales = all_gather_quantized(_padded_storage(q), s, dg.shard_rows)
+    mode, seed = config.mode_for("quantize"), config.seed()
+    x_local = x_local.contiguous()
+    if scale_local is None:
+        scale_local = K._get_scale(x_local, in_row_scale)
+    q = K.alloc_int8(x_local.shape, x_local.device)
+    call = K.next_call() if mode == K.ROUND_STOCHASTIC else 0
+    K._quantize_into(q, x_local, scale_local, mode, seed, call, in_row_scale)
+    q_all, scales = all_gather_quantized(_padded_storage(q), scale_local, dg.shard_rows)
     f = x_local.shape[1]
     out = torch.empty((dg.n_local, f), dtype=torch.float32, device=x_local.device)
     K._csr_spmm(out, part.indptr, part.indices, q_all[:, :f] if q_all.shape[1] != f else q_all, scales,
-                part.schedule, dg.world)
+                part.schedule, dg.world, row_scale, bias, relu)
     return out
+
+
+class _dist_gcn_conv_fused(Function):
+    """The fused "multiply first" graph convolution of tango_b200.gnn on a row partition: left norm folded into the
+    quantizer of the local features, int8 GEMM with output scale, all-gather of the int8 shard, aggregation with the
+    right norm + bias + ReLU in its epilogue.  The backward pass mirrors it on the transposed partition."""
+
+    @staticmethod
+    def forward(ctx, dg, X, W, b, relu):
+        from . import kernels as K
+        mode_f, mode_q, seed = config.mode_for("gemm_fwd"), config.mode_for("quantize"), config.seed()
+        call = K.next_call() if mode_f == K.ROUND_STOCHASTIC else 0
+        if mode_f == K.ROUND_STOCHASTIC:
+            K.next_call()
+        X = X.contiguous()
+        sX, sW = K._get_scale(X, dg.out_norm), K._get_scale(W)
+        Xq, Wq = K.alloc_int8(X.shape, X.device), K.alloc_int8(W.shape, X.device)
+        K._quantize_into(Xq, X, sX, mode_f, seed, call, dg.out_norm)
+        K._quantize_into(Wq, W.contiguous(), sW, mode_f, seed, call + 1)
+        H = torch.empty((X.shape[0], W.shape[0]), dtype=torch.float32, device=X.device)
+        sH = torch.zeros(1, dtype=torch.float32, device=X.device)
+        K._qgemm_nt(H, Xq, Wq, sX, sW, None, sH)
+        out = _aggregate(dg, dg.fwd, H, sH, dg.in_norm, b, relu)
+        ctx.dg, ctx.relu, ctx.has_bias = dg, relu, b is not None
+        ctx.save_for_backward(Xq, sX, Wq, sW, out if relu else None)
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_out):
+        from . import kernels as K
+        dg = ctx.dg
+        Xq, sX, Wq, sW, out = ctx.saved_tensors
+        mode_q, seed = config.mode_for("quantize"), config.seed()
+        g1 = torch.where(out > 0, d_out, torch.zeros((), device=d_out.device)) if ctx.relu else d_out.contiguous()
+        db = g1.sum(0) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
+        dH = _aggregate(dg, dg.bwd, g1, None, None, None, False, in_row_scale=dg.in_norm)
+        dHq, sdH = K.quantize(dH, mode=mode_q, seed=seed)
+        dX, dW = K.QGEMM_backward(dHq, Xq, Wq, sdH, sX, sW, ctx.needs_input_grad[1], ctx.needs_input_grad[2])
+        if dX is not None:
+            dX = dX * dg.out_norm.unsqueeze(1)
+        return None, dX, dW, db, None
 
 
 class DistQGraphConv(nn.Module):
@@ -98,13 +154,13 @@ class DistQGraphConv(nn.Module):
         nn.init.xavier_uniform_(self.weight)
 
     def forward(self, dg: DistGraph, feat_local):
-        from .QLinear import Qlinear_func, Qlinear_func_reduce
-        h = feat_local * dg.out_norm.unsqueeze(1)
+        from .QLinear import Qlinear_func
         if self._in_feats > self._out_feats:
-            h, s = Qlinear_func_reduce.apply(h, self.weight)
-            rst = dist_spmm_copy_u.apply(dg, h, s)
-        else:
-            rst = Qlinear_func.apply(dist_spmm_copy_u.apply(dg, h), self.weight)
+            relu = self._activation in (F.relu, torch.relu)
+            rst = _dist_gcn_conv_fused.apply(dg, feat_local, self.weight, self.bias, relu)
+            return self._activation(rst) if (self._activation is not None and not relu) else rst
+        h = feat_local * dg.out_norm.unsqueeze(1)
+        rst = Qlinear_func.apply(dist_spmm_copy_u.apply(dg, h), self.weight)
         rst = rst * dg.in_norm.unsqueeze(1) + self.bias
         return self._activation(rst) if self._activation is not None else rst
 

@@ -244,27 +244,54 @@ class SpmmSchedule:
         self.n_units = int(self.units.shape[0])
 
 
+def balanced_bounds(weights: torch.Tensor, world: int):
+    """Contiguous row blocks [b_k, b_k+1) with (nearly) equal total weight -- e.g. in-degree + out-degree, so that
+    the skewed rows of a power-law graph do not all land on rank 0.  Returns a list of world + 1 Python ints."""
+    n = weights.numel()
+    cum = torch.cumsum(weights.double(), 0)
+    total = float(cum[-1]) if n else 0.0
+    targets = torch.tensor([total * k / world for k in range(1, world)], dtype=torch.float64, device=weights.device)
+    cuts = torch.searchsorted(cum, targets).tolist() if world > 1 else []
+    b = [0] + [min(n, int(c) + 1) for c in cuts] + [n]
+    for k in range(1, len(b)):            # keep the boundaries monotone
+        b[k] = max(b[k], b[k - 1])
+    return b
+
+
+def uniform_bounds(n_nodes: int, world: int):
+    step = (n_nodes + world - 1) // world
+    return [min(n_nodes, k * step) for k in range(world)] + [n_nodes]
+
+
 class RowPartition:
-    """Rank `rank`'s block of rows [r0, r1) of a CSR/CSC whose column ids stay global.  `indptr` has
-    n_local * world + 1 entries: row v owns `world` consecutive segments, segment k holding the columns that live on
-    rank k (columns are sorted, so segments are contiguous)."""
+    """Rank `rank`'s block of rows [r0, r1) of a CSR/CSC.  Column ids are rewritten for the all-gathered feature
+    buffer, in which rank k's rows start at k * shard_rows (shard_rows = the largest block; shorter blocks are
+    padded).  `indptr` has n_local * world + 1 entries: row v owns `world` consecutive segments, segment k holding the
+    columns that live on rank k (columns are sorted, so segments are contiguous)."""
 
     def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, edge_ids: Optional[torch.Tensor], n_nodes: int,
-                 rank: int, world: int):
+                 rank: int, world: int, bounds=None):
         self.world, self.rank = world, rank
-        self.shard_rows = (n_nodes + world - 1) // world
-        self.r0 = min(n_nodes, rank * self.shard_rows)
-        self.r1 = min(n_nodes, self.r0 + self.shard_rows)
+        self.bounds = list(bounds) if bounds is not None else uniform_bounds(n_nodes, world)
+        assert len(self.bounds) == world + 1 and self.bounds[0] == 0 and self.bounds[-1] == n_nodes
+        self.shard_rows = max(1, max(self.bounds[k + 1] - self.bounds[k] for k in range(world)))
+        self.r0, self.r1 = self.bounds[rank], self.bounds[rank + 1]
         self.n_local = self.r1 - self.r0
+        dev = indptr.device
         ip = indptr.long()
         lo, hi = int(ip[self.r0]), int(ip[self.r1])
-        self.indices = indices[lo:hi].contiguous()
+        cols = indices[lo:hi].long()
+        bt = torch.tensor(self.bounds, dtype=torch.int64, device=dev)
+        owner = torch.searchsorted(bt, cols, right=True) - 1            # rank that owns each column
+        remapped = owner * self.shard_rows + (cols - bt[owner])          # row in the gathered buffer (monotone in col)
+        self.indices = remapped.to(torch.int32).contiguous()
         self.edge_ids = None if edge_ids is None else edge_ids[lo:hi].contiguous()
-        rows = torch.repeat_interleave(torch.arange(self.n_local, device=indptr.device),
+        rows = torch.repeat_interleave(torch.arange(self.n_local, device=dev),
                                        (ip[self.r0 + 1:self.r1 + 1] - ip[self.r0:self.r1]))
-        key = rows * (self.shard_rows * world) + self.indices.long()
-        bounds = (torch.arange(self.n_local, device=indptr.device)[:, None] * (self.shard_rows * world)
-                  + torch.arange(world, device=indptr.device)[None, :] * self.shard_rows).flatten()
-        seg = torch.searchsorted(key, bounds)
-        self.indptr = torch.cat([seg, torch.tensor([hi - lo], device=indptr.device)]).to(torch.int32)
+        span = self.shard_rows * world
+        key = rows * span + remapped
+        seg_bounds = (torch.arange(self.n_local, device=dev)[:, None] * span
+                      + torch.arange(world, device=dev)[None, :] * self.shard_rows).flatten()
+        seg = torch.searchsorted(key, seg_bounds)
+        self.indptr = torch.cat([seg, torch.tensor([hi - lo], device=dev)]).to(torch.int32)
         self.schedule = SpmmSchedule(self.indptr, nseg=world)
