@@ -20,6 +20,15 @@ def _norm(deg: torch.Tensor, both: bool) -> torch.Tensor:
     return torch.pow(d, -0.5) if both else 1.0 / d
 
 
+def _has_zero_in_degree(graph) -> bool:
+    """The reference's layers check this on every forward (evaluation/test_gcn.py:69-79), which costs a device
+    synchronisation per call; the graph is immutable here, so the answer is computed once."""
+    cache = graph.ndata.setdefault("_tango_norm", {})
+    if "zero_in" not in cache:
+        cache["zero_in"] = bool((graph.in_degrees() == 0).any())
+    return cache["zero_in"]
+
+
 def _cached_norm(graph, which: str) -> torch.Tensor:
     """deg^-1/2 (degrees clamped to >= 1) as a contiguous fp32 vector, computed once per graph."""
     cache = graph.ndata.setdefault("_tango_norm", {})
@@ -105,7 +114,7 @@ class QGraphConv(nn.Module):
             nn.init.zeros_(self.bias)
 
     def forward(self, graph, feat):
-        if not self._allow_zero_in_degree and bool((graph.in_degrees() == 0).any()):
+        if not self._allow_zero_in_degree and _has_zero_in_degree(graph):
             raise RuntimeError("There are 0-in-degree nodes in the graph; add self loops first")
         if (self._fused and self._norm == "both" and self.weight is not None and self._in_feats > self._out_feats
                 and feat.dim() == 2):
@@ -229,7 +238,7 @@ class QGATConv(nn.Module):
             nn.init.xavier_normal_(self.res_fc.weight, gain=gain)
 
     def forward(self, graph, feat, get_attention=False):
-        if not self._allow_zero_in_degree and bool((graph.in_degrees() == 0).any()):
+        if not self._allow_zero_in_degree and _has_zero_in_degree(graph):
             raise RuntimeError("There are 0-in-degree nodes in the graph.")
         prefix = feat.shape[:-1]
         h = self.feat_drop(feat).contiguous()
