@@ -178,6 +178,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL collectives are captured into the step's CUDA graph: the process group's watchdog must not poll
+        # events of a capturing stream
+        os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")
         dist.init_process_group("nccl", device_id=dev)
 
     name = args.workload
@@ -193,7 +196,7 @@ def run_ours(args):
         lo, hi = 0, n
     else:
         from tango_b200.dist import DistGCN, DistGraph, allreduce_grads
-        dg = DistGraph(g, rank, world)
+        dg = DistGraph(g, rank, world, scale_mode=args.scale_mode)
         del g
         torch.cuda.empty_cache()
         model = DistGCN(dg, in_feats, hidden, classes, 1).to(dev)
@@ -226,7 +229,7 @@ def run_ours(args):
         torch.cuda.synchronize()
         K.launch_counter[0] = 0
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             static_loss = step(d_feats, d_labels)
         launches_captured = K.launch_counter[0]
 
@@ -324,7 +327,7 @@ def run_ours(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "s8", "data": "synthetic",
             "config": {"workload": name, "nodes": n, "edges": n_edges, "layers": f"{in_feats}-{hidden}-{classes}",
-                       "rounding": args.rounding, "parallelism": f"row-partition x{world}",
+                       "rounding": args.rounding, "parallelism": f"row-partition x{world}", "scale_mode": args.scale_mode if world > 1 else "single",
                        "cuda_graph": graph is not None,
                        "timing": "CUDA events, inputs larger than L2 (no flush)"},
             "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": (h_feats.numel() * 4 + h_labels.numel() * 8),
@@ -338,7 +341,11 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_base
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # the captured graph holds NCCL work; leave without tearing the communicator down under it
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def _cpu_baseline(name, g, model):
@@ -413,6 +420,8 @@ def main():
     ap.add_argument("--workload", default="gcn_c5", choices=sorted(WORKLOADS))
     ap.add_argument("--rounding", default="reference", choices=["reference", "nearest", "stochastic"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scale-mode", default="global", choices=["global", "shard"],
+                    help="multi-GPU: one quantisation scale agreed by all ranks, or one per shard")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of a CUDA graph")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, gemm) and exit")
     args = ap.parse_args()

@@ -20,7 +20,8 @@ from . import config
 from .graph import Graph, RowPartition, balanced_bounds, uniform_bounds
 
 
-def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_rows: int, group=None):
+def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_rows: int, group=None,
+                         gather_scales: bool = True):
     """Gathers every rank's int8 shard ([<= shard_rows, ld], same ld everywhere) and scale.
 
     Returns (q_all [world * shard_rows, ld], scales [world]); rank k's rows start at k * shard_rows.  Works on any
@@ -34,6 +35,8 @@ def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_row
         send = torch.zeros((shard_rows, ld), dtype=torch.int8, device=q_local.device)
         send[:q_local.shape[0]] = q_local
     dist.all_gather_into_tensor(q_all, send, group=group)
+    if not gather_scales:
+        return q_all, s_local
     scales = torch.empty(world, dtype=torch.float32, device=s_local.device)
     dist.all_gather_into_tensor(scales, s_local.reshape(1).contiguous(), group=group)
     return q_all, scales
@@ -42,13 +45,17 @@ def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_row
 class DistGraph:
     """Rank-local view of a graph that every rank holds (or can rebuild from the same seed)."""
 
-    def __init__(self, g: Graph, rank: int, world: int, balance: str = "nnz"):
-        """balance='nnz': contiguous blocks with equal in-degree + out-degree (forward and backward aggregation cost);
-        balance='rows': equal row counts."""
+    def __init__(self, g: Graph, rank: int, world: int, balance: str = "nnz", scale_mode: str = "global"):
+        """balance='nnz': contiguous blocks of equal cost (in-degree + out-degree + a per-row constant, i.e. forward
+        plus backward aggregation work); balance='rows': equal row counts.
+        scale_mode='global': the ranks agree on one quantisation scale per aggregated tensor (all-reduce max of one
+        float), which makes the result bit-identical to the single-GPU run; scale_mode='shard': every shard keeps its
+        own scale and the aggregation kernel applies the scale of the shard a neighbour came from."""
+        assert scale_mode in ("global", "shard")
         n = g.num_nodes()
-        self.rank, self.world, self.n_total = rank, world, n
+        self.rank, self.world, self.n_total, self.scale_mode = rank, world, n, scale_mode
         csc, csr = g.adj_csc, g.adj_csr
-        bounds = (balanced_bounds(g.in_degrees() + g.out_degrees(), world) if balance == "nnz"
+        bounds = (balanced_bounds(g.in_degrees() + g.out_degrees() + 64, world) if balance == "nnz"
                   else uniform_bounds(n, world))
         self.bounds = bounds
         self.fwd = RowPartition(csc[0], csc[1], None, n, rank, world, bounds)
@@ -90,14 +97,22 @@ def _aggregate(dg: DistGraph, part: RowPartition, x_local: torch.Tensor, scale_l
     x_local = x_local.contiguous()
     if scale_local is None:
         scale_local = K._get_scale(x_local, in_row_scale)
+    shared = dg.scale_mode == "global"
+    if shared:
+        scale_local = scale_local.clone()
+        dist.all_reduce(scale_local, op=dist.ReduceOp.MAX)
     q = K.alloc_int8(x_local.shape, x_local.device)
     call = K.next_call() if mode == K.ROUND_STOCHASTIC else 0
     K._quantize_into(q, x_local, scale_local, mode, seed, call, in_row_scale)
-    q_all, scales = all_gather_quantized(_padded_storage(q), scale_local, dg.shard_rows)
+    q_all, scales = all_gather_quantized(_padded_storage(q), scale_local, dg.shard_rows, gather_scales=not shared)
     f = x_local.shape[1]
     out = torch.empty((dg.n_local, f), dtype=torch.float32, device=x_local.device)
-    K._csr_spmm(out, part.indptr, part.indices, q_all[:, :f] if q_all.shape[1] != f else q_all, scales,
-                part.schedule, dg.world, row_scale, bias, relu)
+    feats = q_all[:, :f] if q_all.shape[1] != f else q_all
+    if shared:
+        K._csr_spmm(out, part.indptr_flat, part.indices, feats, scale_local, part.schedule_flat, 1, row_scale, bias,
+                    relu)
+    else:
+        K._csr_spmm(out, part.indptr, part.indices, feats, scales, part.schedule, dg.world, row_scale, bias, relu)
     return out
 
 
@@ -115,6 +130,8 @@ class _dist_gcn_conv_fused(Function):
             K.next_call()
         X = X.contiguous()
         sX, sW = K._get_scale(X, dg.out_norm), K._get_scale(W)
+        if dg.scale_mode == "global":
+            dist.all_reduce(sX, op=dist.ReduceOp.MAX)
         Xq, Wq = K.alloc_int8(X.shape, X.device), K.alloc_int8(W.shape, X.device)
         K._quantize_into(Xq, X, sX, mode_f, seed, call, dg.out_norm)
         K._quantize_into(Wq, W.contiguous(), sW, mode_f, seed, call + 1)
@@ -136,7 +153,10 @@ class _dist_gcn_conv_fused(Function):
         g1 = torch.where(out > 0, d_out, torch.zeros((), device=d_out.device)) if ctx.relu else d_out.contiguous()
         db = g1.sum(0) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
         dH = _aggregate(dg, dg.bwd, g1, None, None, None, False, in_row_scale=dg.in_norm)
-        dHq, sdH = K.quantize(dH, mode=mode_q, seed=seed)
+        sdH = K._get_scale(dH)
+        if dg.scale_mode == "global":
+            dist.all_reduce(sdH, op=dist.ReduceOp.MAX)
+        dHq, _ = K.quantize(dH, sdH, mode=mode_q, seed=seed)
         dX, dW = K.QGEMM_backward(dHq, Xq, Wq, sdH, sX, sW, ctx.needs_input_grad[1], ctx.needs_input_grad[2])
         if dX is not None:
             dX = dX * dg.out_norm.unsqueeze(1)

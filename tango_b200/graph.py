@@ -295,3 +295,6 @@ class RowPartition:
         seg = torch.searchsorted(key, seg_bounds)
         self.indptr = torch.cat([seg, torch.tensor([hi - lo], device=dev)]).to(torch.int32)
         self.schedule = SpmmSchedule(self.indptr, nseg=world)
+        # the same rows without the per-shard cut, for aggregation with one scale shared by all ranks
+        self.indptr_flat = self.indptr[::world].contiguous()
+        self.schedule_flat = SpmmSchedule(self.indptr_flat, nseg=1)
