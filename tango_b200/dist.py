@@ -46,7 +46,7 @@ class DistGraph:
     """Rank-local view of a graph that every rank holds (or can rebuild from the same seed)."""
 
     def __init__(self, g: Graph, rank: int, world: int, balance: str = "nnz", scale_mode: str = "global"):
-        """balance='nnz': contiguous blocks of equal cost (in-degree + out-degree + a per-row constant, i.e. forward
+        """balance='nnz': contiguous blocks of equal cost (in-degree + out-degree + 300 per row for the dense per-row work, i.e. forward
         plus backward aggregation work); balance='rows': equal row counts.
         scale_mode='global': the ranks agree on one quantisation scale per aggregated tensor (all-reduce max of one
         float), which makes the result bit-identical to the single-GPU run; scale_mode='shard': every shard keeps its
@@ -55,7 +55,7 @@ class DistGraph:
         n = g.num_nodes()
         self.rank, self.world, self.n_total, self.scale_mode = rank, world, n, scale_mode
         csc, csr = g.adj_csc, g.adj_csr
-        bounds = (balanced_bounds(g.in_degrees() + g.out_degrees() + 64, world) if balance == "nnz"
+        bounds = (balanced_bounds(g.in_degrees() + g.out_degrees() + 300, world) if balance == "nnz"
                   else uniform_bounds(n, world))
         self.bounds = bounds
         self.fwd = RowPartition(csc[0], csc[1], None, n, rank, world, bounds)
