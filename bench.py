@@ -91,15 +91,15 @@ def build_graph(name: str, device):
     return rmat_graph(n, e, seed, device=device)
 
 
-def make_inputs(name: str, lo: int, hi: int, pin: bool):
-    """Seeded features / labels for node rows [lo, hi) on the host (generated per row block so that a partition sees
-    the same values as the single-GPU run)."""
+def make_inputs(name: str, rows, pin: bool):
+    """Seeded features / labels of the node rows selected by `rows` (a slice or an index tensor) on the host, so that
+    a partition sees the same values as the single-GPU run."""
     import torch
     n, _, in_feats, _, classes, _ = WORKLOADS[name]
     gen = torch.Generator().manual_seed(3)
-    feats = torch.randn((n, in_feats), generator=gen)[lo:hi].contiguous()
+    feats = torch.randn((n, in_feats), generator=gen)[rows].contiguous()
     gen = torch.Generator().manual_seed(5)
-    labels = torch.randint(0, classes, (n,), generator=gen)[lo:hi].contiguous()
+    labels = torch.randint(0, classes, (n,), generator=gen)[rows].contiguous()
     if pin:
         feats, labels = feats.pin_memory(), labels.pin_memory()
     return feats, labels
@@ -132,7 +132,7 @@ def run_reference(args):
     w2 = torch.nn.init.xavier_uniform_(torch.empty(classes, hidden))
     model = B.GCNfp32(a, a_t, outd, ind, [w1, w2], [torch.zeros(hidden), torch.zeros(classes)])
     opt = torch.optim.Adam(model.parameters(), lr=1e-2, weight_decay=5e-4)
-    feats, labels = make_inputs(name, 0, n, False)
+    feats, labels = make_inputs(name, slice(0, n), False)
 
     def step():
         opt.zero_grad(set_to_none=True)
@@ -193,16 +193,16 @@ def run_ours(args):
         from tango_b200.gnn import GCN
         T.graph_preprocess(g)
         model = GCN(g, in_feats, hidden, classes, 1).to(dev)
-        lo, hi = 0, n
+        rows = slice(0, n)
     else:
         from tango_b200.dist import DistGCN, DistGraph, allreduce_grads
-        dg = DistGraph(g, rank, world, scale_mode=args.scale_mode)
+        dg = DistGraph(g, rank, world, balance=args.balance, scale_mode=args.scale_mode)
         del g
         torch.cuda.empty_cache()
         model = DistGCN(dg, in_feats, hidden, classes, 1).to(dev)
-        lo, hi = dg.r0, dg.r1
+        rows = dg.local_ids.cpu()
     opt = torch.optim.Adam(model.parameters(), lr=1e-2, weight_decay=5e-4, capturable=not args.no_graph)
-    h_feats, h_labels = make_inputs(name, lo, hi, True)
+    h_feats, h_labels = make_inputs(name, rows, True)
     d_feats, d_labels = h_feats.to(dev), h_labels.to(dev)
 
     def step(feats, labels):
@@ -327,7 +327,7 @@ def run_ours(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "s8", "data": "synthetic",
             "config": {"workload": name, "nodes": n, "edges": n_edges, "layers": f"{in_feats}-{hidden}-{classes}",
-                       "rounding": args.rounding, "parallelism": f"row-partition x{world}", "scale_mode": args.scale_mode if world > 1 else "single",
+                       "rounding": args.rounding, "parallelism": f"row-partition x{world}", "scale_mode": args.scale_mode if world > 1 else "single", "balance": args.balance if world > 1 else "single",
                        "cuda_graph": graph is not None,
                        "timing": "CUDA events, inputs larger than L2 (no flush)"},
             "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": (h_feats.numel() * 4 + h_labels.numel() * 8),
@@ -363,7 +363,7 @@ def _cpu_baseline(name, g, model):
     bs = [l.bias for l in model.layers]
     ref = B.GCNfp32(a, a_t, g.out_degrees(), g.in_degrees(), ws, bs)
     opt = torch.optim.Adam(ref.parameters(), lr=1e-2, weight_decay=5e-4)
-    feats, labels = make_inputs(name, 0, n, False)
+    feats, labels = make_inputs(name, slice(0, n), False)
     times = []
     for _ in range(2):
         t0 = time.perf_counter()
@@ -422,6 +422,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale-mode", default="global", choices=["global", "shard"],
                     help="multi-GPU: one quantisation scale agreed by all ranks, or one per shard")
+    ap.add_argument("--balance", default="cyclic", choices=["cyclic", "nnz", "rows"], help="multi-GPU node placement")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of a CUDA graph")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, gemm) and exit")
     args = ap.parse_args()

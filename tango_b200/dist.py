@@ -45,9 +45,10 @@ def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_row
 class DistGraph:
     """Rank-local view of a graph that every rank holds (or can rebuild from the same seed)."""
 
-    def __init__(self, g: Graph, rank: int, world: int, balance: str = "nnz", scale_mode: str = "global"):
-        """balance='nnz': contiguous blocks of equal cost (in-degree + out-degree + 300 per row for the dense per-row work, i.e. forward
-        plus backward aggregation work); balance='rows': equal row counts.
+    def __init__(self, g: Graph, rank: int, world: int, balance: str = "cyclic", scale_mode: str = "global"):
+        """balance='cyclic': node v lives on rank v % world (equal rows, nearly equal edges, no padding);
+        balance='nnz': contiguous blocks of equal cost (in-degree + out-degree + 300 per row for the dense per-row
+        work); balance='rows': contiguous blocks of equal row counts.
         scale_mode='global': the ranks agree on one quantisation scale per aggregated tensor (all-reduce max of one
         float), which makes the result bit-identical to the single-GPU run; scale_mode='shard': every shard keeps its
         own scale and the aggregation kernel applies the scale of the shard a neighbour came from."""
@@ -55,14 +56,20 @@ class DistGraph:
         n = g.num_nodes()
         self.rank, self.world, self.n_total, self.scale_mode = rank, world, n, scale_mode
         csc, csr = g.adj_csc, g.adj_csr
-        bounds = (balanced_bounds(g.in_degrees() + g.out_degrees() + 300, world) if balance == "nnz"
-                  else uniform_bounds(n, world))
+        assert balance in ("cyclic", "nnz", "rows")
+        layout = "cyclic" if balance == "cyclic" else "block"
+        bounds = None
+        if balance == "nnz":
+            bounds = balanced_bounds(g.in_degrees() + g.out_degrees() + 300, world)
+        elif balance == "rows":
+            bounds = uniform_bounds(n, world)
         self.bounds = bounds
-        self.fwd = RowPartition(csc[0], csc[1], None, n, rank, world, bounds)
-        self.bwd = RowPartition(csr[0], csr[1], None, n, rank, world, bounds)
-        self.shard_rows, self.r0, self.r1, self.n_local = self.fwd.shard_rows, self.fwd.r0, self.fwd.r1, self.fwd.n_local
-        self.in_norm = g.in_degrees()[self.r0:self.r1].float().clamp(min=1).pow(-0.5).contiguous()
-        self.out_norm = g.out_degrees()[self.r0:self.r1].float().clamp(min=1).pow(-0.5).contiguous()
+        self.fwd = RowPartition(csc[0], csc[1], None, n, rank, world, bounds, layout)
+        self.bwd = RowPartition(csr[0], csr[1], None, n, rank, world, bounds, layout)
+        self.shard_rows, self.n_local, self.local_ids = self.fwd.shard_rows, self.fwd.n_local, self.fwd.local_ids
+        self.r0, self.r1 = self.fwd.r0, self.fwd.r1
+        self.in_norm = g.in_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
+        self.out_norm = g.out_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
 
 
 def _padded_storage(q: torch.Tensor) -> torch.Tensor:

@@ -264,36 +264,61 @@ def uniform_bounds(n_nodes: int, world: int):
 
 
 class RowPartition:
-    """Rank `rank`'s block of rows [r0, r1) of a CSR/CSC.  Column ids are rewritten for the all-gathered feature
-    buffer, in which rank k's rows start at k * shard_rows (shard_rows = the largest block; shorter blocks are
-    padded).  `indptr` has n_local * world + 1 entries: row v owns `world` consecutive segments, segment k holding the
-    columns that live on rank k (columns are sorted, so segments are contiguous)."""
+    """The rows of a CSR/CSC that one rank owns, with column ids rewritten for the all-gathered feature buffer, in
+    which rank k's rows start at k * shard_rows (shard_rows = the largest shard; shorter shards are padded).
+
+    layout='block' : rank k owns the contiguous rows [bounds[k], bounds[k+1]);
+    layout='cyclic': rank k owns rows k, k + world, k + 2*world, ... -- equal row counts *and*, because the heavy rows
+                     of a power-law graph are dealt round-robin, nearly equal edge counts, with no padding.
+    `local_ids` lists the global ids of the owned rows in local order.  `indptr` has n_local * world + 1 entries: row v
+    owns `world` consecutive segments, segment k holding the columns that live on rank k; `indptr_flat` is the same
+    structure without that cut (n_local + 1 entries)."""
 
     def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, edge_ids: Optional[torch.Tensor], n_nodes: int,
-                 rank: int, world: int, bounds=None):
-        self.world, self.rank = world, rank
-        self.bounds = list(bounds) if bounds is not None else uniform_bounds(n_nodes, world)
-        assert len(self.bounds) == world + 1 and self.bounds[0] == 0 and self.bounds[-1] == n_nodes
-        self.shard_rows = max(1, max(self.bounds[k + 1] - self.bounds[k] for k in range(world)))
-        self.r0, self.r1 = self.bounds[rank], self.bounds[rank + 1]
-        self.n_local = self.r1 - self.r0
+                 rank: int, world: int, bounds=None, layout: str = "block"):
+        assert layout in ("block", "cyclic")
+        self.world, self.rank, self.layout = world, rank, layout
         dev = indptr.device
         ip = indptr.long()
-        lo, hi = int(ip[self.r0]), int(ip[self.r1])
-        cols = indices[lo:hi].long()
-        bt = torch.tensor(self.bounds, dtype=torch.int64, device=dev)
-        owner = torch.searchsorted(bt, cols, right=True) - 1            # rank that owns each column
-        remapped = owner * self.shard_rows + (cols - bt[owner])          # row in the gathered buffer (monotone in col)
-        self.indices = remapped.to(torch.int32).contiguous()
-        self.edge_ids = None if edge_ids is None else edge_ids[lo:hi].contiguous()
-        rows = torch.repeat_interleave(torch.arange(self.n_local, device=dev),
-                                       (ip[self.r0 + 1:self.r1 + 1] - ip[self.r0:self.r1]))
+        if layout == "block":
+            self.bounds = list(bounds) if bounds is not None else uniform_bounds(n_nodes, world)
+            assert len(self.bounds) == world + 1 and self.bounds[0] == 0 and self.bounds[-1] == n_nodes
+            self.shard_rows = max(1, max(self.bounds[k + 1] - self.bounds[k] for k in range(world)))
+            self.r0, self.r1 = self.bounds[rank], self.bounds[rank + 1]
+            self.local_ids = torch.arange(self.r0, self.r1, device=dev)
+            bt = torch.tensor(self.bounds, dtype=torch.int64, device=dev)
+
+            def place(cols):
+                owner = torch.searchsorted(bt, cols, right=True) - 1
+                return owner * self.shard_rows + (cols - bt[owner])
+        else:
+            self.bounds = None
+            self.shard_rows = max(1, (n_nodes + world - 1) // world)
+            self.local_ids = torch.arange(rank, n_nodes, world, device=dev)
+            self.r0, self.r1 = None, None
+
+            def place(cols):
+                return (cols % world) * self.shard_rows + cols // world
+        self.n_local = int(self.local_ids.numel())
+        beg, end = ip[self.local_ids], ip[self.local_ids + 1]
+        lens = end - beg
+        total = int(lens.sum())
+        first = torch.cumsum(lens, 0) - lens
+        rows = torch.repeat_interleave(torch.arange(self.n_local, device=dev), lens)
+        pos = torch.arange(total, device=dev) - first[rows] + beg[rows]          # slots of the owned rows, row by row
+        remapped = place(indices[pos].long())
         span = self.shard_rows * world
         key = rows * span + remapped
+        if layout == "cyclic":                      # the rewritten columns are no longer sorted inside a row
+            key, order = torch.sort(key)
+            pos = pos[order]
+            remapped = key - rows * span
+        self.indices = remapped.to(torch.int32).contiguous()
+        self.edge_ids = None if edge_ids is None else edge_ids[pos].contiguous()
         seg_bounds = (torch.arange(self.n_local, device=dev)[:, None] * span
                       + torch.arange(world, device=dev)[None, :] * self.shard_rows).flatten()
         seg = torch.searchsorted(key, seg_bounds)
-        self.indptr = torch.cat([seg, torch.tensor([hi - lo], device=dev)]).to(torch.int32)
+        self.indptr = torch.cat([seg, torch.tensor([total], device=dev)]).to(torch.int32)
         self.schedule = SpmmSchedule(self.indptr, nseg=world)
         # the same rows without the per-shard cut, for aggregation with one scale shared by all ranks
         self.indptr_flat = self.indptr[::world].contiguous()

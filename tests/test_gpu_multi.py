@@ -31,21 +31,22 @@ def _worker(rank, world, port, out_dir, balance, scale_mode):
     torch.manual_seed(4)
     model = DistGCN(dg, 100, 32, 7, 1).to(dev)
     gen = torch.Generator().manual_seed(9)
-    x = torch.randn((n, 100), generator=gen)[dg.r0:dg.r1].to(dev)
-    y = torch.randint(0, 7, (n,), generator=gen)[dg.r0:dg.r1].to(dev)
+    x = torch.randn((n, 100), generator=gen)[dg.local_ids.cpu()].to(dev)
+    y = torch.randint(0, 7, (n,), generator=gen)[dg.local_ids.cpu()].to(dev)
     logits = model(x)
     loss = F.cross_entropy(logits, y, reduction="sum") / n
     loss.backward()
     allreduce_grads(model)
     lt = loss.detach().clone()
     dist.all_reduce(lt)
-    torch.save({"logits": logits.detach().cpu(), "r0": dg.r0, "loss": lt.cpu(),
+    torch.save({"logits": logits.detach().cpu(), "ids": dg.local_ids.cpu(), "loss": lt.cpu(),
                 "grads": [p.grad.cpu() for p in model.parameters()]}, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("balance,scale_mode", [("nnz", "global"), ("rows", "shard"), ("nnz", "shard")])
+@pytest.mark.parametrize("balance,scale_mode", [("cyclic", "global"), ("nnz", "global"), ("rows", "shard"),
+                                                ("cyclic", "shard")])
 def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -67,8 +68,10 @@ def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode):
     loss = F.cross_entropy(logits, y)
     loss.backward()
     parts = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
-    got = torch.cat([p["logits"] for p in sorted(parts, key=lambda p: p["r0"])])
     ref = logits.detach().cpu()
+    got = torch.empty_like(ref)
+    for p in parts:
+        got[p["ids"]] = p["logits"]
     if scale_mode == "global":
         # one scale agreed by all ranks: every int8 tensor, hence every logit, equals the single-GPU run's
         assert torch.equal(got, ref)

@@ -164,3 +164,38 @@ def test_two_rank_gather_and_aggregate(tmp_path):
     # and the per-shard-scale result stays within the stated tolerance of the fp32 aggregation
     a = np.zeros((n, f)); rows = np.repeat(np.arange(n), np.diff(indptr)); np.add.at(a, rows, x[indices])
     assert np.abs(got - a).max() / np.abs(a).max() < 1e-2
+
+
+@pytest.mark.parametrize("layout", ["block", "cyclic"])
+def test_partition_layouts_reproduce_the_unpartitioned_aggregation(layout):
+    """Every rank aggregates its rows from a buffer laid out like the all-gather result (rank k's rows at
+    k * shard_rows); together they must give the plain aggregation, for contiguous and for round-robin placement."""
+    from tango_b200.graph import balanced_bounds
+    n, world, f = 1003, 4, 8
+    g = rmat_graph(n, 20000, 4)
+    indptr, indices, eids = g.adj_csc
+    nq = np.random.default_rng(0).integers(-127, 128, (n, f), dtype=np.int8)
+    ref = O.spmm_copy_u(indptr.numpy().astype(np.int64), indices.numpy().astype(np.int64), nq, np.float32(0.5))
+    bounds = balanced_bounds(g.in_degrees() + g.out_degrees() + 10, world) if layout == "block" else None
+    parts = [RowPartition(indptr, indices, eids, n, r, world, bounds, layout) for r in range(world)]
+    shard = parts[0].shard_rows
+    gathered = np.zeros((world * shard, f), dtype=np.int8)
+    for p in parts:
+        ids = p.local_ids.numpy()
+        gathered[p.rank * shard:p.rank * shard + len(ids)] = nq[ids]
+    seen = 0
+    for p in parts:
+        out = O.spmm_copy_u(p.indptr_flat.numpy().astype(np.int64), p.indices.numpy().astype(np.int64), gathered,
+                            np.float32(0.5))
+        np.testing.assert_array_equal(out, ref[p.local_ids.numpy()])
+        ip = p.indptr.long()
+        for v in (0, p.n_local - 1):                       # segment k only holds columns stored in rank k's slice
+            for k in range(world):
+                seg = p.indices[ip[v * world + k]:ip[v * world + k + 1]]
+                assert bool(((seg // shard) == k).all())
+        src, dst = g.coo                                   # edge ids follow their slots through the re-ordering
+        assert torch.equal(dst[p.edge_ids.long()].long(),
+                           p.local_ids[torch.repeat_interleave(torch.arange(p.n_local),
+                                                               (p.indptr_flat[1:] - p.indptr_flat[:-1]).long())])
+        seen += p.indices.numel()
+    assert seen == g.num_edges()
