@@ -422,7 +422,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale-mode", default="global", choices=["global", "shard"],
                     help="multi-GPU: one quantisation scale agreed by all ranks, or one per shard")
-    ap.add_argument("--balance", default="cyclic", choices=["cyclic", "nnz", "rows"], help="multi-GPU node placement")
+    ap.add_argument("--balance", default="dealt", choices=["dealt", "cyclic", "nnz", "rows"], help="multi-GPU node placement")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of a CUDA graph")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, gemm) and exit")
     args = ap.parse_args()

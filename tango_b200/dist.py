@@ -45,8 +45,10 @@ def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_row
 class DistGraph:
     """Rank-local view of a graph that every rank holds (or can rebuild from the same seed)."""
 
-    def __init__(self, g: Graph, rank: int, world: int, balance: str = "cyclic", scale_mode: str = "global"):
-        """balance='cyclic': node v lives on rank v % world (equal rows, nearly equal edges, no padding);
+    def __init__(self, g: Graph, rank: int, world: int, balance: str = "dealt", scale_mode: str = "global"):
+        """balance='dealt': nodes sorted by in-degree + out-degree are dealt round-robin to the ranks (equal rows,
+        nearly equal edges even on power-law graphs, no padding of the gathered buffer);
+        balance='cyclic': node v lives on rank v % world;
         balance='nnz': contiguous blocks of equal cost (in-degree + out-degree + 300 per row for the dense per-row
         work); balance='rows': contiguous blocks of equal row counts.
         scale_mode='global': the ranks agree on one quantisation scale per aggregated tensor (all-reduce max of one
@@ -56,16 +58,18 @@ class DistGraph:
         n = g.num_nodes()
         self.rank, self.world, self.n_total, self.scale_mode = rank, world, n, scale_mode
         csc, csr = g.adj_csc, g.adj_csr
-        assert balance in ("cyclic", "nnz", "rows")
-        layout = "cyclic" if balance == "cyclic" else "block"
-        bounds = None
+        assert balance in ("dealt", "cyclic", "nnz", "rows")
+        layout = balance if balance in ("cyclic", "dealt") else "block"
+        bounds, order = None, None
+        if balance == "dealt":
+            order = torch.argsort(g.in_degrees() + g.out_degrees(), descending=True, stable=True)
         if balance == "nnz":
             bounds = balanced_bounds(g.in_degrees() + g.out_degrees() + 300, world)
         elif balance == "rows":
             bounds = uniform_bounds(n, world)
         self.bounds = bounds
-        self.fwd = RowPartition(csc[0], csc[1], None, n, rank, world, bounds, layout)
-        self.bwd = RowPartition(csr[0], csr[1], None, n, rank, world, bounds, layout)
+        self.fwd = RowPartition(csc[0], csc[1], None, n, rank, world, bounds, layout, order)
+        self.bwd = RowPartition(csr[0], csr[1], None, n, rank, world, bounds, layout, order)
         self.shard_rows, self.n_local, self.local_ids = self.fwd.shard_rows, self.fwd.n_local, self.fwd.local_ids
         self.r0, self.r1 = self.fwd.r0, self.fwd.r1
         self.in_norm = g.in_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()

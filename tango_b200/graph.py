@@ -268,15 +268,17 @@ class RowPartition:
     which rank k's rows start at k * shard_rows (shard_rows = the largest shard; shorter shards are padded).
 
     layout='block' : rank k owns the contiguous rows [bounds[k], bounds[k+1]);
-    layout='cyclic': rank k owns rows k, k + world, k + 2*world, ... -- equal row counts *and*, because the heavy rows
-                     of a power-law graph are dealt round-robin, nearly equal edge counts, with no padding.
+    layout='cyclic': rank k owns rows k, k + world, k + 2*world, ... (equal row counts, no padding);
+    layout='dealt' : the rows of `order` (e.g. nodes sorted by degree) are dealt round-robin, order[i] going to rank
+                     i % world at local position i // world -- equal row counts and, for a degree-sorted order,
+                     nearly equal edge counts even on power-law graphs.
     `local_ids` lists the global ids of the owned rows in local order.  `indptr` has n_local * world + 1 entries: row v
     owns `world` consecutive segments, segment k holding the columns that live on rank k; `indptr_flat` is the same
     structure without that cut (n_local + 1 entries)."""
 
     def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, edge_ids: Optional[torch.Tensor], n_nodes: int,
-                 rank: int, world: int, bounds=None, layout: str = "block"):
-        assert layout in ("block", "cyclic")
+                 rank: int, world: int, bounds=None, layout: str = "block", order: Optional[torch.Tensor] = None):
+        assert layout in ("block", "cyclic", "dealt")
         self.world, self.rank, self.layout = world, rank, layout
         dev = indptr.device
         ip = indptr.long()
@@ -291,7 +293,7 @@ class RowPartition:
             def place(cols):
                 owner = torch.searchsorted(bt, cols, right=True) - 1
                 return owner * self.shard_rows + (cols - bt[owner])
-        else:
+        elif layout == "cyclic":
             self.bounds = None
             self.shard_rows = max(1, (n_nodes + world - 1) // world)
             self.local_ids = torch.arange(rank, n_nodes, world, device=dev)
@@ -299,6 +301,19 @@ class RowPartition:
 
             def place(cols):
                 return (cols % world) * self.shard_rows + cols // world
+        else:
+            assert order is not None and order.numel() == n_nodes
+            self.bounds = None
+            self.shard_rows = max(1, (n_nodes + world - 1) // world)
+            order = order.long()
+            self.local_ids = order[rank::world].contiguous()
+            self.r0, self.r1 = None, None
+            slot = torch.empty(n_nodes, dtype=torch.int64, device=dev)      # node -> row in the gathered buffer
+            i = torch.arange(n_nodes, device=dev)
+            slot[order] = (i % world) * self.shard_rows + i // world
+
+            def place(cols):
+                return slot[cols]
         self.n_local = int(self.local_ids.numel())
         beg, end = ip[self.local_ids], ip[self.local_ids + 1]
         lens = end - beg
@@ -309,7 +324,7 @@ class RowPartition:
         remapped = place(indices[pos].long())
         span = self.shard_rows * world
         key = rows * span + remapped
-        if layout == "cyclic":                      # the rewritten columns are no longer sorted inside a row
+        if layout != "block":                       # the rewritten columns are no longer sorted inside a row
             key, order = torch.sort(key)
             pos = pos[order]
             remapped = key - rows * span

@@ -45,8 +45,8 @@ def _worker(rank, world, port, out_dir, balance, scale_mode):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("balance,scale_mode", [("cyclic", "global"), ("nnz", "global"), ("rows", "shard"),
-                                                ("cyclic", "shard")])
+@pytest.mark.parametrize("balance,scale_mode", [("dealt", "global"), ("nnz", "global"), ("rows", "shard"),
+                                                ("dealt", "shard"), ("cyclic", "global")])
 def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")

@@ -166,7 +166,7 @@ def test_two_rank_gather_and_aggregate(tmp_path):
     assert np.abs(got - a).max() / np.abs(a).max() < 1e-2
 
 
-@pytest.mark.parametrize("layout", ["block", "cyclic"])
+@pytest.mark.parametrize("layout", ["block", "cyclic", "dealt"])
 def test_partition_layouts_reproduce_the_unpartitioned_aggregation(layout):
     """Every rank aggregates its rows from a buffer laid out like the all-gather result (rank k's rows at
     k * shard_rows); together they must give the plain aggregation, for contiguous and for round-robin placement."""
@@ -177,7 +177,11 @@ def test_partition_layouts_reproduce_the_unpartitioned_aggregation(layout):
     nq = np.random.default_rng(0).integers(-127, 128, (n, f), dtype=np.int8)
     ref = O.spmm_copy_u(indptr.numpy().astype(np.int64), indices.numpy().astype(np.int64), nq, np.float32(0.5))
     bounds = balanced_bounds(g.in_degrees() + g.out_degrees() + 10, world) if layout == "block" else None
-    parts = [RowPartition(indptr, indices, eids, n, r, world, bounds, layout) for r in range(world)]
+    order = torch.argsort(g.in_degrees() + g.out_degrees(), descending=True, stable=True) if layout == "dealt" else None
+    parts = [RowPartition(indptr, indices, eids, n, r, world, bounds, layout, order) for r in range(world)]
+    if layout == "dealt":
+        nnz = [p.indices.numel() for p in parts]
+        assert max(nnz) < 1.1 * min(nnz)
     shard = parts[0].shard_rows
     gathered = np.zeros((world * shard, f), dtype=np.int8)
     for p in parts:
