@@ -134,7 +134,7 @@ int64_t tango_qgemm_dw_noalloc_max_elems(void);
 /* Optional schedule for rows too long for one warp.  A row whose degree exceeds `split_threshold` is cut into
  * `n_units` units (vrow, begin, end, slot) stored as int32 quadruples; each unit adds its partial sums into
  * int32 scratch `ws` ([n_heavy * nseg, ws_ld]) and the rows listed in `heavy_rows` ([n_heavy]) are finished by a
- * second kernel.  With n_units == 0 every row is handled by one warp. */
+ * second kernel.  With n_units == 0 every row is handled by one warp (the units/heavy_rows/ws fields are ignored). */
 typedef struct tango_spmm_plan {
     const int32_t *units;      /* [n_units, 4] */
     int64_t n_units;
@@ -143,6 +143,8 @@ typedef struct tango_spmm_plan {
     int32_t *ws;               /* [n_heavy * nseg, ws_ld] int32 scratch */
     int64_t ws_ld;             /* >= round_up(F, 16) */
     int32_t split_threshold;
+    const int32_t *row_order;  /* optional [n_rows]: warp w works on row row_order[w] (e.g. rows sorted by degree, so
+                                  that the warps of a CTA finish together); NULL = natural order */
 } tango_spmm_plan;
 
 /* out[v,:] = sum_k scales[k] * float(sum_{j in segment k of row v} Nq[indices[j], :]) for v < n_rows.

@@ -27,6 +27,7 @@ class SpmmPlan(Structure):
         ("ws", c_void_p),
         ("ws_ld", c_int64),
         ("split_threshold", c_int32),
+        ("row_order", c_void_p),
     ]
 
 

@@ -36,6 +36,7 @@ struct SpmmArgs {
     int32_t *ws;
     int64_t ws_ld;
     int split_threshold;
+    const int32_t *row_order;
     int G;  // lanes per neighbour (power of two)
 };
 
@@ -228,7 +229,8 @@ __global__ void __launch_bounds__(SPMM_THREADS, SPMM_MINB) spmm_kernel(const Spm
             }
         }
     } else if (w - a.n_units < a.n_rows) {
-        const int64_t row = w - a.n_units;
+        int64_t row = w - a.n_units;
+        if (a.row_order) row = __ldg(a.row_order + row);
         const int32_t *ip = a.indptr + row * a.nseg;
         const int row_beg = __ldg(ip), row_end = __ldg(ip + a.nseg);
         if (a.n_heavy > 0 && row_end - row_beg > a.split_threshold) return;  // finished by spmm_finalize_kernel
@@ -308,6 +310,7 @@ static int pow2_ceil(int x) {
 template <int MODE>
 static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t stream) {
     if (a.n_rows == 0 || a.f == 0) return TANGO_OK;
+    if (plan) a.row_order = plan->row_order;
     if (plan && plan->n_units > 0) {
         if (!plan->units || !plan->heavy_rows || !plan->ws || plan->ws_ld < a.f || plan->n_heavy <= 0)
             return TANGO_EINVAL;

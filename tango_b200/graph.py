@@ -221,6 +221,9 @@ class SpmmSchedule:
         n_rows = (indptr.numel() - 1) // nseg
         ip = indptr.long()
         row_deg = ip[nseg::nseg] - ip[:-1:nseg][:n_rows] if nseg > 1 else ip[1:] - ip[:-1]
+        # rows in order of decreasing length: the warps of a CTA then work on rows of similar length and the
+        # longest rows start first
+        self.row_order = torch.argsort(row_deg, descending=True, stable=True).to(torch.int32)
         heavy = torch.nonzero(row_deg > threshold).flatten()
         self.n_heavy = int(heavy.numel())
         self.heavy_rows = heavy.to(torch.int32)
