@@ -411,6 +411,93 @@ def run_case(args):
         raise SystemExit(f"unknown case {args.case}")
 
 
+def run_primitives(args):
+    """Per-primitive numbers on the shapes of BASELINE configs 2 (QLinear) and 3 (SpMM / SDDMM): one JSON line per
+    primitive with ms, algorithmic GB/s (and TOPS for the GEMMs) and the fraction of the measured HBM peak.  L2 is
+    flushed (256 MB write) before every timed launch."""
+    import torch
+    import tango_b200 as T
+    from tango_b200 import kernels as K
+    from tango_b200.graph import rmat_graph
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    peaks, peak_kind = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out_lines = []
+
+    def timeit(fn, reps=10):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    def report(name, ms, nbytes, ops=None, **extra):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        line = {"primitive": name, "ms": round(ms, 4), "algorithmic_bytes": int(nbytes), "GBps": round(gbs, 1),
+                "frac_hbm_peak": round(gbs / peaks["hbm_gbs"], 3), "peak_source": peak_kind}
+        if ops:
+            line["TOPS"] = round(ops / (ms * 1e-3) / 1e12, 1)
+        line.update(extra)
+        out_lines.append(line)
+        print(json.dumps(line), flush=True)
+
+    # ---- config 2: QLinear 232,965 x 602 -> 256
+    m, k, n = 232_965, 602, 256
+    gen = torch.Generator(device=dev).manual_seed(3)
+    X = torch.randn((m, k), device=dev, generator=gen)
+    W = (torch.rand((n, k), device=dev, generator=gen) * 2 - 1) / k ** 0.5
+    dY = torch.randn((m, n), device=dev, generator=gen)
+    sx, sw, sdy = K.cuda_kernels.get_scale(X), K.cuda_kernels.get_scale(W), K.cuda_kernels.get_scale(dY)
+    xq, wq, dyq = K.alloc_int8(X.shape, dev), K.alloc_int8(W.shape, dev), K.alloc_int8(dY.shape, dev)
+    ldk = xq.stride(0)
+    report("absmax X[232965,602]", timeit(lambda: K.cuda_kernels.get_scale(X)), 4 * m * k)
+    report("quantize X[232965,602]", timeit(lambda: K._quantize_into(xq, X, sx)), 4 * m * k + m * ldk)
+    report("quantize dY[232965,256]", timeit(lambda: K._quantize_into(dyq, dY, sdy)), 5 * m * n)
+    K._quantize_into(wq, W, sw)
+    Y = torch.empty((m, n), device=dev)
+    ops = 2.0 * m * k * n
+    report("qgemm forward, int8 operands", timeit(lambda: K._qgemm_nt(Y, xq, wq, sx, sw)),
+           m * ldk + n * ldk + 4 * m * n, ops)
+    report("qgemm forward fused (quantize X, W + GEMM)", timeit(lambda: K.QGEMM_forward(X, xq, sx, W, wq, sw)),
+           4 * m * k + m * ldk + 4 * n * k + n * ldk + 4 * m * n, ops)
+    dX, dW = torch.empty((m, k), device=dev), torch.empty((n, k), device=dev)
+    report("qgemm dX", timeit(lambda: K.cuda_kernels.QGEMM_backward_gradX(dX, dyq, wq, sdy, sw)),
+           m * n + n * ldk + 4 * m * k, ops)
+    report("qgemm dW", timeit(lambda: K.cuda_kernels.QGEMM_backward_gradW(dW, dyq, xq, sdy, sx)),
+           m * n + m * ldk + 4 * n * k, ops)
+    del X, dY, Y, dX, xq, dyq
+    # ---- config 3: SpMM / SDDMM on 169,343 nodes, 1,166,243 edges (+ self loops)
+    nn_, ne_ = 169_343, 1_166_243
+    g = rmat_graph(nn_, ne_, 20243, device=dev)
+    T.graph_preprocess(g)
+    e = g.num_edges()
+    for f in (128, 256):
+        q, s = K.quantize(torch.randn((nn_, f), device=dev))
+        report(f"spmm copy_u F={f}", timeit(lambda: K.csr_SPMM(g, q, s)), nn_ * f + 4 * e + 4 * (nn_ + 1) + 4 * nn_ * f)
+        q3 = q.view(nn_, 4, f // 4)
+        eq, se = K.quantize(torch.rand((e, 4), device=dev), align=1)
+        report(f"spmm u_mul_e H=4 F={f}", timeit(lambda: K.spmm_u_mul_e_int8(g, q3, eq, s * se)),
+               nn_ * f + 8 * e + 4 * (nn_ + 1) + 4 * e + 4 * nn_ * f)
+        for h in (1, 4):
+            qh = q.view(nn_, h, f // h)
+            report(f"sddmm dot H={h} F={f}", timeit(lambda: K.mySDDMM_int8(g, "dot", qh, qh, s, s, False)),
+                   2 * nn_ * f + 8 * e + 4 * e * h)
+    for wdt in (4, 16, 32):
+        zq, sz = K.quantize(torch.randn((e, wdt), device=dev), align=4)
+        report(f"incidence spmm width={wdt}", timeit(lambda: K.incidence_SPMM(g, zq, sz)),
+               e * wdt + 4 * e + 4 * (nn_ + 1) + 4 * nn_ * wdt)
+    q16, s16 = K.quantize(torch.randn((nn_, 1, 16), device=dev))
+    report("sddmm add H=1 D=16", timeit(lambda: K.mySDDMM_int8(g, "add", q16, q16, s16, s16, False)),
+           2 * nn_ * 16 + 8 * e + 4 * e * 16)
+    print(json.dumps({"suite": "primitives", "status_word": K.device_status(), "n": len(out_lines)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -424,9 +511,13 @@ def main():
                     help="multi-GPU: one quantisation scale agreed by all ranks, or one per shard")
     ap.add_argument("--balance", default="dealt", choices=["dealt", "cyclic", "nnz", "rows"], help="multi-GPU node placement")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of a CUDA graph")
+    ap.add_argument("--suite", default=None, choices=["primitives"],
+                    help="per-primitive numbers on the QLinear and SpMM/SDDMM configurations instead of the epoch")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, gemm) and exit")
     args = ap.parse_args()
-    if args.case:
+    if args.suite == "primitives":
+        run_primitives(args)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)
