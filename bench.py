@@ -312,7 +312,10 @@ def run_ours(args):
         touched = n_edges * hidden + 4 * n_edges + 4 * (n + 1) + 4 * n * hidden
         ach = alg / (k_ms * 1e-3) / 1e9
         roof = {"kernel": "spmm_kernel<16,copy_u> F=256 (layer-1 aggregation)", "bound": "hbm", "achieved": ach,
-                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                # dram__bytes_read+write of one ncu capture on a 20.2 M-edge copy of the graph (397 MB), plus 4 B for
+                # every further edge of the index stream (profiles/spmm_copy_u_f256_ncu.md)
+                "traffic": 397_105_920 + 4 * max(0, n_edges - 20_232_965),
                 "peak_source": peak_kind, "kernel_ms": k_ms, "algorithmic_bytes": alg,
                 "gathered_bytes_per_s_GB": touched / (k_ms * 1e-3) / 1e9,
                 "note": "gathers of E*F bytes are served by L2; see DESIGN.md"}
