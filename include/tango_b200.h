@@ -145,6 +145,8 @@ typedef struct tango_spmm_plan {
     int32_t split_threshold;
     const int32_t *row_order;  /* optional [n_rows]: warp w works on row row_order[w] (e.g. rows sorted by degree, so
                                   that the warps of a CTA finish together); NULL = natural order */
+    int64_t n_long_rows;       /* with row_order: rows row_order[0, n_long_rows) get one warp each, the shorter rows
+                                  after them are handled by groups of lanes (several rows per warp); -1 = all long */
 } tango_spmm_plan;
 
 /* out[v,:] = sum_k scales[k] * float(sum_{j in segment k of row v} Nq[indices[j], :]) for v < n_rows.

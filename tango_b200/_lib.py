@@ -28,6 +28,7 @@ class SpmmPlan(Structure):
         ("ws_ld", c_int64),
         ("split_threshold", c_int32),
         ("row_order", c_void_p),
+        ("n_long_rows", c_int64),
     ]
 
 

@@ -37,6 +37,7 @@ struct SpmmArgs {
     int64_t ws_ld;
     int split_threshold;
     const int32_t *row_order;
+    int64_t n_long;   // rows row_order[0, n_long) go to the warp-per-row kernel, the rest to the lane-group kernel
     int G;  // lanes per neighbour (power of two)
 };
 
@@ -228,7 +229,7 @@ __global__ void __launch_bounds__(SPMM_THREADS, SPMM_MINB) spmm_kernel(const Spm
                     if (off + i < a.f && acc[i] != 0) atomicAdd(a.ws + (int64_t)u.w * a.ws_ld + off + i, acc[i]);
             }
         }
-    } else if (w - a.n_units < a.n_rows) {
+    } else if (w - a.n_units < a.n_long) {
         int64_t row = w - a.n_units;
         if (a.row_order) row = __ldg(a.row_order + row);
         const int32_t *ip = a.indptr + row * a.nseg;
@@ -277,6 +278,78 @@ __global__ void __launch_bounds__(SPMM_THREADS, SPMM_MINB) spmm_kernel(const Spm
     }
 }
 
+// Short rows: a group of G lanes owns one row (32 / G rows per warp), walks its neighbours four at a time and needs
+// neither shuffles nor a cross-lane reduction -- the warp-per-row kernel would spend most of its time in the ragged
+// tail on rows with a handful of neighbours.
+template <int VEC, int MODE>
+__global__ void __launch_bounds__(128) spmm_short_kernel(const SpmmArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int G = a.G, sub = lane % G;
+    const int64_t gid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const int64_t n_short = a.n_rows - a.n_long;
+    const int off = sub * VEC;
+    const bool active = gid < n_short && off < a.f_pad;
+    float amax = 0.f;
+    if (active) {
+        const int64_t row = a.row_order ? (int64_t)__ldg(a.row_order + a.n_long + gid) : a.n_long + gid;
+        const int32_t *ip = a.indptr + row * a.nseg;
+        const int8_t *base = a.feat + off;
+        const int head = (MODE == MODE_WEIGHT_LANE) ? off / a.D : 0;
+        float facc[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) facc[i] = 0.f;
+        for (int k = 0; k < a.nseg; ++k) {
+            const int beg = __ldg(ip + k), end = __ldg(ip + k + 1);
+            int acc[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = 0;
+            for (int j = beg; j < end; j += 4) {
+                VecLoad<VEC> v[4];
+                uint32_t wvec = (MODE == MODE_WEIGHT_LANE) ? 0u : 0x01010101u;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (j + u < end) {
+                        const int idx = a.indices ? __ldg(a.indices + j + u) : j + u;
+                        v[u].load(base + (int64_t)idx * a.ld);
+                        if (MODE == MODE_WEIGHT_LANE) {
+                            const int eid = a.edge_ids ? __ldg(a.edge_ids + j + u) : j + u;
+                            wvec |= (uint32_t)(uint8_t)__ldg(a.ew + (int64_t)eid * a.H + head) << (8 * u);
+                        }
+                    } else {
+                        v[u].zero();
+                    }
+                }
+                accumulate_four<VEC>(acc, v, wvec);
+            }
+            const float sc = __ldg(a.scales + k);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) facc[i] = __fadd_rn(facc[i], __fmul_rn((float)acc[i], sc));
+        }
+        float *o = a.out + row * a.ldo + off;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            facc[i] = finish_value(facc[i], row, min(off + i, a.f - 1), a);
+            if (off + i < a.f) amax = fmaxf(amax, fabsf(facc[i]));
+        }
+        if (VEC == 16 && off + 16 <= a.f && (a.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                reinterpret_cast<float4 *>(o)[i] = make_float4(facc[4 * i], facc[4 * i + 1], facc[4 * i + 2], facc[4 * i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i)
+                if (off + i < a.f) o[i] = facc[i];
+        }
+    }
+    if (a.out_absmax) {
+        amax = warp_max(amax);
+        if (lane == 0 && amax > 0.f) {
+            const float s = __fdiv_rn(amax, 127.0f);
+            if (s > __ldcg(a.out_absmax)) atomic_max_nonneg(a.out_absmax, s);
+        }
+    }
+}
+
 // Finishes the rows that were cut into units: one thread per (heavy row, feature byte).
 __global__ void __launch_bounds__(256) spmm_finalize_kernel(const SpmmArgs a) {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -310,6 +383,7 @@ static int pow2_ceil(int x) {
 template <int MODE>
 static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t stream) {
     if (a.n_rows == 0 || a.f == 0) return TANGO_OK;
+    a.n_long = a.n_rows;
     if (plan) a.row_order = plan->row_order;
     if (plan && plan->n_units > 0) {
         if (!plan->units || !plan->heavy_rows || !plan->ws || plan->ws_ld < a.f || plan->n_heavy <= 0)
@@ -335,10 +409,16 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
             vec = 4; a.f_pad = (int)round_up(a.f, 4); a.G = pow2_ceil(a.f_pad / 4); if (a.G > 32) a.G = 32;
         }
     }
-    const int64_t warps = a.n_units + a.n_rows;
+    // short rows (the tail of the degree-sorted order) go to the lane-group kernel when one pass of G lanes covers a row
+    const bool four = vec >= 4 && !(MODE == MODE_WEIGHT_LANE && (a.D % vec) != 0);
+    if (plan && plan->row_order && plan->n_long_rows >= 0 && plan->n_long_rows <= a.n_rows && four &&
+        a.f_pad <= 32 * vec)
+        a.n_long = plan->n_long_rows;
+    const int64_t warps = a.n_units + a.n_long;
     const int64_t blocks = ceil_div(warps, SPMM_THREADS / 32);
     if (blocks > 0x7fffffff) return TANGO_ESIZE;
-#define TANGO_SPMM_LAUNCH(V, M) spmm_kernel<V, M><<<(unsigned)blocks, SPMM_THREADS, 0, stream>>>(a)
+#define TANGO_SPMM_LAUNCH(V, M) \
+    if (blocks > 0) spmm_kernel<V, M><<<(unsigned)blocks, SPMM_THREADS, 0, stream>>>(a)
     if (MODE == MODE_WEIGHT_LANE && (a.D % vec) != 0) {
         if (vec == 16) TANGO_SPMM_LAUNCH(16, MODE_WEIGHT_ELEM);
         else if (vec == 4) TANGO_SPMM_LAUNCH(4, MODE_WEIGHT_ELEM);
@@ -350,6 +430,14 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
     }
 #undef TANGO_SPMM_LAUNCH
     TANGO_LAUNCH_CHECK();
+    if (a.n_long < a.n_rows) {
+        const int64_t threads = (a.n_rows - a.n_long) * a.G;
+        const int64_t sb = ceil_div(threads, 128);
+        if (sb > 0x7fffffff) return TANGO_ESIZE;
+        if (vec == 16) spmm_short_kernel<16, MODE><<<(unsigned)sb, 128, 0, stream>>>(a);
+        else spmm_short_kernel<4, MODE><<<(unsigned)sb, 128, 0, stream>>>(a);
+        TANGO_LAUNCH_CHECK();
+    }
     if (a.n_units > 0) {
         const int64_t fb = ceil_div(a.n_heavy * a.f, 256);
         spmm_finalize_kernel<<<(unsigned)fb, 256, 0, stream>>>(a);

@@ -231,13 +231,14 @@ def _make_plan(sched: Optional[SpmmSchedule], f: int, device):
         return None, ()
     order = getattr(sched, "row_order", None)
     order_ptr = order.data_ptr() if order is not None and order.numel() else None
+    n_long = getattr(sched, "n_long", -1) if order_ptr else -1
     if sched.n_units == 0:
-        plan = SpmmPlan(None, 0, None, 0, None, 0, sched.threshold, order_ptr)
+        plan = SpmmPlan(None, 0, None, 0, None, 0, sched.threshold, order_ptr, n_long)
         return ctypes.byref(plan), (plan,)
     ws_ld = _round_up(f, 16)
     ws = torch.empty((sched.n_heavy * sched.nseg, ws_ld), dtype=torch.int32, device=device)
     plan = SpmmPlan(sched.units.data_ptr(), sched.n_units, sched.heavy_rows.data_ptr(), sched.n_heavy, ws.data_ptr(),
-                    ws_ld, sched.threshold, order_ptr)
+                    ws_ld, sched.threshold, order_ptr, n_long)
     return ctypes.byref(plan), (plan, ws)
 
 
@@ -250,7 +251,7 @@ def _csr_spmm(out, indptr, indices, U, scaleU, sched=None, nseg=1, row_scale=Non
     with torch.cuda.device(U.device):
         check(lib.tango_spmm_copy_u(_p(indptr), _pi(indices), n_rows, nseg, _p(U), ldn, f, _p(scaleU), _p(row_scale),
                                     _p(bias), int(relu), _p(out), ldo, _p(out_absmax), plan, _stream()), "csr_SPMM")
-    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0)
+    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0) + (sched is not None and sched.n_long < sched.row_order.numel())
     del keep
 
 
@@ -266,7 +267,7 @@ def _u_mul_e_spmm(indptr, indices, edge_ids, N, E, scale, sched=None):
     with torch.cuda.device(N.device):
         check(lib.tango_spmm_u_mul_e(_p(indptr), _pi(indices), _p(edge_ids), n_rows, _p(N), ldn, h, d, _p(E), _p(scale),
                                      _p(out), f, plan, _stream()), "multi_cusparse_SPMM")
-    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0)
+    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0) + (sched is not None and sched.n_long < sched.row_order.numel())
     del keep
     return out
 
@@ -279,7 +280,7 @@ def _incidence_spmm(out, indptr, edge_ids, E, scale, sched=None):
     with torch.cuda.device(E.device):
         check(lib.tango_spmm_incidence(_p(indptr), _p(edge_ids), n_rows, _p(E), ldz, f, _p(scale), _p(out), ldo, plan,
                                        _stream()), "incidence_SPMM")
-    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0)
+    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0) + (sched is not None and sched.n_long < sched.row_order.numel())
     del keep
 
 
