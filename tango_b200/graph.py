@@ -216,7 +216,18 @@ class SpmmSchedule:
     """Device arrays consumed by the SpMM kernels: `units` [n_units, 4] = (segment row, begin, end, scratch slot)
     for every slice of a row longer than the threshold, and `heavy_rows` = those rows."""
 
-    def __init__(self, indptr: torch.Tensor, nseg: int = 1, threshold: int = SPLIT_THRESHOLD, unit: int = UNIT_NNZ):
+    def __init__(self, indptr: torch.Tensor, nseg: int = 1, threshold: Optional[int] = None,
+                 unit: Optional[int] = None):
+        if threshold is None:
+            # A row is worked on by one warp, neighbour batch after neighbour batch, so the longest unsplit row sets
+            # the critical path of the kernel.  Keep it short relative to the total work: about nnz / 16384 (one
+            # batch-chain per resident warp slot), between 256 and SPLIT_THRESHOLD.
+            nnz = int(indptr[-1]) if indptr.numel() else 0
+            threshold = 256
+            while threshold < SPLIT_THRESHOLD and threshold * 16384 < nnz:
+                threshold *= 2
+        if unit is None:
+            unit = max(128, threshold // 2)
         self.nseg = nseg
         self.threshold = threshold
         n_rows = (indptr.numel() - 1) // nseg
