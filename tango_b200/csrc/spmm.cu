@@ -417,8 +417,10 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
     const int64_t warps = a.n_units + a.n_long;
     const int64_t blocks = ceil_div(warps, SPMM_THREADS / 32);
     if (blocks > 0x7fffffff) return TANGO_ESIZE;
-#define TANGO_SPMM_LAUNCH(V, M) \
-    if (blocks > 0) spmm_kernel<V, M><<<(unsigned)blocks, SPMM_THREADS, 0, stream>>>(a)
+#define TANGO_SPMM_LAUNCH(V, M)                                                                  \
+    do {                                                                                         \
+        if (blocks > 0) spmm_kernel<V, M><<<(unsigned)blocks, SPMM_THREADS, 0, stream>>>(a);     \
+    } while (0)
     if (MODE == MODE_WEIGHT_LANE && (a.D % vec) != 0) {
         if (vec == 16) TANGO_SPMM_LAUNCH(16, MODE_WEIGHT_ELEM);
         else if (vec == 4) TANGO_SPMM_LAUNCH(4, MODE_WEIGHT_ELEM);
