@@ -30,6 +30,8 @@ WORKLOADS = {
     # name: (nodes, directed non-loop edges, in_feats, hidden, classes, graph seed)
     "gcn_c5": (232_965, 114_615_892 - 232_965, 602, 256, 41, 20245),
     "gcn_c1": (19_717, 88_648, 500, 16, 3, 20241),
+    # 2-layer GAT, 4 heads x 64 hidden, 1 output head x 41 classes (BASELINE config 4), same graph as gcn_c5
+    "gat_c4": (232_965, 114_615_892 - 232_965, 602, 64, 41, 20245),
 }
 
 
@@ -190,11 +192,16 @@ def run_ours(args):
     n_edges = g.num_edges()
     torch.manual_seed(6)
     if world == 1:
-        from tango_b200.gnn import GCN
+        from tango_b200.gnn import GAT, GCN
         T.graph_preprocess(g)
-        model = GCN(g, in_feats, hidden, classes, 1).to(dev)
+        if name.startswith("gat"):
+            model = GAT(g, 2, in_feats, hidden, classes, [4, 1]).to(dev)
+        else:
+            model = GCN(g, in_feats, hidden, classes, 1).to(dev)
         rows = slice(0, n)
     else:
+        if name.startswith("gat"):
+            raise SystemExit("the GAT workload runs on one GPU")
         from tango_b200.dist import DistGCN, DistGraph, allreduce_grads
         dg = DistGraph(g, rank, world, balance=args.balance, scale_mode=args.scale_mode)
         del g
@@ -321,12 +328,13 @@ def run_ours(args):
                 "note": "gathers of E*F bytes are served by L2; see DESIGN.md"}
 
     cpu_base = None
-    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+    if world == 1 and rank == 0 and not args.no_cpu_baseline and not name.startswith("gat"):
         cpu_base = _cpu_baseline(name, g, model)
 
     if rank == 0:
         line = {
-            "metric": "gcn_epoch_ms", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "metric": "gat_epoch_ms" if name.startswith("gat") else "gcn_epoch_ms", "value": ms, "unit": "ms",
+            "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "s8", "data": "synthetic",
             "config": {"workload": name, "nodes": n, "edges": n_edges, "layers": f"{in_feats}-{hidden}-{classes}",

@@ -37,13 +37,34 @@ __device__ __forceinline__ int dot_bytes(const int8_t *pu, const int8_t *pv) {
     }
 }
 
+template <int VEC> struct DotVec;
+template <> struct DotVec<16> { typedef uint4 T; };
+template <> struct DotVec<4> { typedef uint32_t T; };
+template <> struct DotVec<1> { typedef int8_t T; };
+
+template <int VEC>
+__device__ __forceinline__ int dot_regs(const typename DotVec<VEC>::T &a, const typename DotVec<VEC>::T &b);
+template <> __device__ __forceinline__ int dot_regs<16>(const uint4 &a, const uint4 &b) {
+    int s = __dp4a((int)a.x, (int)b.x, 0);
+    s = __dp4a((int)a.y, (int)b.y, s);
+    s = __dp4a((int)a.z, (int)b.z, s);
+    return __dp4a((int)a.w, (int)b.w, s);
+}
+template <> __device__ __forceinline__ int dot_regs<4>(const uint32_t &a, const uint32_t &b) {
+    return __dp4a((int)a, (int)b, 0);
+}
+template <> __device__ __forceinline__ int dot_regs<1>(const int8_t &a, const int8_t &b) { return (int)a * (int)b; }
+
 template <int VEC>
 __global__ void __launch_bounds__(256) sddmm_dot_kernel(const DotArgs a) {
+    typedef typename DotVec<VEC>::T V;
     const int lane = threadIdx.x & 31;
     const int G = a.G, IPS = 32 / G, grp = lane / G, sub = lane % G;
     const float sc = __fmul_rn(__ldg(a.su), __ldg(a.sv));
     const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int64_t nwarp = (int64_t)gridDim.x * (blockDim.x >> 5);
+    const bool single_trip = a.d_pad <= G * VEC;   // one load per operand covers a head: keep 4 items in flight
+    constexpr int UN = 4;
     float amax = 0.f;
     for (int64_t e0 = warp * 32; e0 < a.n_edges; e0 += nwarp * 32) {
         const int64_t e = e0 + lane;
@@ -51,22 +72,38 @@ __global__ void __launch_bounds__(256) sddmm_dot_kernel(const DotArgs a) {
         if (e < a.n_edges) { my_s = __ldg(a.src + e); my_d = __ldg(a.dst + e); }
         const int n_e = (int)min((int64_t)32, a.n_edges - e0);
         const int items = n_e * a.H;
-        for (int it0 = 0; it0 < items; it0 += IPS) {
-            const int item = it0 + grp;
-            const int el = item / a.H, hd = item - el * a.H;
-            const int s_id = __shfl_sync(0xffffffffu, my_s, el & 31);
-            const int d_id = __shfl_sync(0xffffffffu, my_d, el & 31);
-            int acc = 0;
-            if (item < items) {
-                const int8_t *pu = a.u + (int64_t)s_id * a.ldu + (int64_t)hd * a.D;
-                const int8_t *pv = a.v + (int64_t)d_id * a.ldv + (int64_t)hd * a.D;
-                for (int off = sub * VEC; off < a.d_pad; off += G * VEC) acc += dot_bytes<VEC>(pu + off, pv + off);
+        for (int it0 = 0; it0 < items; it0 += IPS * UN) {
+            int acc[UN], el[UN], hd[UN];
+            V ru[UN], rv[UN];
+            bool ok[UN];
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const int item = it0 + u * IPS + grp;
+                el[u] = item / a.H; hd[u] = item - el[u] * a.H;
+                const int s_id = __shfl_sync(0xffffffffu, my_s, el[u] & 31);
+                const int d_id = __shfl_sync(0xffffffffu, my_d, el[u] & 31);
+                ok[u] = item < items;
+                acc[u] = 0;
+                const int8_t *pu = a.u + (int64_t)s_id * a.ldu + (int64_t)hd[u] * a.D;
+                const int8_t *pv = a.v + (int64_t)d_id * a.ldv + (int64_t)hd[u] * a.D;
+                if (single_trip) {
+                    const bool ld = ok[u] && sub * VEC < a.d_pad;
+                    ru[u] = ld ? __ldg(reinterpret_cast<const V *>(pu + sub * VEC)) : V();
+                    rv[u] = ld ? __ldg(reinterpret_cast<const V *>(pv + sub * VEC)) : V();
+                } else if (ok[u]) {
+                    for (int off = sub * VEC; off < a.d_pad; off += G * VEC)
+                        acc[u] += dot_bytes<VEC>(pu + off, pv + off);
+                }
             }
-            for (int o = G >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (item < items && sub == 0) {
-                const float r = __fmul_rn((float)acc, sc);
-                __stcs(a.out + (e0 + el) * a.H + hd, r);
-                amax = fmaxf(amax, fabsf(r));
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                if (single_trip) acc[u] = dot_regs<VEC>(ru[u], rv[u]);
+                for (int o = G >> 1; o > 0; o >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+                if (ok[u] && sub == 0) {
+                    const float r = __fmul_rn((float)acc[u], sc);
+                    __stcs(a.out + (e0 + el[u]) * a.H + hd[u], r);
+                    amax = fmaxf(amax, fabsf(r));
+                }
             }
         }
     }
@@ -190,6 +227,44 @@ __global__ void __launch_bounds__(256) gat_edge_softmax_kernel(const int32_t *__
     }
 }
 
+// Backward of the fused pass above.  For destination row v and head h, with a_j the softmax weights and g_j the
+// incoming gradient of a_j:  dz_j = a_j * (g_j - sum_k a_k g_k) * (z_j >= 0 ? 1 : slope), z_j recomputed from the
+// int8 operands.  One warp per row, two sweeps (the weighted sum, then the write).
+__global__ void __launch_bounds__(256) gat_edge_softmax_bwd_kernel(const int32_t *__restrict__ indptr,
+                                                                   const int32_t *__restrict__ indices,
+                                                                   const int32_t *__restrict__ edge_ids,
+                                                                   int64_t n_rows, const int8_t *__restrict__ elq,
+                                                                   const int8_t *__restrict__ erq, int H,
+                                                                   const float *__restrict__ sl_,
+                                                                   const float *__restrict__ sr_, float slope,
+                                                                   const float *__restrict__ att,
+                                                                   const float *__restrict__ datt,
+                                                                   float *__restrict__ dz) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const float sl = __ldg(sl_), sr = __ldg(sr_);
+    const int beg = __ldg(indptr + row), end = __ldg(indptr + row + 1);
+    for (int h = 0; h < H; ++h) {
+        const float er = __fmul_rn((float)__ldg(erq + row * H + h), sr);
+        float dot = 0.f;
+        for (int j = beg + lane; j < end; j += 32) {
+            const int64_t eid = edge_ids ? __ldg(edge_ids + j) : j;
+            dot += __ldg(att + eid * H + h) * __ldg(datt + eid * H + h);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        for (int j = beg + lane; j < end; j += 32) {
+            const int64_t eid = edge_ids ? __ldg(edge_ids + j) : j;
+            const float z = __fadd_rn(__fmul_rn((float)__ldg(elq + (int64_t)__ldg(indices + j) * H + h), sl), er);
+            const float a = __ldg(att + eid * H + h);
+            float g = a * (__ldg(datt + eid * H + h) - dot);
+            if (z < 0.f) g *= slope;
+            dz[eid * H + h] = g;
+        }
+    }
+}
+
 static int pow2_ceil(int x) {
     int p = 1;
     while (p < x) p <<= 1;
@@ -272,6 +347,21 @@ extern "C" int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indi
     const int64_t blocks = ceil_div(n_rows, 8);
     gat_edge_softmax_kernel<<<(unsigned)blocks, 256, 0, stream>>>(indptr, indices, edge_ids, n_rows, elq, erq, h, sl,
                                                                   sr, slope, a);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}
+
+extern "C" int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                                          int64_t n_rows, const int8_t *elq, const int8_t *erq, int h, const float *sl,
+                                          const float *sr, float slope, const float *a, const float *da, float *dz,
+                                          tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (n_rows < 0 || h < 1) return TANGO_EINVAL;
+    if (n_rows == 0) return TANGO_OK;
+    if (!indptr || !indices || !elq || !erq || !sl || !sr || !a || !da || !dz) return TANGO_EINVAL;
+    const int64_t blocks = ceil_div(n_rows, 8);
+    gat_edge_softmax_bwd_kernel<<<(unsigned)blocks, 256, 0, stream>>>(indptr, indices, edge_ids, n_rows, elq, erq, h, sl,
+                                                                      sr, slope, a, da, dz);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
 }

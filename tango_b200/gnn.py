@@ -203,13 +203,47 @@ def edge_softmax(g, e):
     return _edge_softmax_fn.apply(g, e)
 
 
+class _gat_attention_fused(Function):
+    """Attention weights of a GAT layer in one pass per direction:
+
+        a = edge_softmax(leaky_relu(Q(el)[src] + Q(er)[dst]))
+
+    i.e. the reference's sddmm_u_add_v -> nn.LeakyReLU -> dgl.ops.edge_softmax chain (evaluation/test_gat.py:141-146)
+    without materialising the logits: el / er are quantized to int8 exactly as sddmm_u_add_v does, one kernel walks
+    every destination's incoming edges (max, sum, normalise), and the backward kernel produces the gradient of the
+    logits, which then takes sddmm_u_add_v's backward route (int8 quantisation + incidence sums)."""
+
+    @staticmethod
+    def forward(ctx, g, el, er, slope):
+        mode, seed = config.mode_for("quantize"), config.seed()
+        n, h = el.shape[0], el.shape[1]
+        elq, sl = kernels.quantize(el.reshape(n, h), mode=mode, seed=seed, align=1)
+        erq, sr = kernels.quantize(er.reshape(n, h), mode=mode, seed=seed, align=1)
+        a = kernels.gat_edge_softmax(g, elq, erq, sl, sr, slope)
+        ctx.g, ctx.slope, ctx.shapes = g, slope, (el.shape, er.shape)
+        ctx.save_for_backward(elq, erq, sl, sr, a)
+        return a.view(a.shape[0], h, 1)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, da):
+        elq, erq, sl, sr, a = ctx.saved_tensors
+        g = ctx.g
+        dz = kernels.gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, ctx.slope)
+        dzq, sdz = kernels.quantize(dz, mode=config.mode_for("quantize"), seed=config.seed(), align=1)
+        d_el = kernels.incidence_SPMM(g, dzq, sdz, True).view(ctx.shapes[0]) if ctx.needs_input_grad[1] else None
+        d_er = kernels.incidence_SPMM(g, dzq, sdz).view(ctx.shapes[1]) if ctx.needs_input_grad[2] else None
+        return None, d_el, d_er, None
+
+
 class QGATConv(nn.Module):
     """Graph attention layer on the quantized operators (evaluation/test_gat.py:30-169): QLinear projection,
     int8 u_add_v edge logits, LeakyReLU, edge softmax (fp32), int8 u_mul_e aggregation."""
 
     def __init__(self, in_feats, out_feats, num_heads, feat_drop=0.0, attn_drop=0.0, negative_slope=0.2,
-                 residual=False, activation=None, allow_zero_in_degree=False, bias=True):
+                 residual=False, activation=None, allow_zero_in_degree=False, bias=True, fused=True):
         super().__init__()
+        self._fused, self._slope = fused, negative_slope
         self._num_heads, self._in_feats, self._out_feats = num_heads, in_feats, out_feats
         self._allow_zero_in_degree = allow_zero_in_degree
         self.fc = QLinear(in_feats, out_feats * num_heads, bias=False)
@@ -245,8 +279,11 @@ class QGATConv(nn.Module):
         ft = self.fc(h).view(*prefix, self._num_heads, self._out_feats)
         el = (ft * self.attn_l).sum(dim=-1).unsqueeze(-1)
         er = (ft * self.attn_r).sum(dim=-1).unsqueeze(-1)
-        e = self.leaky_relu(sddmm_u_add_v.apply(graph, el, er))
-        a = self.attn_drop(edge_softmax(graph, e))
+        if self._fused:
+            a = self.attn_drop(_gat_attention_fused.apply(graph, el, er, self._slope))
+        else:
+            e = self.leaky_relu(sddmm_u_add_v.apply(graph, el, er))
+            a = self.attn_drop(edge_softmax(graph, e))
         rst = spmm_u_mul_e.apply(graph, ft, a)
         if self.res_fc is not None:
             rst = rst + self.res_fc(h).view(*prefix, -1, self._out_feats)
@@ -261,18 +298,18 @@ class GAT(nn.Module):
     """evaluation/test_gat.py:172-224."""
 
     def __init__(self, g, num_layers, in_dim, num_hidden, num_classes, heads, activation=F.elu, feat_drop=0.0,
-                 attn_drop=0.0, negative_slope=0.2, residual=False):
+                 attn_drop=0.0, negative_slope=0.2, residual=False, fused=True):
         super().__init__()
         self.g, self.num_layers = g, num_layers
         self.gat_layers = nn.ModuleList()
         if num_layers > 1:
             self.gat_layers.append(QGATConv(in_dim, num_hidden, heads[0], feat_drop, attn_drop, negative_slope,
-                                            False, activation))
+                                            False, activation, fused=fused))
             for l in range(1, num_layers - 1):
                 self.gat_layers.append(QGATConv(num_hidden * heads[l - 1], num_hidden, heads[l], feat_drop, attn_drop,
-                                                negative_slope, residual, activation))
+                                                negative_slope, residual, activation, fused=fused))
             self.gat_layers.append(QGATConv(num_hidden * heads[-2], num_classes, heads[-1], feat_drop, attn_drop,
-                                            negative_slope, residual, None))
+                                            negative_slope, residual, None, fused=fused))
         else:
             self.gat_layers.append(QGATConv(in_dim, num_classes, heads[0], feat_drop, attn_drop, negative_slope,
                                             residual, None))

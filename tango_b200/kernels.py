@@ -495,3 +495,19 @@ def gat_edge_softmax(g, elq, erq, sl, sr, slope: float = 0.2):
                                          _p(sl), _p(sr), float(slope), _p(a), _stream()), "gat_edge_softmax")
     launch_counter[0] += 1
     return a
+
+
+def gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, slope: float = 0.2):
+    """Gradient of `gat_edge_softmax` with respect to the edge logits (before the LeakyReLU); fp32 [E, H]."""
+    indptr, indices, edge_ids = g.adj_csc
+    h = elq.shape[1]
+    elq = elq.reshape(elq.shape[0], -1).contiguous()
+    erq = erq.reshape(erq.shape[0], -1).contiguous()
+    a, da = a.reshape(-1, h).contiguous(), da.reshape(-1, h).contiguous()
+    dz = torch.empty_like(a)
+    with torch.cuda.device(elq.device):
+        check(lib.tango_gat_edge_softmax_bwd(_p(indptr), _p(indices), _p(edge_ids), g.num_nodes(), _p(elq), _p(erq), h,
+                                             _p(sl), _p(sr), float(slope), _p(a), _p(da), _p(dz), _stream()),
+              "gat_edge_softmax_bwd")
+    launch_counter[0] += 1
+    return dz

@@ -161,3 +161,46 @@ def test_gat_layer_close_to_fp32(cuda):
         h1 = ref_layer(m.gat_layers[0], x, F.elu).flatten(1)
         ref = ref_layer(m.gat_layers[1], h1, None).mean(1)
     assert (logits - ref).abs().max() / ref.abs().max() < 0.1
+
+
+def test_fused_gat_attention_matches_unfused_chain(cuda):
+    """Fused edge-softmax pass (forward and backward) against the operator-by-operator chain of the reference layer."""
+    from tango_b200.gnn import GAT
+    g = _setup(1200, 20000, 21)
+    n = g.num_nodes()
+    torch.manual_seed(8)
+    x = torch.randn(n, 64, device="cuda")
+    y = torch.randint(0, 6, (n,), device="cuda")
+    res = []
+    for fused in (True, False):
+        torch.manual_seed(9)
+        m = GAT(g, 2, 64, 16, 6, [4, 1], fused=fused).cuda()
+        logits = m(x)
+        F.cross_entropy(logits, y).backward()
+        res.append((logits.detach(), [p.grad.clone() for p in m.parameters()]))
+    # same int8 operands and the same logits; only exp/normalisation differ in the last bits -> the int8 attention
+    # weights can flip by one step here and there
+    assert (res[0][0] - res[1][0]).abs().max() / res[1][0].abs().max() < 2e-2
+    for a, b in zip(res[0][1], res[1][1]):
+        cos = torch.dot(a.flatten(), b.flatten()) / (a.norm() * b.norm() + 1e-30)
+        assert cos > 0.98, cos
+
+
+def test_gat_edge_softmax_bwd_kernel(cuda):
+    from tango_b200 import kernels as K
+    g = _setup(500, 6000, 23)
+    n, e = g.num_nodes(), g.num_edges()
+    src, dst = [t.long() for t in g.coo]
+    torch.manual_seed(1)
+    el = torch.randint(-127, 128, (n, 4), dtype=torch.int8, device="cuda")
+    er = torch.randint(-127, 128, (n, 4), dtype=torch.int8, device="cuda")
+    sl, sr = torch.tensor([0.02], device="cuda"), torch.tensor([0.015], device="cuda")
+    a = K.gat_edge_softmax(g, el, er, sl, sr, 0.2)
+    da = torch.randn(e, 4, device="cuda")
+    dz = K.gat_edge_softmax_bwd(g, el, er, sl, sr, a, da, 0.2)
+    z = (el.float() * sl)[src] + (er.float() * sr)[dst]
+    z.requires_grad_(True)
+    ex = torch.exp(F.leaky_relu(z, 0.2) - 5.0)       # shift-invariant; any constant works for the reference
+    s = torch.zeros(n, 4, device="cuda").index_add_(0, dst, ex)
+    (ex / s[dst] * da).sum().backward()
+    assert (dz - z.grad).abs().max() < 1e-4 * max(1.0, z.grad.abs().max().item())
