@@ -193,19 +193,23 @@ int tango_sddmm_elementwise(int op, const int32_t *src, const int32_t *dst, int6
  *   z[j] = leaky_relu(float(elq[indices[j],h])*sl[0] + float(erq[v,h])*sr[0], slope)
  *   a[eid(j),h] = exp(z[j]-max_v)/sum_v
  * i.e. the reference's sddmm_u_add_v -> LeakyReLU -> dgl edge_softmax chain (evaluation/test_gat.py:141-146,
- * cuda/SDDMM.py:10-20) in one pass; `a` is fp32 [E, H] in edge-id order; elq / erq are contiguous int8 [N, H]. */
-int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids, int64_t n_rows,
-                           const int8_t *elq, const int8_t *erq, int h, const float *sl, const float *sr, float slope,
-                           float *a, tango_stream_t stream);
+ * cuda/SDDMM.py:10-20) in one pass; `a` is fp32 [E, H] in edge-id order; elq / erq are contiguous int8 [N, H], H <= 8.
+ * Optional schedule: with row_order (rows by decreasing degree) the first n_block_rows rows get a whole CTA each, the
+ * others a warp; row_order == NULL means one warp per row in natural order. */
+int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                           const int32_t *row_order, int64_t n_block_rows, int64_t n_rows, const int8_t *elq,
+                           const int8_t *erq, int h, const float *sl, const float *sr, float slope, float *a,
+                           tango_stream_t stream);
 
 /* Gradient of the pass above with respect to the edge logits: for every destination row and head
- *   dz[eid(j),h] = a_j * (da_j - sum_k a_k da_k) * (z_j >= 0 ? 1 : slope)
+ *   dz[eid(j),h] = a_j * (da_j - sum_k a_k da_k) * (z_j > 0 ? 1 : slope)
  * (softmax backward, then LeakyReLU backward with z recomputed from the int8 operands).  `a`, `da`, `dz` are fp32
  * [E, H] in edge-id order; elq / erq are contiguous int8 [N, H].  Replaces the autograd backward of
  * dgl.ops.edge_softmax and nn.LeakyReLU in the reference's GAT layer (evaluation/test_gat.py:144-146). */
-int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids, int64_t n_rows,
-                               const int8_t *elq, const int8_t *erq, int h, const float *sl, const float *sr,
-                               float slope, const float *a, const float *da, float *dz, tango_stream_t stream);
+int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                               const int32_t *row_order, int64_t n_block_rows, int64_t n_rows, const int8_t *elq,
+                               const int8_t *erq, int h, const float *sl, const float *sr, float slope, const float *a,
+                               const float *da, float *dz, tango_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,231 @@
+// Fused attention-weight pass of a GAT layer and its gradient.
+//
+// forward : a[e,h]  = softmax over the incoming edges of dst(e) of leaky_relu(el_q[src(e),h]*sl + er_q[dst(e),h]*sr)
+// backward: dz[e,h] = a * (da - sum_row a*da) * (z > 0 ? 1 : slope)   (PyTorch's LeakyReLU gradient convention at 0)
+//
+// A destination row is owned by a thread team: a whole CTA for the rows at the head of the degree-sorted order (a
+// power-law graph has rows with 10^5 incoming edges; one warp would serialise them), a warp for the rest.  All heads
+// of an edge are handled together (one 128-bit access per edge when H == 4).  The softmax statistics are
+// accumulated "online" (running maximum with rescaling), so the forward needs two sweeps over a row, and every
+// reduction runs in a fixed order, which makes the result deterministic.
+#include "common.cuh"
+
+namespace tango {
+
+constexpr int kMaxHeads = 8;
+
+struct GatArgs {
+    const int32_t *indptr, *indices, *edge_ids, *row_order;
+    int64_t n_rows, n_block_rows;
+    const int8_t *elq, *erq;
+    int H;
+    const float *sl, *sr;
+    float slope;
+    float *att;          // forward: output; backward: input
+    const float *datt;   // backward
+    float *dz;           // backward
+};
+
+__device__ __forceinline__ float leaky(float z, float slope) { return z >= 0.f ? z : __fmul_rn(z, slope); }
+
+// z for all heads of slot j of row `row`
+template <int HT>
+__device__ __forceinline__ void edge_logits(const GatArgs &a, int j, const float (&er)[kMaxHeads], float sl,
+                                            float (&z)[kMaxHeads]) {
+    const int64_t s = __ldg(a.indices + j);
+    if (HT == 4) {
+        const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(a.elq + s * 4));
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+            z[h] = leaky(__fadd_rn(__fmul_rn((float)(int8_t)(w >> (8 * h)), sl), er[h]), a.slope);
+    } else {
+        for (int h = 0; h < a.H; ++h)
+            z[h] = leaky(__fadd_rn(__fmul_rn((float)__ldg(a.elq + s * a.H + h), sl), er[h]), a.slope);
+    }
+}
+
+// Fixed-order reductions over a team of NT threads (NT = 32: one warp; else the whole CTA through shared memory).
+template <int NT>
+__device__ __forceinline__ float team_sum(float v, float *smem) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (NT == 32) return v;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < NT / 32; ++w) t += smem[w];
+    return t;
+}
+
+// merges online-softmax states (m, s): fixed butterfly inside a warp, then warp 0..n in order
+template <int NT>
+__device__ __forceinline__ void team_softmax_merge(float &m, float &s, float *smem) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        const float mm = fmaxf(m, m2);
+        s = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+        m = mm;
+    }
+    if (NT == 32) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) { smem[warp] = m; smem[32 + warp] = s; }
+    __syncthreads();
+    float mm = -INFINITY, ss = 0.f;
+    for (int w = 0; w < NT / 32; ++w) {
+        const float m2 = smem[w], s2 = smem[32 + w];
+        const float mx = fmaxf(mm, m2);
+        ss = (mm == -INFINITY ? 0.f : ss * __expf(mm - mx)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mx));
+        mm = mx;
+    }
+    m = mm; s = ss;
+}
+
+template <int NT, int HT>
+__device__ __forceinline__ void softmax_row(const GatArgs &a, int64_t row, int tid, float *smem) {
+    const float sl = __ldg(a.sl), sr = __ldg(a.sr);
+    const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
+    const int H = HT ? HT : a.H;
+    float er[kMaxHeads], m[kMaxHeads], s[kMaxHeads];
+#pragma unroll
+    for (int h = 0; h < kMaxHeads; ++h) {
+        er[h] = h < H ? __fmul_rn((float)__ldg(a.erq + row * H + h), sr) : 0.f;
+        m[h] = -INFINITY; s[h] = 0.f;
+    }
+    for (int j = beg + tid; j < end; j += NT) {
+        float z[kMaxHeads];
+        edge_logits<HT>(a, j, er, sl, z);
+#pragma unroll
+        for (int h = 0; h < kMaxHeads; ++h) {
+            if (h < H) {
+                if (z[h] > m[h]) { s[h] = s[h] * __expf(m[h] - z[h]) + 1.f; m[h] = z[h]; }
+                else s[h] += __expf(z[h] - m[h]);
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < kMaxHeads; ++h)
+        if (h < H) team_softmax_merge<NT>(m[h], s[h], smem);
+    float inv[kMaxHeads];
+#pragma unroll
+    for (int h = 0; h < kMaxHeads; ++h) inv[h] = h < H ? 1.f / s[h] : 0.f;
+    for (int j = beg + tid; j < end; j += NT) {
+        float z[kMaxHeads];
+        edge_logits<HT>(a, j, er, sl, z);
+        const int64_t eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
+        if (HT == 4) {
+            *reinterpret_cast<float4 *>(a.att + eid * 4) =
+                make_float4(__expf(z[0] - m[0]) * inv[0], __expf(z[1] - m[1]) * inv[1], __expf(z[2] - m[2]) * inv[2],
+                            __expf(z[3] - m[3]) * inv[3]);
+        } else {
+            for (int h = 0; h < H; ++h) a.att[eid * H + h] = __expf(z[h] - m[h]) * inv[h];
+        }
+    }
+}
+
+template <int NT, int HT>
+__device__ __forceinline__ void softmax_bwd_row(const GatArgs &a, int64_t row, int tid, float *smem) {
+    const float sl = __ldg(a.sl), sr = __ldg(a.sr);
+    const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
+    const int H = HT ? HT : a.H;
+    float er[kMaxHeads], dot[kMaxHeads];
+#pragma unroll
+    for (int h = 0; h < kMaxHeads; ++h) {
+        er[h] = h < H ? __fmul_rn((float)__ldg(a.erq + row * H + h), sr) : 0.f;
+        dot[h] = 0.f;
+    }
+    for (int j = beg + tid; j < end; j += NT) {
+        const int64_t eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
+        if (HT == 4) {
+            const float4 p = __ldg(reinterpret_cast<const float4 *>(a.att + eid * 4));
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(a.datt + eid * 4));
+            dot[0] += p.x * g.x; dot[1] += p.y * g.y; dot[2] += p.z * g.z; dot[3] += p.w * g.w;
+        } else {
+            for (int h = 0; h < H; ++h) dot[h] += __ldg(a.att + eid * H + h) * __ldg(a.datt + eid * H + h);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < kMaxHeads; ++h)
+        if (h < H) dot[h] = team_sum<NT>(dot[h], smem);
+    for (int j = beg + tid; j < end; j += NT) {
+        float z[kMaxHeads];
+        edge_logits<HT>(a, j, er, sl, z);   // leaky(z) has the sign of z
+        const int64_t eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
+        if (HT == 4) {
+            const float4 p = __ldg(reinterpret_cast<const float4 *>(a.att + eid * 4));
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(a.datt + eid * 4));
+            float4 o = make_float4(p.x * (g.x - dot[0]), p.y * (g.y - dot[1]), p.z * (g.z - dot[2]),
+                                   p.w * (g.w - dot[3]));
+            if (!(z[0] > 0.f)) o.x *= a.slope;
+            if (!(z[1] > 0.f)) o.y *= a.slope;
+            if (!(z[2] > 0.f)) o.z *= a.slope;
+            if (!(z[3] > 0.f)) o.w *= a.slope;
+            *reinterpret_cast<float4 *>(a.dz + eid * 4) = o;
+        } else {
+            for (int h = 0; h < H; ++h) {
+                float o = __ldg(a.att + eid * H + h) * (__ldg(a.datt + eid * H + h) - dot[h]);
+                if (!(z[h] > 0.f)) o *= a.slope;
+                a.dz[eid * H + h] = o;
+            }
+        }
+    }
+}
+
+// blocks [0, n_block_rows): one CTA per row; the remaining blocks: one warp per row
+template <int HT, bool BWD>
+__global__ void __launch_bounds__(256) gat_softmax_kernel(const GatArgs a) {
+    __shared__ float smem[64];
+    if ((int64_t)blockIdx.x < a.n_block_rows) {
+        const int64_t row = a.row_order ? (int64_t)__ldg(a.row_order + blockIdx.x) : (int64_t)blockIdx.x;
+        if (BWD) softmax_bwd_row<256, HT>(a, row, threadIdx.x, smem);
+        else softmax_row<256, HT>(a, row, threadIdx.x, smem);
+    } else {
+        const int64_t i = a.n_block_rows + ((int64_t)blockIdx.x - a.n_block_rows) * 8 + (threadIdx.x >> 5);
+        if (i >= a.n_rows) return;
+        const int64_t row = a.row_order ? (int64_t)__ldg(a.row_order + i) : i;
+        if (BWD) softmax_bwd_row<32, HT>(a, row, threadIdx.x & 31, smem);
+        else softmax_row<32, HT>(a, row, threadIdx.x & 31, smem);
+    }
+}
+
+template <bool BWD>
+static int launch_gat(GatArgs &a, cudaStream_t stream) {
+    if (a.n_rows < 0 || a.H < 1 || a.H > kMaxHeads) return TANGO_EINVAL;
+    if (a.n_rows == 0) return TANGO_OK;
+    if (!a.row_order) a.n_block_rows = 0;
+    if (a.n_block_rows < 0 || a.n_block_rows > a.n_rows) return TANGO_EINVAL;
+    const int64_t blocks = a.n_block_rows + ceil_div(a.n_rows - a.n_block_rows, 8);
+    if (blocks > 0x7fffffff) return TANGO_ESIZE;
+    const bool h4 = a.H == 4 && aligned(a.att, 16) && aligned(a.elq, 4) && (!BWD || (aligned(a.datt, 16) && aligned(a.dz, 16)));
+    if (h4) gat_softmax_kernel<4, BWD><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else gat_softmax_kernel<0, BWD><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}
+
+}  // namespace tango
+
+using namespace tango;
+
+extern "C" int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                                      const int32_t *row_order, int64_t n_block_rows, int64_t n_rows,
+                                      const int8_t *elq, const int8_t *erq, int h, const float *sl, const float *sr,
+                                      float slope, float *a, tango_stream_t stream) {
+    if (n_rows > 0 && (!indptr || !indices || !elq || !erq || !sl || !sr || !a)) return TANGO_EINVAL;
+    GatArgs g{indptr, indices, edge_ids, row_order, n_rows, n_block_rows, elq, erq, h, sl, sr, slope, a, nullptr, nullptr};
+    return launch_gat<false>(g, (cudaStream_t)stream);
+}
+
+extern "C" int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                                          const int32_t *row_order, int64_t n_block_rows, int64_t n_rows,
+                                          const int8_t *elq, const int8_t *erq, int h, const float *sl,
+                                          const float *sr, float slope, const float *a, const float *da, float *dz,
+                                          tango_stream_t stream) {
+    if (n_rows > 0 && (!indptr || !indices || !elq || !erq || !sl || !sr || !a || !da || !dz)) return TANGO_EINVAL;
+    GatArgs g{indptr, indices, edge_ids, row_order, n_rows, n_block_rows, elq, erq, h, sl, sr, slope,
+              const_cast<float *>(a), da, dz};
+    return launch_gat<true>(g, (cudaStream_t)stream);
+}

@@ -1,4 +1,4 @@
-// SDDMM over int8 node features (per-edge dot products / element-wise ops) and the fused GAT edge-softmax pass.
+// SDDMM over int8 node features: per-edge dot products and element-wise ops.
 //
 // dot: a group of G lanes owns one (edge, head) pair; every lane loads VEC bytes of the source row and of the
 // destination row, multiplies them with dp4a into an exact int32 and the group reduces by shuffle.  Edge endpoints
@@ -183,88 +183,6 @@ __global__ void __launch_bounds__(256) sddmm_elem_kernel(const ElemArgs a) {
     }
 }
 
-// ------------------------------------------------------------------------------------ fused GAT edge softmax
-// One warp per destination row, all heads.  Three sweeps over the row's slots (max, sum, write); the gathered
-// operands are one int8 per (source, head), so the sweeps hit L1/L2.
-__global__ void __launch_bounds__(256) gat_edge_softmax_kernel(const int32_t *__restrict__ indptr,
-                                                               const int32_t *__restrict__ indices,
-                                                               const int32_t *__restrict__ edge_ids, int64_t n_rows,
-                                                               const int8_t *__restrict__ elq,
-                                                               const int8_t *__restrict__ erq, int H,
-                                                               const float *__restrict__ sl_,
-                                                               const float *__restrict__ sr_, float slope,
-                                                               float *__restrict__ out) {
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= n_rows) return;
-    const float sl = __ldg(sl_), sr = __ldg(sr_);
-    const int beg = __ldg(indptr + row), end = __ldg(indptr + row + 1);
-    for (int h = 0; h < H; ++h) {
-        const float er = __fmul_rn((float)__ldg(erq + row * H + h), sr);
-        float m = -INFINITY;
-        for (int j = beg + lane; j < end; j += 32) {
-            float z = __fadd_rn(__fmul_rn((float)__ldg(elq + (int64_t)__ldg(indices + j) * H + h), sl), er);
-            z = z >= 0.f ? z : __fmul_rn(z, slope);
-            m = fmaxf(m, z);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        float sum = 0.f;
-        for (int j = beg + lane; j < end; j += 32) {
-            float z = __fadd_rn(__fmul_rn((float)__ldg(elq + (int64_t)__ldg(indices + j) * H + h), sl), er);
-            z = z >= 0.f ? z : __fmul_rn(z, slope);
-            sum += __expf(z - m);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        const float inv = 1.f / sum;
-        for (int j = beg + lane; j < end; j += 32) {
-            float z = __fadd_rn(__fmul_rn((float)__ldg(elq + (int64_t)__ldg(indices + j) * H + h), sl), er);
-            z = z >= 0.f ? z : __fmul_rn(z, slope);
-            const int64_t eid = edge_ids ? __ldg(edge_ids + j) : j;
-            out[eid * H + h] = __expf(z - m) * inv;
-        }
-    }
-}
-
-// Backward of the fused pass above.  For destination row v and head h, with a_j the softmax weights and g_j the
-// incoming gradient of a_j:  dz_j = a_j * (g_j - sum_k a_k g_k) * (z_j >= 0 ? 1 : slope), z_j recomputed from the
-// int8 operands.  One warp per row, two sweeps (the weighted sum, then the write).
-__global__ void __launch_bounds__(256) gat_edge_softmax_bwd_kernel(const int32_t *__restrict__ indptr,
-                                                                   const int32_t *__restrict__ indices,
-                                                                   const int32_t *__restrict__ edge_ids,
-                                                                   int64_t n_rows, const int8_t *__restrict__ elq,
-                                                                   const int8_t *__restrict__ erq, int H,
-                                                                   const float *__restrict__ sl_,
-                                                                   const float *__restrict__ sr_, float slope,
-                                                                   const float *__restrict__ att,
-                                                                   const float *__restrict__ datt,
-                                                                   float *__restrict__ dz) {
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= n_rows) return;
-    const float sl = __ldg(sl_), sr = __ldg(sr_);
-    const int beg = __ldg(indptr + row), end = __ldg(indptr + row + 1);
-    for (int h = 0; h < H; ++h) {
-        const float er = __fmul_rn((float)__ldg(erq + row * H + h), sr);
-        float dot = 0.f;
-        for (int j = beg + lane; j < end; j += 32) {
-            const int64_t eid = edge_ids ? __ldg(edge_ids + j) : j;
-            dot += __ldg(att + eid * H + h) * __ldg(datt + eid * H + h);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        for (int j = beg + lane; j < end; j += 32) {
-            const int64_t eid = edge_ids ? __ldg(edge_ids + j) : j;
-            const float z = __fadd_rn(__fmul_rn((float)__ldg(elq + (int64_t)__ldg(indices + j) * H + h), sl), er);
-            const float a = __ldg(att + eid * H + h);
-            float g = a * (__ldg(datt + eid * H + h) - dot);
-            if (z < 0.f) g *= slope;
-            dz[eid * H + h] = g;
-        }
-    }
-}
-
 static int pow2_ceil(int x) {
     int p = 1;
     while (p < x) p <<= 1;
@@ -335,33 +253,4 @@ extern "C" int tango_sddmm_elementwise(int op, const int32_t *src, const int32_t
         case TANGO_OP_MUL: return launch_elem<TANGO_OP_MUL>(a, vec4, stream);
         default: return launch_elem<TANGO_OP_DIV>(a, vec4, stream);
     }
-}
-
-extern "C" int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
-                                      int64_t n_rows, const int8_t *elq, const int8_t *erq, int h, const float *sl,
-                                      const float *sr, float slope, float *a, tango_stream_t stream_) {
-    cudaStream_t stream = (cudaStream_t)stream_;
-    if (n_rows < 0 || h < 1) return TANGO_EINVAL;
-    if (n_rows == 0) return TANGO_OK;
-    if (!indptr || !indices || !elq || !erq || !sl || !sr || !a) return TANGO_EINVAL;
-    const int64_t blocks = ceil_div(n_rows, 8);
-    gat_edge_softmax_kernel<<<(unsigned)blocks, 256, 0, stream>>>(indptr, indices, edge_ids, n_rows, elq, erq, h, sl,
-                                                                  sr, slope, a);
-    TANGO_LAUNCH_CHECK();
-    return TANGO_OK;
-}
-
-extern "C" int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
-                                          int64_t n_rows, const int8_t *elq, const int8_t *erq, int h, const float *sl,
-                                          const float *sr, float slope, const float *a, const float *da, float *dz,
-                                          tango_stream_t stream_) {
-    cudaStream_t stream = (cudaStream_t)stream_;
-    if (n_rows < 0 || h < 1) return TANGO_EINVAL;
-    if (n_rows == 0) return TANGO_OK;
-    if (!indptr || !indices || !elq || !erq || !sl || !sr || !a || !da || !dz) return TANGO_EINVAL;
-    const int64_t blocks = ceil_div(n_rows, 8);
-    gat_edge_softmax_bwd_kernel<<<(unsigned)blocks, 256, 0, stream>>>(indptr, indices, edge_ids, n_rows, elq, erq, h, sl,
-                                                                      sr, slope, a, da, dz);
-    TANGO_LAUNCH_CHECK();
-    return TANGO_OK;
 }

@@ -208,6 +208,7 @@ def rmat_graph(n_nodes: int, n_edges: int, seed: int, device="cpu", self_loops: 
 # Schedules for rows that are too long for one warp, and 1-D row partitions for multi-GPU training.
 # ----------------------------------------------------------------------------------------------------------------
 SPLIT_THRESHOLD = 4096
+BLOCK_ROW_NNZ = 1024
 SHORT_ROW_NNZ = 48      # rows up to this length are processed by a group of lanes instead of a whole warp
 UNIT_NNZ = 2048
 
@@ -237,6 +238,7 @@ class SpmmSchedule:
         # longest rows start first
         self.row_order = torch.argsort(row_deg, descending=True, stable=True).to(torch.int32)
         self.n_long = int((row_deg > SHORT_ROW_NNZ).sum())
+        self.n_block_rows = int((row_deg > BLOCK_ROW_NNZ).sum())   # rows that deserve a whole CTA in row-team kernels
         heavy = torch.nonzero(row_deg > threshold).flatten()
         self.n_heavy = int(heavy.numel())
         self.heavy_rows = heavy.to(torch.int32)

@@ -491,7 +491,10 @@ def gat_edge_softmax(g, elq, erq, sl, sr, slope: float = 0.2):
     erq = erq.reshape(erq.shape[0], -1).contiguous()
     a = torch.empty((g.num_edges(), h), dtype=torch.float32, device=elq.device)
     with torch.cuda.device(elq.device):
-        check(lib.tango_gat_edge_softmax(_p(indptr), _p(indices), _p(edge_ids), g.num_nodes(), _p(elq), _p(erq), h,
+        sched = _schedule(g, False)
+        order = sched.row_order if sched is not None else None
+        check(lib.tango_gat_edge_softmax(_p(indptr), _p(indices), _p(edge_ids), _p(order),
+                                         sched.n_block_rows if sched is not None else 0, g.num_nodes(), _p(elq), _p(erq), h,
                                          _p(sl), _p(sr), float(slope), _p(a), _stream()), "gat_edge_softmax")
     launch_counter[0] += 1
     return a
@@ -506,7 +509,10 @@ def gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, slope: float = 0.2):
     a, da = a.reshape(-1, h).contiguous(), da.reshape(-1, h).contiguous()
     dz = torch.empty_like(a)
     with torch.cuda.device(elq.device):
-        check(lib.tango_gat_edge_softmax_bwd(_p(indptr), _p(indices), _p(edge_ids), g.num_nodes(), _p(elq), _p(erq), h,
+        sched = _schedule(g, False)
+        order = sched.row_order if sched is not None else None
+        check(lib.tango_gat_edge_softmax_bwd(_p(indptr), _p(indices), _p(edge_ids), _p(order),
+                                             sched.n_block_rows if sched is not None else 0, g.num_nodes(), _p(elq), _p(erq), h,
                                              _p(sl), _p(sr), float(slope), _p(a), _p(da), _p(dz), _stream()),
               "gat_edge_softmax_bwd")
     launch_counter[0] += 1
