@@ -98,6 +98,7 @@ class Graph:
         self._csc = None
         self._plans = {}
         self._deg = {}
+        self._identity = {}   # fmt -> True when slot k of that format holds edge k (edge ids follow the format's order)
         self.n_classes = None
 
     # ---- DGL-like surface used by the operators and the layers
@@ -156,6 +157,7 @@ class Graph:
             indptr = torch.zeros(self._n + 1, dtype=torch.int64, device=self.device)
             torch.cumsum(counts, 0, out=indptr[1:])
             cached = (indptr.to(torch.int32), (key % self._n).to(torch.int32), perm.to(torch.int32))
+            self._identity[fmt] = bool((perm == torch.arange(perm.numel(), device=perm.device)).all())
             if fmt == "csr":
                 self._csr = cached
             else:
@@ -197,10 +199,17 @@ def add_self_loop(src: torch.Tensor, dst: torch.Tensor, n_nodes: int):
     return torch.cat([src[keep], loop]), torch.cat([dst[keep], loop])
 
 
-def rmat_graph(n_nodes: int, n_edges: int, seed: int, device="cpu", self_loops: bool = True) -> Graph:
+def rmat_graph(n_nodes: int, n_edges: int, seed: int, device="cpu", self_loops: bool = True,
+               edge_order: str = "dst") -> Graph:
+    """Seeded R-MAT graph.  edge_order='dst' numbers the edges by (destination, source), so that edge ids follow the
+    CSC order and every per-edge tensor is streamed by the destination-major kernels; 'append' keeps the generator's
+    (source, destination) order with the self loops appended, as dgl.add_self_loop leaves them."""
     src, dst = rmat_edges(n_nodes, n_edges, seed, device)
     if self_loops:
         src, dst = add_self_loop(src, dst, n_nodes)
+    if edge_order == "dst":
+        order = torch.argsort(dst.long() * n_nodes + src.long())
+        src, dst = src[order].contiguous(), dst[order].contiguous()
     return Graph(src, dst, n_nodes)
 
 

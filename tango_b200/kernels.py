@@ -357,6 +357,16 @@ def _incidence_from_coo(out, nodes, edge_ids, E, scale):
 
 
 # --------------------------------------------------------------------------------------------------- wrappers
+def _bundle(g, reverse: bool):
+    """(indptr, indices, edge_ids) of the CSR (reverse) or CSC; edge_ids is None when slot k stores edge k, so the
+    kernels skip the indirection (and the 4 bytes per edge it would stream)."""
+    indptr, indices, edge_ids = _bundle(g, reverse)
+    ident = getattr(g, "_identity", None)
+    if ident is not None and ident.get("csr" if reverse else "csc", False):
+        edge_ids = None
+    return indptr, indices, edge_ids
+
+
 def _schedule(g, reverse: bool) -> Optional[SpmmSchedule]:
     plans = getattr(g, "_plans", None)
     if plans is None:
@@ -446,21 +456,21 @@ def multi_cusparse_SPMM(g, N, E_T, scale, reverse=False):
     per-slot permutation by edge_ids that the reference performs with index_select happens inside the kernel."""
     assert E_T.ndim == 3 and N.ndim == 3, "E and N must be 3D tensors"
     assert E_T.size(1) == 1, "Cannot broadcast E"
-    indptr, indices, edge_ids = g.adj_csr if reverse else g.adj_csc
+    indptr, indices, edge_ids = _bundle(g, reverse)
     E = E_T.reshape(E_T.shape[0], -1).t().contiguous()  # [E, H]
     return _u_mul_e_spmm(indptr, indices, edge_ids, N, E, scale, _schedule(g, reverse))
 
 
 def spmm_u_mul_e_int8(g, N, E, scale, reverse=False):
     """Same product with the edge weights given as int8 [E, H] in edge-id order (no transposed copy)."""
-    indptr, indices, edge_ids = g.adj_csr if reverse else g.adj_csc
+    indptr, indices, edge_ids = _bundle(g, reverse)
     return _u_mul_e_spmm(indptr, indices, edge_ids, N, E.reshape(E.shape[0], -1), scale, _schedule(g, reverse))
 
 
 def incidence_SPMM(g, E, scaleE, reverse=False):
     """cuda/kernels.py:139-152: sums int8 edge features into their destination (or source, if reverse) nodes."""
     assert E.is_cuda and scaleE.is_cuda
-    indptr, _, edge_ids = g.adj_csr if reverse else g.adj_csc
+    indptr, _, edge_ids = _bundle(g, reverse)
     out_shape = (g.num_nodes(),) + E.shape[1:]
     dim = E.numel() // E.size(0)
     out = torch.empty((g.num_nodes(), dim), dtype=torch.float32, device=E.device)
@@ -485,7 +495,7 @@ def multi_cusparse_SPMV(g, N_T, E_T, scale, reverse=False):
 
 def gat_edge_softmax(g, elq, erq, sl, sr, slope: float = 0.2):
     """Fused u_add_v -> LeakyReLU -> edge softmax over incoming edges; returns fp32 [E, H] in edge-id order."""
-    indptr, indices, edge_ids = g.adj_csc
+    indptr, indices, edge_ids = _bundle(g, False)
     h = elq.shape[1]
     elq = elq.reshape(elq.shape[0], -1).contiguous()
     erq = erq.reshape(erq.shape[0], -1).contiguous()
@@ -502,7 +512,7 @@ def gat_edge_softmax(g, elq, erq, sl, sr, slope: float = 0.2):
 
 def gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, slope: float = 0.2):
     """Gradient of `gat_edge_softmax` with respect to the edge logits (before the LeakyReLU); fp32 [E, H]."""
-    indptr, indices, edge_ids = g.adj_csc
+    indptr, indices, edge_ids = _bundle(g, False)
     h = elq.shape[1]
     elq = elq.reshape(elq.shape[0], -1).contiguous()
     erq = erq.reshape(erq.shape[0], -1).contiguous()

@@ -25,8 +25,8 @@ def _scale_t(s):
 
 def _graph(n, e, seed, loops=True):
     from tango_b200.graph import rmat_graph
-    g = rmat_graph(n, e, seed, device="cuda", self_loops=loops)
-    return g
+    # edge ids in generation order (not CSC order): the kernels must follow the edge_ids indirection
+    return rmat_graph(n, e, seed, device="cuda", self_loops=loops, edge_order="append")
 
 
 def _np_graph(g):
@@ -324,3 +324,22 @@ def test_empty_graph_and_rows(cuda):
     assert out.shape == (10, 16) and float(out.abs().sum()) == 0.0
     o, _ = K.mySDDMM_int8(g, "dot", nq, nq, _scale_t(1.0), _scale_t(1.0), False)
     assert o.shape == (0, 1)
+
+
+def test_csc_numbered_graph_skips_edge_id_indirection(cuda):
+    """With edges numbered in CSC order the wrappers pass no edge_ids; results must match the indirect path."""
+    from tango_b200 import kernels as K
+    from tango_b200.graph import rmat_graph
+    g = rmat_graph(300, 4000, 13, device="cuda")            # edge_order="dst"
+    assert g.adj_csc is not None and g._identity["csc"] and K._bundle(g, False)[2] is None
+    (csr, csc, src, dst) = _np_graph(g)
+    np.testing.assert_array_equal(csc[2], np.arange(g.num_edges()))
+    rng = np.random.default_rng(3)
+    nq = rng.integers(-127, 128, (300, 4, 16), dtype=np.int8)
+    eq = rng.integers(-127, 128, (g.num_edges(), 4), dtype=np.int8)
+    s = np.float32(0.01)
+    for reverse, (indptr, indices, eids) in ((False, csc), (True, csr)):
+        out = K.spmm_u_mul_e_int8(g, _dev(nq), _dev(eq), _scale_t(s), reverse).cpu().numpy()
+        np.testing.assert_array_equal(out, O.spmm_u_mul_e(indptr, indices, eids, nq, eq, s))
+    np.testing.assert_array_equal(K.incidence_SPMM(g, _dev(eq), _scale_t(s)).cpu().numpy(),
+                                  O.spmm_incidence(csc[0], csc[2], eq, s))
