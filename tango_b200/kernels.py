@@ -360,7 +360,7 @@ def _incidence_from_coo(out, nodes, edge_ids, E, scale):
 def _bundle(g, reverse: bool):
     """(indptr, indices, edge_ids) of the CSR (reverse) or CSC; edge_ids is None when slot k stores edge k, so the
     kernels skip the indirection (and the 4 bytes per edge it would stream)."""
-    indptr, indices, edge_ids = _bundle(g, reverse)
+    indptr, indices, edge_ids = g.adj_csr if reverse else g.adj_csc
     ident = getattr(g, "_identity", None)
     if ident is not None and ident.get("csr" if reverse else "csc", False):
         edge_ids = None
