@@ -244,6 +244,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             if (p.mode == 0) sc = __fmul_rn(__ldg(p.sa), __ldg(p.sb));
             const bool vec_ok = p.mode == 0 ? ((p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0)
                                             : false;
+            // n0 and every 32-column chunk start are even, so an even ldo keeps each row's chunk 8-byte aligned
+            const bool vec2_ok = p.mode == 0 && (p.ldo & 1) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0;
             for (int c0 = 0; c0 < p.n_tile; c0 += 32) {
                 const int col0 = n0 + c0;
                 const int width = min(32, p.n_tile - c0);  // 32, or 16 for the last chunk
@@ -283,6 +285,19 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                                 const uint32_t e[4] = {t.x, t.y, t.z, t.w};
                                 for (int i = 0; i < 4 && gcol + i < p.N; ++i) o[i] = __uint_as_float(e[i]);
                             }
+                        }
+                    }
+                } else if (p.mode == 0 && vec2_ok) {
+                    // rows that are only 8-byte aligned (e.g. ldo = 602): half a warp per row, 64-bit stores
+#pragma unroll 4
+                    for (int it = 0; it < 16; ++it) {
+                        const int rr = it * 2 + (lane >> 4), cv = (lane & 15) * 2;
+                        const int grow = m0 + q * 32 + rr, gcol = col0 + cv;
+                        if (grow < p.M && cv < width && gcol < p.N) {
+                            const uint2 t = *reinterpret_cast<const uint2 *>(tile + rr * kTileLd + cv);
+                            float *o = p.out + (int64_t)grow * p.ldo + gcol;
+                            if (gcol + 2 <= p.N) *reinterpret_cast<uint2 *>(o) = t;
+                            else o[0] = __uint_as_float(t.x);
                         }
                     }
                 } else {
