@@ -338,6 +338,226 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Persistent, B-stationary variant for the products whose B operand (one N-tile of it, all of K) fits in shared
+// memory next to a ring of A tiles -- the forward and dX products of the layer (W_q is a few hundred KB at most).
+// One CTA per SM keeps its B tile resident, streams 128-row A tiles through a TMA ring, and alternates between two
+// accumulators in tensor memory so that the epilogue of tile i (TMEM -> registers -> shared -> coalesced stores)
+// overlaps the loads and MMAs of tile i+1.  Same roles and the same bounded waits as igemm_kernel.
+constexpr int kStageLd = 20;  // words per staged epilogue row (16 columns + pad), 16-byte aligned
+
+__global__ void __launch_bounds__(192, 1)
+igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                        const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_a_full[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_a_empty[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_b_full;
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t b_base = smem_base;                                   // kb_total x b_bytes, resident
+    const uint32_t a_base = b_base + (uint32_t)p.kb_total * p.b_bytes;   // stages x 16 KiB ring
+    const uint32_t st_off = (a_base - smem_u32(smem_raw)) + (uint32_t)p.stages * kABytes;  // epilogue staging
+    const int n0 = blockIdx.y * p.n_tile;
+    const int m_tiles = (p.M + kTileM - 1) / kTileM;
+    const uint32_t acc_cols = p.tmem_cols >> 1;   // two accumulators side by side
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&bar_a_full[s]), 1);
+            mbar_init(smem_u32(&bar_a_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_b_full), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_acc_full[b]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[b]), 4);   // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                     "r"(p.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = s_tmem_base;
+    volatile int *abort_flag = &s_abort;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_b) : "memory");
+            const uint32_t bfull = smem_u32(&bar_b_full);
+            mbar_expect_tx(bfull, (uint32_t)p.kb_total * p.b_bytes);
+            for (int kb = 0; kb < p.kb_total; ++kb) {
+                const uint32_t dst = b_base + kb * p.b_bytes;
+                if (!p.b_mn) {
+                    tma_load_2d(dst, &tm_b, bfull, kb * kBlockK, n0);
+                } else {
+                    for (int j = 0; j < p.b_boxes; ++j)
+                        tma_load_2d(dst + j * kABytes, &tm_b, bfull, n0 + j * 128, kb * kBlockK);
+                }
+            }
+            int it = 0;
+            bool ok = true;
+            for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
+                for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
+                    const int s = it % p.stages;
+                    const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+                    if (!mbar_wait(smem_u32(&bar_a_empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t full = smem_u32(&bar_a_full[s]);
+                    mbar_expect_tx(full, kABytes);
+                    if (!p.a_mn) tma_load_2d(a_base + s * kABytes, &tm_a, full, kb * kBlockK, mt * kTileM);
+                    else tma_load_2d(a_base + s * kABytes, &tm_a, full, mt * kTileM, kb * kBlockK);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn << 15) |
+                                   ((uint32_t)p.b_mn << 16) | ((uint32_t)(p.n_tile >> 3) << 17) |
+                                   ((uint32_t)(kTileM >> 4) << 24);
+            const uint32_t a_kstep = p.a_mn ? 32u * 128u : 32u, b_kstep = p.b_mn ? 32u * 128u : 32u;
+            const uint32_t a_lbo = p.a_mn ? (uint32_t)kABytes : 16u, b_lbo = p.b_mn ? (uint32_t)kABytes : 16u;
+            bool ok = mbar_wait(smem_u32(&bar_b_full), 0u, abort_flag);
+            int it = 0, t = 0;
+            for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x, ++t) {
+                const int buf = t & 1;
+                const uint32_t acc_ph = (uint32_t)(t >> 1) & 1u;
+                if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + buf * acc_cols;
+                for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
+                    const int s = it % p.stages;
+                    const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+                    if (!mbar_wait(smem_u32(&bar_a_full[s]), ph, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_src = a_base + s * kABytes, b_src = b_base + kb * p.b_bytes;
+                    const int nk = min(4, (p.K - kb * kBlockK + 31) >> 5);
+                    for (int k = 0; k < nk; ++k)
+                        umma_i8(tmem_d, make_smem_desc(a_src + k * a_kstep, a_lbo, 1024u),
+                                make_smem_desc(b_src + k * b_kstep, b_lbo, 1024u), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(smem_u32(&bar_a_empty[s]));
+                }
+                if (ok) umma_commit(smem_u32(&bar_acc_full[buf]));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;
+        uint32_t *tile = reinterpret_cast<uint32_t *>(smem_raw + st_off) + q * 32 * kStageLd;
+        const float sc = __fmul_rn(__ldg(p.sa), __ldg(p.sb));
+        const bool vec_ok = (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+        const bool vec2_ok = (p.ldo & 1) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0;
+        float amax = 0.f;
+        int t = 0;
+        bool ok = true;
+        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x, ++t) {
+            const int buf = t & 1;
+            const uint32_t acc_ph = (uint32_t)(t >> 1) & 1u;
+            ok = mbar_wait(smem_u32(&bar_acc_full[buf]), acc_ph, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int m0 = mt * kTileM;
+            const int row = m0 + q * 32 + lane;
+            for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+                const int col0 = n0 + c0;
+                uint32_t r[16];
+                tmem_ld16(tmem_base + buf * acc_cols + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int col = col0 + i;
+                    float v = __fmul_rn((float)(int)r[i], sc);
+                    if (p.bias && col < p.N) v = __fadd_rn(v, __ldg(p.bias + col));
+                    if (col < p.N && row < p.M) amax = fmaxf(amax, fabsf(v));
+                    r[i] = __float_as_uint(v);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    *reinterpret_cast<uint4 *>(tile + lane * kStageLd + 4 * i) =
+                        make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+                __syncwarp();
+                if (vec_ok) {
+#pragma unroll
+                    for (int itr = 0; itr < 4; ++itr) {      // 4 lanes x 16 B per row, 8 rows per step
+                        const int rr = itr * 8 + (lane >> 2), cv = (lane & 3) * 4;
+                        const int grow = m0 + q * 32 + rr, gcol = col0 + cv;
+                        if (grow < p.M && gcol < p.N) {
+                            const uint4 v4 = *reinterpret_cast<const uint4 *>(tile + rr * kStageLd + cv);
+                            float *o = p.out + (int64_t)grow * p.ldo + gcol;
+                            if (gcol + 4 <= p.N) {
+                                *reinterpret_cast<uint4 *>(o) = v4;
+                            } else {
+                                const uint32_t e[4] = {v4.x, v4.y, v4.z, v4.w};
+                                for (int i = 0; i < 4 && gcol + i < p.N; ++i) o[i] = __uint_as_float(e[i]);
+                            }
+                        }
+                    }
+                } else if (vec2_ok) {
+#pragma unroll
+                    for (int itr = 0; itr < 8; ++itr) {      // 8 lanes x 8 B per row, 4 rows per step
+                        const int rr = itr * 4 + (lane >> 3), cv = (lane & 7) * 2;
+                        const int grow = m0 + q * 32 + rr, gcol = col0 + cv;
+                        if (grow < p.M && gcol < p.N) {
+                            const uint2 v2 = *reinterpret_cast<const uint2 *>(tile + rr * kStageLd + cv);
+                            float *o = p.out + (int64_t)grow * p.ldo + gcol;
+                            if (gcol + 2 <= p.N) *reinterpret_cast<uint2 *>(o) = v2;
+                            else o[0] = __uint_as_float(v2.x);
+                        }
+                    }
+                } else {
+                    for (int itr = 0; itr < 16; ++itr) {     // 16 lanes x 4 B per row, 2 rows per step
+                        const int rr = itr * 2 + (lane >> 4), cv = lane & 15;
+                        const int grow = m0 + q * 32 + rr, gcol = col0 + cv;
+                        if (grow < p.M && gcol < p.N)
+                            p.out[(int64_t)grow * p.ldo + gcol] = __uint_as_float(tile[rr * kStageLd + cv]);
+                    }
+                }
+                __syncwarp();
+            }
+            // this warp has read its quarter of the accumulator: hand the buffer back to the MMA issuer
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_acc_empty[buf])) : "memory");
+        }
+        if (p.absmax) {
+            amax = warp_max(amax);
+            if (lane == 0 && amax > 0.f) {
+                const float s = __fdiv_rn(amax, 127.0f);
+                if (s > __ldcg(p.absmax)) atomic_max_nonneg(p.absmax, s);
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, TANGO_ETIMEOUT);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
+                     : "memory");
+    }
+}
+
 __global__ void __launch_bounds__(256) dequant_ws_kernel(const int32_t *__restrict__ ws, int64_t ldws, int64_t rows,
                                                          int64_t cols, const float *__restrict__ sa,
                                                          const float *__restrict__ sb, float *__restrict__ out,
@@ -433,6 +653,33 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
     else rc = make_map(&tm_b, c.b, c.N, c.K, c.ldb, 128, kBlockK);
     if (rc) return rc;
 
+    // Persistent B-stationary kernel when one N-tile of B (all of K) fits in shared memory beside >= 3 A stages.
+    if (c.mode == 0 && splits == 1) {
+        const int64_t budget = 227 * 1024 - 2048;   // dynamic limit minus static barriers and alignment slack
+        const int64_t b_res = (int64_t)p.kb_total * p.b_bytes;
+        const int64_t staging = 4 * 32 * kStageLd * 4;
+        int64_t st = (budget - 1024 - b_res - staging) / kABytes;
+        if (st > kMaxStages) st = kMaxStages;
+        if (st >= 3) {
+            GemmParams pp = p;
+            pp.stages = (int)st;
+            uint32_t cols = 32;
+            while ((int)cols < p.n_tile) cols <<= 1;
+            pp.tmem_cols = cols * 2;
+            const size_t smem_p = (size_t)(1024 + b_res + st * kABytes + staging);
+            TANGO_CUDA_TRY(cudaFuncSetAttribute(igemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)(227 * 1024 - 1024)));
+            const int64_t m_tiles = ceil_div(c.M, kTileM);
+            int64_t gx = kNumSMs / n_tiles;
+            if (gx < 1) gx = 1;
+            if (gx > m_tiles) gx = m_tiles;
+            const dim3 pgrid((unsigned)gx, (unsigned)n_tiles, 1);
+            if (pgrid.y > 65535) return TANGO_ESIZE;
+            igemm_persistent_kernel<<<pgrid, 192, smem_p, stream>>>(tm_a, tm_b, pp);
+            TANGO_LAUNCH_CHECK();
+            return TANGO_OK;
+        }
+    }
     const size_t smem = (size_t)p.stages * stage_bytes + 1024;
     // per-device attribute; setting it on every call keeps the entry point free of global state
     TANGO_CUDA_TRY(cudaFuncSetAttribute(igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
