@@ -132,14 +132,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+        "[%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -356,8 +354,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 // One CTA per SM keeps its B tile resident, streams 128-row A tiles through a TMA ring, and alternates between two
 // accumulators in tensor memory so that the epilogue of tile i (TMEM -> registers -> shared -> coalesced stores)
 // overlaps the loads and MMAs of tile i+1.  Same roles and the same bounded waits as igemm_kernel.
+constexpr int kStageLd = 20;  // words per staged epilogue row (16 columns + pad), 16-byte aligned
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(192, 1)
 igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                         const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -373,6 +372,7 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t b_base = smem_base;                                   // kb_total x b_bytes, resident
     const uint32_t a_base = b_base + (uint32_t)p.kb_total * p.b_bytes;   // stages x 16 KiB ring
+    const uint32_t st_off = (a_base - smem_u32(smem_raw)) + (uint32_t)p.stages * kABytes;  // epilogue staging
     const int n0 = blockIdx.y * p.n_tile;
     const int m_tiles = (p.M + kTileM - 1) / kTileM;
     const uint32_t acc_cols = p.tmem_cols >> 1;   // two accumulators side by side
@@ -386,7 +386,7 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         mbar_init(smem_u32(&bar_b_full), 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bar_acc_full[b]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[b]), 8);   // one arrival per epilogue warp
+            mbar_init(smem_u32(&bar_acc_empty[b]), 4);   // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -466,47 +466,15 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..9)
-        // Eight warps drain an accumulator: warp w reads TMEM lanes 32*(w%4).. and every other 32-column chunk.
-        // A chunk is loaded with one tcgen05.ld (32 registers = 32 columns of this lane's row); the load of the next
-        // chunk is issued before the current one is converted and stored, so TMEM latency overlaps the stores.
-        // Each lane writes 128 contiguous bytes of its own row per chunk.
-        const int q = warp & 3, half = (warp - 2) >> 2;
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;
+        uint32_t *tile = reinterpret_cast<uint32_t *>(smem_raw + st_off) + q * 32 * kStageLd;
         const float sc = __fmul_rn(__ldg(p.sa), __ldg(p.sb));
         const bool vec_ok = (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
         const bool vec2_ok = (p.ldo & 1) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0;
-        const int n_chunks = (p.n_tile + 31) >> 5;   // the last chunk may hold 16 valid accumulator columns only
         float amax = 0.f;
         int t = 0;
         bool ok = true;
-
-        auto emit = [&](uint32_t (&r)[32], int row, int col0) {
-            if (row >= p.M) return;
-            float *o = p.out + (int64_t)row * p.ldo + col0;
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                float v[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int col = col0 + 4 * g + i;
-                    v[i] = __fmul_rn((float)(int)r[4 * g + i], sc);
-                    if (p.bias && col < p.N) v[i] = __fadd_rn(v[i], __ldg(p.bias + col));
-                    if (col < p.N) amax = fmaxf(amax, fabsf(v[i]));
-                }
-                const int c = col0 + 4 * g;
-                if (c + 4 <= p.N && vec_ok) {
-                    *reinterpret_cast<float4 *>(o + 4 * g) = make_float4(v[0], v[1], v[2], v[3]);
-                } else if (c + 4 <= p.N && vec2_ok) {
-                    *reinterpret_cast<float2 *>(o + 4 * g) = make_float2(v[0], v[1]);
-                    *reinterpret_cast<float2 *>(o + 4 * g + 2) = make_float2(v[2], v[3]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (c + i < p.N) o[4 * g + i] = v[i];
-                }
-            }
-        };
-
         for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x, ++t) {
             const int buf = t & 1;
             const uint32_t acc_ph = (uint32_t)(t >> 1) & 1u;
@@ -514,23 +482,70 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = mt * kTileM + q * 32 + lane;
+            const int m0 = mt * kTileM;
+            const int row = m0 + q * 32 + lane;
             const uint32_t tbase = tmem_base + buf * acc_cols + ((uint32_t)(q * 32) << 16);
-            uint32_t ra[32], rb[32];
-            int c = half;
-            if (c < n_chunks) tmem_ld32_nowait(tbase + (uint32_t)(c * 32), ra);
-            while (c < n_chunks) {
+            uint32_t nxt[16];
+            tmem_ld16_nowait(tbase, nxt);
+            for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+                const int col0 = n0 + c0;
+                uint32_t r[16];
                 tmem_ld_wait();
-                if (c + 2 < n_chunks) tmem_ld32_nowait(tbase + (uint32_t)((c + 2) * 32), rb);
-                emit(ra, row, n0 + c * 32);
-                c += 2;
-                if (c >= n_chunks) break;
-                tmem_ld_wait();
-                if (c + 2 < n_chunks) tmem_ld32_nowait(tbase + (uint32_t)((c + 2) * 32), ra);
-                emit(rb, row, n0 + c * 32);
-                c += 2;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) r[i] = nxt[i];
+                if (c0 + 16 < p.n_tile) tmem_ld16_nowait(tbase + (uint32_t)(c0 + 16), nxt);   // overlaps the stores below
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int col = col0 + i;
+                    float v = __fmul_rn((float)(int)r[i], sc);
+                    if (p.bias && col < p.N) v = __fadd_rn(v, __ldg(p.bias + col));
+                    if (col < p.N && row < p.M) amax = fmaxf(amax, fabsf(v));
+                    r[i] = __float_as_uint(v);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    *reinterpret_cast<uint4 *>(tile + lane * kStageLd + 4 * i) =
+                        make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+                __syncwarp();
+                if (vec_ok) {
+#pragma unroll
+                    for (int itr = 0; itr < 4; ++itr) {      // 4 lanes x 16 B per row, 8 rows per step
+                        const int rr = itr * 8 + (lane >> 2), cv = (lane & 3) * 4;
+                        const int grow = m0 + q * 32 + rr, gcol = col0 + cv;
+                        if (grow < p.M && gcol < p.N) {
+                            const uint4 v4 = *reinterpret_cast<const uint4 *>(tile + rr * kStageLd + cv);
+                            float *o = p.out + (int64_t)grow * p.ldo + gcol;
+                            if (gcol + 4 <= p.N) {
+                                *reinterpret_cast<uint4 *>(o) = v4;
+                            } else {
+                                const uint32_t e[4] = {v4.x, v4.y, v4.z, v4.w};
+                                for (int i = 0; i < 4 && gcol + i < p.N; ++i) o[i] = __uint_as_float(e[i]);
+                            }
+                        }
+                    }
+                } else if (vec2_ok) {
+#pragma unroll
+                    for (int itr = 0; itr < 8; ++itr) {      // 8 lanes x 8 B per row, 4 rows per step
+                        const int rr = itr * 4 + (lane >> 3), cv = (lane & 7) * 2;
+                        const int grow = m0 + q * 32 + rr, gcol = col0 + cv;
+                        if (grow < p.M && gcol < p.N) {
+                            const uint2 v2 = *reinterpret_cast<const uint2 *>(tile + rr * kStageLd + cv);
+                            float *o = p.out + (int64_t)grow * p.ldo + gcol;
+                            if (gcol + 2 <= p.N) *reinterpret_cast<uint2 *>(o) = v2;
+                            else o[0] = __uint_as_float(v2.x);
+                        }
+                    }
+                } else {
+                    for (int itr = 0; itr < 16; ++itr) {     // 16 lanes x 4 B per row, 2 rows per step
+                        const int rr = itr * 2 + (lane >> 4), cv = lane & 15;
+                        const int grow = m0 + q * 32 + rr, gcol = col0 + cv;
+                        if (grow < p.M && gcol < p.N)
+                            p.out[(int64_t)grow * p.ldo + gcol] = __uint_as_float(tile[rr * kStageLd + cv]);
+                    }
+                }
+                __syncwarp();
             }
-            // this warp has read its share of the accumulator: hand the buffer back to the MMA issuer
+            // this warp has read its quarter of the accumulator: hand the buffer back to the MMA issuer
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0)
@@ -658,7 +673,7 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
     if (c.mode == 0 && splits == 1) {
         const int64_t budget = 227 * 1024 - 2048;   // dynamic limit minus static barriers and alignment slack
         const int64_t b_res = (int64_t)p.kb_total * p.b_bytes;
-        const int64_t staging = 0;
+        const int64_t staging = 4 * 32 * kStageLd * 4;
         int64_t st = (budget - 1024 - b_res - staging) / kABytes;
         if (st > kMaxStages) st = kMaxStages;
         if (st >= 3) {
@@ -676,7 +691,7 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
             if (gx > m_tiles) gx = m_tiles;
             const dim3 pgrid((unsigned)gx, (unsigned)n_tiles, 1);
             if (pgrid.y > 65535) return TANGO_ESIZE;
-            igemm_persistent_kernel<<<pgrid, 320, smem_p, stream>>>(tm_a, tm_b, pp);
+            igemm_persistent_kernel<<<pgrid, 192, smem_p, stream>>>(tm_a, tm_b, pp);
             TANGO_LAUNCH_CHECK();
             return TANGO_OK;
         }
