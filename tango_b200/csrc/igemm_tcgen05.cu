@@ -354,9 +354,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 // One CTA per SM keeps its B tile resident, streams 128-row A tiles through a TMA ring, and alternates between two
 // accumulators in tensor memory so that the epilogue of tile i (TMEM -> registers -> shared -> coalesced stores)
 // overlaps the loads and MMAs of tile i+1.  Same roles and the same bounded waits as igemm_kernel.
-constexpr int kStageLd = 20;  // words per staged epilogue row (16 columns + pad), 16-byte aligned
+constexpr int kStageLd = 16;  // words per staged epilogue row (16 columns, no padding needed for 128-bit accesses)
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                         const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -386,7 +386,7 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         mbar_init(smem_u32(&bar_b_full), 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bar_acc_full[b]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[b]), 4);   // one arrival per epilogue warp
+            mbar_init(smem_u32(&bar_acc_empty[b]), 8);   // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -466,12 +466,18 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..5)
-        const int q = warp & 3;
-        uint32_t *tile = reinterpret_cast<uint32_t *>(smem_raw + st_off) + q * 32 * kStageLd;
+        // ------------------------------------------------------------------ epilogue (warps 2..9)
+        // Eight warps drain an accumulator -- one warp runs a long dependent chain per chunk (TMEM load, convert,
+        // stage, store), so four warps alone were the kernel's bottleneck.  Warp w reads TMEM lanes 32*(w%4).. and
+        // every other 16-column chunk; the next chunk's tcgen05.ld is issued before the current chunk is processed.
+        // Values go through a 32 x 16 word tile in shared memory (unpadded: 128-bit accesses of 8 lanes cover whole
+        // 128-byte lines) so that four lanes write one row's 64 contiguous bytes.
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        uint32_t *tile = reinterpret_cast<uint32_t *>(smem_raw + st_off) + (warp - 2) * 32 * kStageLd;
         const float sc = __fmul_rn(__ldg(p.sa), __ldg(p.sb));
         const bool vec_ok = (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
         const bool vec2_ok = (p.ldo & 1) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0;
+        const bool has_bias = p.bias != nullptr, want_max = p.absmax != nullptr;
         float amax = 0.f;
         int t = 0;
         bool ok = true;
@@ -486,20 +492,20 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             const int row = m0 + q * 32 + lane;
             const uint32_t tbase = tmem_base + buf * acc_cols + ((uint32_t)(q * 32) << 16);
             uint32_t nxt[16];
-            tmem_ld16_nowait(tbase, nxt);
-            for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+            if (half * 16 < p.n_tile) tmem_ld16_nowait(tbase + (uint32_t)(half * 16), nxt);
+            for (int c0 = half * 16; c0 < p.n_tile; c0 += 32) {
                 const int col0 = n0 + c0;
                 uint32_t r[16];
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 16; ++i) r[i] = nxt[i];
-                if (c0 + 16 < p.n_tile) tmem_ld16_nowait(tbase + (uint32_t)(c0 + 16), nxt);   // overlaps the stores below
+                if (c0 + 32 < p.n_tile) tmem_ld16_nowait(tbase + (uint32_t)(c0 + 32), nxt);   // overlaps the work below
+                const bool full_cols = col0 + 16 <= p.N;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const int col = col0 + i;
                     float v = __fmul_rn((float)(int)r[i], sc);
-                    if (p.bias && col < p.N) v = __fadd_rn(v, __ldg(p.bias + col));
-                    if (col < p.N && row < p.M) amax = fmaxf(amax, fabsf(v));
+                    if (has_bias && (full_cols || col0 + i < p.N)) v = __fadd_rn(v, __ldg(p.bias + col0 + i));
+                    if (want_max && row < p.M && (full_cols || col0 + i < p.N)) amax = fmaxf(amax, fabsf(v));
                     r[i] = __float_as_uint(v);
                 }
 #pragma unroll
@@ -545,7 +551,7 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
                 }
                 __syncwarp();
             }
-            // this warp has read its quarter of the accumulator: hand the buffer back to the MMA issuer
+            // this warp has read its share of the accumulator: hand the buffer back to the MMA issuer
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0)
@@ -673,7 +679,7 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
     if (c.mode == 0 && splits == 1) {
         const int64_t budget = 227 * 1024 - 2048;   // dynamic limit minus static barriers and alignment slack
         const int64_t b_res = (int64_t)p.kb_total * p.b_bytes;
-        const int64_t staging = 4 * 32 * kStageLd * 4;
+        const int64_t staging = 8 * 32 * kStageLd * 4;
         int64_t st = (budget - 1024 - b_res - staging) / kABytes;
         if (st > kMaxStages) st = kMaxStages;
         if (st >= 3) {
@@ -691,7 +697,7 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
             if (gx > m_tiles) gx = m_tiles;
             const dim3 pgrid((unsigned)gx, (unsigned)n_tiles, 1);
             if (pgrid.y > 65535) return TANGO_ESIZE;
-            igemm_persistent_kernel<<<pgrid, 192, smem_p, stream>>>(tm_a, tm_b, pp);
+            igemm_persistent_kernel<<<pgrid, 320, smem_p, stream>>>(tm_a, tm_b, pp);
             TANGO_LAUNCH_CHECK();
             return TANGO_OK;
         }
