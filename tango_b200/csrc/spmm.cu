@@ -116,7 +116,7 @@ __device__ __forceinline__ void gather_segment(int (&acc)[VEC], int beg, int end
     const int head = (MODE == MODE_WEIGHT_LANE) ? ld_off / a.D : 0;
     const int8_t *base = a.feat + ld_off;
     const int8_t *wbase = (MODE == MODE_WEIGHT_LANE) ? a.ew + head : a.ew;
-    const int64_t ld = a.ld;
+    const uint32_t ld = (uint32_t)a.ld;   // 32 x 32 -> 64-bit products: one wide multiply per gathered row
     const int H = a.H;
     int j0 = beg;
     if (kFour && G >= U) {
@@ -133,17 +133,17 @@ __device__ __forceinline__ void gather_segment(int (&acc)[VEC], int beg, int end
                 nxt_idx = a.indices ? __ldg(a.indices + j0 + 32 + lane) : j0 + 32 + lane;
                 if (MODE != MODE_COPY) nxt_eid = a.edge_ids ? __ldg(a.edge_ids + j0 + 32 + lane) : j0 + 32 + lane;
             }
-            for (int s = 0; s < G; s += U) {
+            for (int s = 0, lane0 = grp; s < G; s += U, lane0 += U * NB) {
                 VecLoad<VEC> v[U];
                 uint32_t wvec = 0x01010101u;
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int src_lane = (s + u) * NB + grp;
+                    const int src_lane = lane0 + u * NB;
                     const int idx = __shfl_sync(0xffffffffu, my_idx, src_lane);
-                    v[u].load(base + (int64_t)idx * ld);
+                    v[u].load(base + (uint64_t)(uint32_t)idx * ld);
                     if (MODE == MODE_WEIGHT_LANE) {
                         const int eid = __shfl_sync(0xffffffffu, my_eid, src_lane);
-                        const uint32_t wb = (uint32_t)(uint8_t)__ldg(wbase + (int64_t)eid * H);
+                        const uint32_t wb = (uint32_t)(uint8_t)__ldg(wbase + (uint64_t)(uint32_t)eid * (uint32_t)H);
                         wvec = (u == 0) ? wb : (wvec | (wb << (8 * u)));
                     }
                 }
@@ -173,9 +173,9 @@ __device__ __forceinline__ void gather_segment(int (&acc)[VEC], int beg, int end
                 if (s + u >= steps) idx = -1;
                 wsel[u] = 0; wrow[u] = nullptr;
                 if (idx >= 0) {
-                    v[u].load(base + (int64_t)idx * ld);
-                    if (MODE == MODE_WEIGHT_LANE) wsel[u] = (uint32_t)(uint8_t)__ldg(wbase + (int64_t)eid * H);
-                    if (MODE == MODE_WEIGHT_ELEM) wrow[u] = a.ew + (int64_t)eid * H;
+                    v[u].load(base + (uint64_t)(uint32_t)idx * ld);
+                    if (MODE == MODE_WEIGHT_LANE) wsel[u] = (uint32_t)(uint8_t)__ldg(wbase + (uint64_t)(uint32_t)eid * (uint32_t)H);
+                    if (MODE == MODE_WEIGHT_ELEM) wrow[u] = a.ew + (uint64_t)(uint32_t)eid * (uint32_t)H;
                 } else {
                     v[u].zero();
                 }
@@ -310,10 +310,10 @@ __global__ void __launch_bounds__(128) spmm_short_kernel(const SpmmArgs a) {
                 for (int u = 0; u < 4; ++u) {
                     if (j + u < end) {
                         const int idx = a.indices ? __ldg(a.indices + j + u) : j + u;
-                        v[u].load(base + (int64_t)idx * a.ld);
+                        v[u].load(base + (uint64_t)(uint32_t)idx * (uint32_t)a.ld);
                         if (MODE == MODE_WEIGHT_LANE) {
                             const int eid = a.edge_ids ? __ldg(a.edge_ids + j + u) : j + u;
-                            wvec |= (uint32_t)(uint8_t)__ldg(a.ew + (int64_t)eid * a.H + head) << (8 * u);
+                            wvec |= (uint32_t)(uint8_t)__ldg(a.ew + (uint64_t)(uint32_t)eid * (uint32_t)a.H + head) << (8 * u);
                         }
                     } else {
                         v[u].zero();
@@ -383,6 +383,7 @@ static int pow2_ceil(int x) {
 template <int MODE>
 static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t stream) {
     if (a.n_rows == 0 || a.f == 0) return TANGO_OK;
+    if (a.ld > 0x7fffffff) return TANGO_ESIZE;
     a.n_long = a.n_rows;
     if (plan) a.row_order = plan->row_order;
     if (plan && plan->n_units > 0) {
