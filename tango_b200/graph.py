@@ -199,6 +199,25 @@ def add_self_loop(src: torch.Tensor, dst: torch.Tensor, n_nodes: int):
     return torch.cat([src[keep], loop]), torch.cat([dst[keep], loop])
 
 
+def graph_from_edge_list(path: str, n_nodes: Optional[int] = None, device="cpu", self_loops: bool = True,
+                         symmetric: bool = False) -> Graph:
+    """Reads a whitespace-separated "src dst" edge list (the SNAP text format the reference's loader parses for its
+    DBLP / Amazon graphs, evaluation/util.py:15-22; lines starting with '#' are comments), optionally adds the reverse
+    edges, drops duplicates, and applies the reference's remove_self_loop + add_self_loop."""
+    import numpy as np
+    arr = np.loadtxt(path, dtype=np.int64, comments="#", ndmin=2)
+    src, dst = torch.from_numpy(arr[:, 0].copy()), torch.from_numpy(arr[:, 1].copy())
+    if symmetric:
+        src, dst = torch.cat([src, dst]), torch.cat([dst, src])
+    n = int(max(int(src.max()), int(dst.max())) + 1) if n_nodes is None else int(n_nodes)
+    key = torch.unique(src * n + dst)
+    src, dst = (key // n).to(torch.int32), (key % n).to(torch.int32)
+    if self_loops:
+        src, dst = add_self_loop(src, dst, n)
+    order = torch.argsort(dst.long() * n + src.long())
+    return Graph(src[order].contiguous(), dst[order].contiguous(), n).to(device)
+
+
 def rmat_graph(n_nodes: int, n_edges: int, seed: int, device="cpu", self_loops: bool = True,
                edge_order: str = "dst") -> Graph:
     """Seeded R-MAT graph.  edge_order='dst' numbers the edges by (destination, source), so that edge ids follow the

@@ -204,3 +204,25 @@ def test_gat_edge_softmax_bwd_kernel(cuda):
     s = torch.zeros(n, 4, device="cuda").index_add_(0, dst, ex)
     (ex / s[dst] * da).sum().backward()
     assert (dz - z.grad).abs().max() < 1e-4 * max(1.0, z.grad.abs().max().item())
+
+
+def test_config1_gcn_forward_bit_exact_vs_oracle(cuda):
+    """BASELINE config 1 at full size (19,717 nodes, 88,648 edges + self loops, 500 -> 16 -> 3): the logits of the
+    2-layer quantized GCN equal the oracle's layer chain bit for bit."""
+    import tango_b200 as T
+    from tango_b200.gnn import GCN
+    from tango_b200.graph import rmat_graph
+    g = rmat_graph(19_717, 88_648, 20241, device="cuda")
+    T.graph_preprocess(g)
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((g.num_nodes(), 500)).astype(np.float32)
+    torch.manual_seed(6)
+    m = GCN(g, 500, 16, 3, 1).cuda()
+    with torch.no_grad():
+        m.layers[0].bias.copy_(torch.from_numpy(rng.standard_normal(16).astype(np.float32)))
+        m.layers[1].bias.copy_(torch.from_numpy(rng.standard_normal(3).astype(np.float32)))
+    logits = m(torch.from_numpy(x).cuda()).detach().cpu().numpy()
+    h = _oracle_gcn_layer(g, x, m.layers[0].weight.detach().cpu().numpy(), m.layers[0].bias.detach().cpu().numpy(), True)
+    ref = _oracle_gcn_layer(g, h, m.layers[1].weight.detach().cpu().numpy(), m.layers[1].bias.detach().cpu().numpy(),
+                            False)
+    np.testing.assert_array_equal(logits, ref)

@@ -203,3 +203,15 @@ def test_partition_layouts_reproduce_the_unpartitioned_aggregation(layout):
                                                                (p.indptr_flat[1:] - p.indptr_flat[:-1]).long())])
         seen += p.indices.numel()
     assert seen == g.num_edges()
+
+
+def test_graph_from_edge_list(tmp_path):
+    from tango_b200.graph import graph_from_edge_list
+    f = tmp_path / "g.txt"
+    f.write_text("# comment\n0 1\n1 2\n1 2\n2 2\n3 0\n")
+    g = graph_from_edge_list(str(f), symmetric=True)
+    src, dst = g.coo
+    pairs = set(zip(src.tolist(), dst.tolist()))
+    assert pairs == {(0, 1), (1, 0), (1, 2), (2, 1), (3, 0), (0, 3), (0, 0), (1, 1), (2, 2), (3, 3)}
+    assert g.num_nodes() == 4 and g.adj_csc[0].tolist() == [0, 3, 6, 8, 10]
+    assert g._identity["csc"]
