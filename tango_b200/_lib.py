@@ -49,7 +49,7 @@ _SIGS = {
     "tango_quantize_transpose": ([P, c_int64, c_int64, P, P, P], c_int),
     "tango_qgemm_dw_workspace_bytes": ([c_int64, c_int64], c_int64),
     "tango_qgemm_nt": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, P, c_int64, P, P, P], c_int),
-    "tango_qgemm_forward": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, c_int64, P, P,
+    "tango_qgemm_forward": ([P, c_int64, P, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, c_int64, P, P,
                              c_int64, P, c_int, c_uint64, c_uint64, P, P], c_int),
     "tango_qgemm_dx": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, P], c_int),
     "tango_qgemm_dw": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, c_int64, P, P], c_int),

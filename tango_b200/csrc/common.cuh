@@ -61,6 +61,46 @@ __device__ __forceinline__ float inv_scale(float s) {
     return isinf(inv) ? 0.f : inv;
 }
 
+// ---------------------------------------------------------------------------------------------- Philox4x32-10
+struct Philox {
+    uint32_t k0, k1;
+    __device__ __forceinline__ uint4 operator()(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3) const {
+        uint32_t a = k0, b = k1;
+#pragma unroll
+        for (int r = 0; r < 10; ++r) {
+            const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+            const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+            const uint32_t n0 = hi1 ^ c1 ^ a, n2 = hi0 ^ c3 ^ b;
+            c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+            a += 0x9E3779B9u; b += 0xBB67AE85u;
+        }
+        return make_uint4(c0, c1, c2, c3);
+    }
+};
+
+__device__ __forceinline__ int round_to_i8(float t, int mode, float u) {
+    float r;
+    if (mode == TANGO_ROUND_NEAREST) r = rintf(t);
+    else if (mode == TANGO_ROUND_TRUNC) r = truncf(t);
+    else r = floorf(__fadd_rn(t, u));
+    r = fminf(fmaxf(r, -127.f), 127.f);
+    return (int)r;
+}
+
+// Stochastic-rounding uniform in [0,1) of flat element index `flat`: lane flat%4 of Philox block flat/4, keyed by
+// (seed, call).  `cached_blk` / `rnd` let consecutive elements of one thread share a block.
+__device__ __forceinline__ float sr_uniform(const Philox &ph, uint64_t flat, uint64_t call, uint64_t &cached_blk,
+                                            uint4 &rnd) {
+    const uint64_t blk = flat >> 2;
+    if (blk != cached_blk) {
+        rnd = ph((uint32_t)blk, (uint32_t)(blk >> 32), (uint32_t)call, (uint32_t)(call >> 32));
+        cached_blk = blk;
+    }
+    const uint32_t lane = (uint32_t)flat & 3u;
+    const uint32_t rr = lane == 0 ? rnd.x : lane == 1 ? rnd.y : lane == 2 ? rnd.z : rnd.w;
+    return __fmul_rn((float)(rr >> 8), 5.9604644775390625e-08f);  // 2^-24
+}
+
 // sign-extended byte i (0..3) of a packed word, added into acc: dp4a with a one-hot selector.
 template <int I>
 __device__ __forceinline__ int add_byte(uint32_t w, int acc) {

@@ -6,23 +6,6 @@ namespace tango {
 
 thread_local int g_last_cuda_error = 0;
 
-// ---------------------------------------------------------------------------------------------- Philox4x32-10
-struct Philox {
-    uint32_t k0, k1;
-    __device__ __forceinline__ uint4 operator()(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3) const {
-        uint32_t a = k0, b = k1;
-#pragma unroll
-        for (int r = 0; r < 10; ++r) {
-            const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
-            const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
-            const uint32_t n0 = hi1 ^ c1 ^ a, n2 = hi0 ^ c3 ^ b;
-            c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
-            a += 0x9E3779B9u; b += 0xBB67AE85u;
-        }
-        return make_uint4(c0, c1, c2, c3);
-    }
-};
-
 // ---------------------------------------------------------------------------------------------- absmax
 // LW = floats per load (4, 2 or 1): rows must start on an LW-float boundary (base aligned, ld % LW == 0); the columns
 // past the last full vector of a row are read one by one.
@@ -61,14 +44,6 @@ __global__ void __launch_bounds__(256) absmax_kernel(const float *__restrict__ x
 }
 
 // ---------------------------------------------------------------------------------------------- quantize
-__device__ __forceinline__ int round_to_i8(float t, int mode, float u) {
-    float r;
-    if (mode == TANGO_ROUND_NEAREST) r = rintf(t);
-    else if (mode == TANGO_ROUND_TRUNC) r = truncf(t);
-    else r = floorf(__fadd_rn(t, u));
-    r = fminf(fmaxf(r, -127.f), 127.f);
-    return (int)r;
-}
 
 // One thread produces 16 consecutive output bytes of one row (a 128-bit store).  LW = floats per input load.
 template <int LW>

@@ -144,11 +144,9 @@ class _dist_gcn_conv_fused(Function):
         if dg.scale_mode == "global":
             dist.all_reduce(sX, op=dist.ReduceOp.MAX)
         Xq, Wq = K.alloc_int8(X.shape, X.device), K.alloc_int8(W.shape, X.device)
-        K._quantize_into(Xq, X, sX, mode_f, seed, call, dg.out_norm)
-        K._quantize_into(Wq, W.contiguous(), sW, mode_f, seed, call + 1)
         H = torch.empty((X.shape[0], W.shape[0]), dtype=torch.float32, device=X.device)
         sH = torch.zeros(1, dtype=torch.float32, device=X.device)
-        K._qgemm_nt(H, Xq, Wq, sX, sW, None, sH)
+        K._qgemm_forward(H, X, Xq, W.contiguous(), Wq, None, sH, sX, sW, mode_f, seed, call, dg.out_norm)
         out = _aggregate(dg, dg.fwd, H, sH, dg.in_norm, b, relu)
         ctx.dg, ctx.relu, ctx.has_bias = dg, relu, b is not None
         ctx.save_for_backward(Xq, sX, Wq, sW, out if relu else None)

@@ -59,11 +59,10 @@ class _gcn_conv_fused(Function):
         sX = kernels._get_scale(X, out_norm)
         sW = kernels._get_scale(W)
         Xq, Wq = alloc_int8(X.shape, X.device), alloc_int8(W.shape, X.device)
-        kernels._quantize_into(Xq, X, sX, mode_f, seed, call, out_norm)
-        kernels._quantize_into(Wq, W.contiguous(), sW, mode_f, seed, call + 1)
         H = torch.empty((X.shape[0], W.shape[0]), dtype=torch.float32, device=X.device)
         sH = torch.zeros(1, dtype=torch.float32, device=X.device)
-        kernels._qgemm_nt(H, Xq, Wq, sX, sW, None, sH)
+        # X * d_out^-1/2 is quantized on load inside the GEMM kernel, which also writes Xq for the backward pass
+        kernels._qgemm_forward(H, X, Xq, W.contiguous(), Wq, None, sH, sX, sW, mode_f, seed, call, out_norm)
         Hq, _ = kernels.quantize(H, sH, mode=mode_q, seed=seed)
         out = kernels.csr_SPMM(g, Hq, sH, False, in_norm, b, relu)
         ctx.g, ctx.relu, ctx.has_bias = g, relu, b is not None

@@ -173,7 +173,7 @@ def _transpose_quant(data: torch.Tensor, scale: torch.Tensor, nrow: int, ncol: i
     return out
 
 
-def _qgemm_forward(Y, X, X_q, W, W_q, bias, scaleY, scaleX, scaleW, mode=ROUND_TRUNC, seed=0, call=0):
+def _qgemm_forward(Y, X, X_q, W, W_q, bias, scaleY, scaleX, scaleW, mode=ROUND_TRUNC, seed=0, call=0, row_scale=None):
     X, m, k, ldx = _matrix(X)
     W, n, k2, ldw = _matrix(W)
     assert k == k2
@@ -182,10 +182,10 @@ def _qgemm_forward(Y, X, X_q, W, W_q, bias, scaleY, scaleX, scaleW, mode=ROUND_T
     _, _, _, ldy = _matrix(Y)
     st = _status_word(X.device)
     with torch.cuda.device(X.device):
-        check(lib.tango_qgemm_forward(_p(X), ldx, _p(W), ldw, m, n, k, _p(scaleX), _p(scaleW), _p(X_q), ldxq, _p(W_q),
+        check(lib.tango_qgemm_forward(_p(X), ldx, _p(row_scale), _p(W), ldw, m, n, k, _p(scaleX), _p(scaleW), _p(X_q), ldxq, _p(W_q),
                                       ldwq, _p(bias), _p(Y), ldy, _p(scaleY), mode, seed, call, _p(st), _stream()),
               "QGEMM_forward")
-    launch_counter[0] += 3
+    launch_counter[0] += 2
 
 
 def _qgemm_nt(Y, X_q, W_q, scaleX, scaleW, bias=None, scaleY=None):
