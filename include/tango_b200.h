@@ -92,9 +92,9 @@ int tango_qgemm_nt(const int8_t *xq, int64_t ldx, const int8_t *wq, int64_t ldw,
 
 /* The reference's fused forward: quantises X[M,K] (times row_scale[r] if given) and W[N,K] with the given rounding
  * mode and the scales sx, sw, writes the int8 copies xq, wq that the backward pass re-uses, and computes the GEMM
- * above.  When one N-tile (N <= 256) of W fits in shared memory, X is quantized on load inside the GEMM kernel
- * (fp32 X is read once; no separate quantize pass), like the reference's QuantizeTileIterator2dThreadTile
- * (cuda/src/iterator.h:155-164); otherwise two kernels run.  Stochastic mode draws X with `call`, W with `call`+1.
+ * above.  Stochastic mode draws X with `call`, W with `call`+1.  (The reference quantizes on load inside the GEMM,
+ * cuda/src/iterator.h:155-164; here the quantizer is a separate streaming kernel in front of the TMA-fed GEMM -- a
+ * quantize-on-load producer for the tcgen05 kernel was built and measured 3x slower, see DESIGN.md.)
  * Replaces QGEMM_forward (cuda/src/cuda.cpp:183, cuda/kernels.py:79-94). */
 int tango_qgemm_forward(const float *x, int64_t ldx_f, const float *row_scale, const float *w, int64_t ldw_f,
                         int64_t m, int64_t n, int64_t k, const float *sx, const float *sw, int8_t *xq, int64_t ldxq,

@@ -45,14 +45,6 @@ struct GemmParams {
     float *absmax;
     int *status;
     uint32_t tmem_cols;
-    // fused quantize-on-load of the A operand (forward product only): fp32 source, optional per-row factor, int8 copy
-    const float *a_f32;
-    int64_t lda_f32;
-    const float *a_row_scale;
-    int8_t *aq_out;
-    int64_t ldaq;
-    int qmode;
-    uint64_t seed, call;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -82,8 +74,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the wait was abandoned (timeout here or abort raised by another role).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    // hand-offs between the roles are short (a pipeline stage): poll for a while before starting to sleep
 #pragma unroll 1
-    for (int i = 0; i < 128; ++i)
+    for (int i = 0; i < 4096; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
 #pragma unroll 1
@@ -94,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             *abort_flag = 1;
             return false;
         }
-        __nanosleep(128);
+        __nanosleep(64);
     }
 }
 
@@ -364,8 +357,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 // overlaps the loads and MMAs of tile i+1.  Same roles and the same bounded waits as igemm_kernel.
 constexpr int kStageLd = 16;  // words per staged epilogue row (16 columns, no padding needed for 128-bit accesses)
 
-template <bool FUSED_A>
-__global__ void __launch_bounds__(FUSED_A ? 576 : 320, 1)
+__global__ void __launch_bounds__(320, 1)
 igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                         const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -389,7 +381,7 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < p.stages; ++s) {
-            mbar_init(smem_u32(&bar_a_full[s]), FUSED_A ? 8 : 1);   // one arrival per converter warp, or the TMA
+            mbar_init(smem_u32(&bar_a_full[s]), 1);
             mbar_init(smem_u32(&bar_a_empty[s]), 1);
         }
         mbar_init(smem_u32(&bar_b_full), 1);
@@ -429,7 +421,7 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             }
             int it = 0;
             bool ok = true;
-            for (int mt = blockIdx.x; !FUSED_A && mt < m_tiles && ok; mt += gridDim.x) {
+            for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
                 for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
                     const int s = it % p.stages;
                     const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
@@ -474,7 +466,7 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             }
         }
         __syncwarp();
-    } else if (warp < 10) {
+    } else {
         // ------------------------------------------------------------------ epilogue (warps 2..9)
         // Eight warps drain an accumulator -- one warp runs a long dependent chain per chunk (TMEM load, convert,
         // stage, store), so four warps alone were the kernel's bottleneck.  Warp w reads TMEM lanes 32*(w%4).. and
@@ -573,83 +565,6 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
                 if (s > __ldcg(p.absmax)) atomic_max_nonneg(p.absmax, s);
             }
         }
-    } else if (FUSED_A) {
-        // ------------------------------------------------------------------ A converters (warps 10..17)
-        // Quantize-on-load: the fp32 rows of X are read with plain coalesced loads (a warp covers 128 columns of a
-        // row), scaled, rounded to int8, packed, written into the 128-byte-swizzled K-major tile the MMA reads and,
-        // as the int8 copy the backward pass needs, to global memory.  Eight warps, 16 rows of the tile each.
-        const int cw = warp - 10;
-        const float inv = inv_scale(__ldg(p.sa));
-        const Philox ph{(uint32_t)p.seed, (uint32_t)(p.seed >> 32)};
-        const bool v4 = (p.lda_f32 & 3) == 0 && (reinterpret_cast<uintptr_t>(p.a_f32) & 15) == 0;
-        const bool v2 = (p.lda_f32 & 1) == 0 && (reinterpret_cast<uintptr_t>(p.a_f32) & 7) == 0;
-        int it = 0;
-        bool ok = true;
-        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
-            for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
-                const int s = it % p.stages;
-                const uint32_t ph_bit = (uint32_t)(it / p.stages) & 1u;
-                ok = mbar_wait(smem_u32(&bar_a_empty[s]), ph_bit ^ 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                uint8_t *tile = smem_raw + (a_base - smem_u32(smem_raw)) + s * kABytes;
-                const int col = kb * kBlockK + lane * 4;          // first of this lane's 4 columns
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    float x[8][4];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {                 // 8 rows in flight per lane
-                        const int r = cw * 16 + half * 8 + j;
-                        const int64_t grow = (int64_t)mt * kTileM + r;
-                        x[j][0] = x[j][1] = x[j][2] = x[j][3] = 0.f;
-                        if (grow < p.M) {
-                            const float *src = p.a_f32 + grow * p.lda_f32 + col;
-                            if (col + 4 <= p.K && v4) {
-                                const float4 t = __ldcs(reinterpret_cast<const float4 *>(src));
-                                x[j][0] = t.x; x[j][1] = t.y; x[j][2] = t.z; x[j][3] = t.w;
-                            } else if (col + 4 <= p.K && v2) {
-                                const float2 t0 = __ldcs(reinterpret_cast<const float2 *>(src));
-                                const float2 t1 = __ldcs(reinterpret_cast<const float2 *>(src + 2));
-                                x[j][0] = t0.x; x[j][1] = t0.y; x[j][2] = t1.x; x[j][3] = t1.y;
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    if (col + e < p.K) x[j][e] = src[e];
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int r = cw * 16 + half * 8 + j;
-                        const int64_t grow = (int64_t)mt * kTileM + r;
-                        const float rs = (p.a_row_scale && grow < p.M) ? __ldg(p.a_row_scale + grow) : 1.f;
-                        uint32_t word = 0;
-                        uint64_t cached = ~0ull;
-                        uint4 rnd = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float t = p.a_row_scale ? __fmul_rn(x[j][e], rs) : x[j][e];
-                            t = __fmul_rn(t, inv);
-                            float u = 0.f;
-                            if (p.qmode == TANGO_ROUND_STOCHASTIC)
-                                u = sr_uniform(ph, (uint64_t)(grow * p.K + col + e), p.call, cached, rnd);
-                            const int qi = (col + e < p.K && grow < p.M) ? round_to_i8(t, p.qmode, u) : 0;
-                            word |= ((uint32_t)qi & 0xffu) << (8 * e);
-                        }
-                        // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
-                        const uint32_t chunk = (uint32_t)(lane >> 2) ^ (uint32_t)(r & 7);
-                        *reinterpret_cast<uint32_t *>(tile + r * 128 + chunk * 16 + (lane & 3) * 4) = word;
-                        if (grow < p.M && col < p.ldaq)
-                            *reinterpret_cast<uint32_t *>(p.aq_out + grow * p.ldaq + col) = word;
-                    }
-                }
-                // make the generic-proxy writes visible to the tensor core's async proxy, then signal the stage
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0)
-                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_a_full[s])) : "memory");
-            }
-        }
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -722,9 +637,6 @@ struct GemmCall {
     int mode; int splits;
     float *out; int64_t ldo; int32_t *ws; int64_t ldws;
     const float *sa, *sb, *bias; float *absmax; int *status;
-    // optional quantize-on-load of A (forward only): when a_f32 != nullptr the kernel reads fp32 A, writes int8 `a`
-    const float *a_f32 = nullptr; int64_t lda_f32 = 0; const float *a_row_scale = nullptr;
-    int qmode = 0; uint64_t seed = 0, call = 0;
 };
 
 static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
@@ -765,7 +677,7 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
     if (rc) return rc;
 
     // Persistent B-stationary kernel when one N-tile of B (all of K) fits in shared memory beside >= 3 A stages.
-    if (c.mode == 0 && splits == 1 && (!c.a_f32 || (!c.a_mn && n_tiles == 1))) {
+    if (c.mode == 0 && splits == 1) {
         const int64_t budget = 227 * 1024 - 2048;   // dynamic limit minus static barriers and alignment slack
         const int64_t b_res = (int64_t)p.kb_total * p.b_bytes;
         const int64_t staging = 8 * 32 * kStageLd * 4;
@@ -778,28 +690,19 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
             while ((int)cols < p.n_tile) cols <<= 1;
             pp.tmem_cols = cols * 2;
             const size_t smem_p = (size_t)(1024 + b_res + st * kABytes + staging);
-            const bool fused = c.a_f32 != nullptr;
-            pp.a_f32 = c.a_f32; pp.lda_f32 = c.lda_f32; pp.a_row_scale = c.a_row_scale;
-            pp.aq_out = const_cast<int8_t *>(c.a); pp.ldaq = c.lda; pp.qmode = c.qmode; pp.seed = c.seed; pp.call = c.call;
-            if (fused)
-                TANGO_CUDA_TRY(cudaFuncSetAttribute(igemm_persistent_kernel<true>,
-                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - 1024)));
-            else
-                TANGO_CUDA_TRY(cudaFuncSetAttribute(igemm_persistent_kernel<false>,
-                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - 1024)));
+            TANGO_CUDA_TRY(cudaFuncSetAttribute(igemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)(227 * 1024 - 1024)));
             const int64_t m_tiles = ceil_div(c.M, kTileM);
             int64_t gx = kNumSMs / n_tiles;
             if (gx < 1) gx = 1;
             if (gx > m_tiles) gx = m_tiles;
             const dim3 pgrid((unsigned)gx, (unsigned)n_tiles, 1);
             if (pgrid.y > 65535) return TANGO_ESIZE;
-            if (fused) igemm_persistent_kernel<true><<<pgrid, 576, smem_p, stream>>>(tm_a, tm_b, pp);
-            else igemm_persistent_kernel<false><<<pgrid, 320, smem_p, stream>>>(tm_a, tm_b, pp);
+            igemm_persistent_kernel<<<pgrid, 320, smem_p, stream>>>(tm_a, tm_b, pp);
             TANGO_LAUNCH_CHECK();
             return TANGO_OK;
         }
     }
-    if (c.a_f32) return TANGO_ESIZE;   // quantize-on-load exists only in the persistent kernel; the caller falls back
     const size_t smem = (size_t)p.stages * stage_bytes + 1024;
     // per-device attribute; setting it on every call keeps the entry point free of global state
     TANGO_CUDA_TRY(cudaFuncSetAttribute(igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -834,19 +737,9 @@ extern "C" int tango_qgemm_forward(const float *x, int64_t ldx_f, const float *r
                                    int8_t *xq, int64_t ldxq, int8_t *wq, int64_t ldwq, const float *bias, float *y,
                                    int64_t ldy, float *scale_y, int mode, uint64_t seed, uint64_t call, int *status,
                                    tango_stream_t stream) {
-    if (m < 0 || n < 0 || k <= 0 || ldx_f < k || ldw_f < k || ldxq < k || ldwq < k || ldy < n) return TANGO_EINVAL;
-    if (mode < 0 || mode > 2) return TANGO_EINVAL;
-    if (m == 0 || n == 0) return TANGO_OK;
-    if (!x || !w || !sx || !sw || !xq || !wq || !y) return TANGO_EINVAL;
-    int rc = tango_quantize(w, n, k, ldw_f, nullptr, sw, wq, ldwq, mode, seed, call + 1, stream);
+    int rc = tango_quantize(x, m, k, ldx_f, row_scale, sx, xq, ldxq, mode, seed, call, stream);
     if (rc) return rc;
-    // quantize-on-load: X is read once as fp32 inside the GEMM, which also writes the int8 copy
-    GemmCall c{xq, ldxq, 0, wq, ldwq, 0, m, n, k, 0, 1, y, ldy, nullptr, 0, sx, sw, bias, scale_y, status};
-    c.a_f32 = x; c.lda_f32 = ldx_f; c.a_row_scale = row_scale; c.qmode = mode; c.seed = seed; c.call = call;
-    rc = launch_gemm(c, (cudaStream_t)stream);
-    if (rc != TANGO_ESIZE) return rc;
-    // shapes the persistent kernel does not take (N > 256 or a weight too large for shared memory): two passes
-    rc = tango_quantize(x, m, k, ldx_f, row_scale, sx, xq, ldxq, mode, seed, call, stream);
+    rc = tango_quantize(w, n, k, ldw_f, nullptr, sw, wq, ldwq, mode, seed, call + 1, stream);
     if (rc) return rc;
     return tango_qgemm_nt(xq, ldxq, wq, ldwq, m, n, k, sx, sw, bias, y, ldy, scale_y, status, stream);
 }
