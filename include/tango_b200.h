@@ -78,6 +78,21 @@ int tango_quantize(const float *x, int64_t rows, int64_t cols, int64_t ldx, cons
 int tango_quantize_transpose(const float *x, int64_t nrow, int64_t ncol, const float *scale, int8_t *out,
                              tango_stream_t stream);
 
+/* Backward of y = relu(.): the masked gradient m[r,c] = (y[r,c] > 0 ? g[r,c] : 0) is consumed without being written.
+ * tango_relu_grad_stats: scale[0] = max |m[r,c] * row_scale[r]| / 127 and, if colsum != NULL, colsum[c] = sum_r m[r,c]
+ * (the bias gradient), added in a fixed order through `scratch` (tango_relu_grad_stats_scratch_bytes).
+ * tango_quantize_relu_grad: q = round_mode(m * row_scale[r] / scale[0]), q rows padded to ldq (multiple of 16).
+ * They replace the torch ops between the aggregation's backward and its quantizer in the reference's layer
+ * (ReLU backward, `grad_output.sum(0)`, `* norm`, get_scale, quantize: evaluation/test_gcn.py:123-137,
+ * cuda/SPMM.py:18-24) with two passes over g and y. */
+int64_t tango_relu_grad_stats_scratch_bytes(int64_t rows, int64_t cols);
+int tango_relu_grad_stats(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows, int64_t cols,
+                          const float *row_scale, float *scale, float *colsum, void *scratch, int64_t scratch_bytes,
+                          tango_stream_t stream);
+int tango_quantize_relu_grad(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows, int64_t cols,
+                             const float *row_scale, const float *scale, int8_t *q, int64_t ldq, int mode,
+                             uint64_t seed, uint64_t call, tango_stream_t stream);
+
 /* ---------------------------------------------------------------- int8 GEMMs (tcgen05 kind::i8) */
 
 /* Bytes of scratch tango_qgemm_dw needs for an [n, k] weight gradient. */

@@ -244,3 +244,151 @@ extern "C" int tango_quantize_transpose(const float *x, int64_t nrow, int64_t nc
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
 }
+
+// ------------------------------------------------------------------------------------------------ ReLU-gradient fusion
+// Backward of  y = relu(...):  the incoming gradient g is masked by (y > 0) before anything else uses it.  The two
+// kernels below read g and y directly, so the masked gradient is never written to memory:
+//   relu_grad_stats : scale = max |m| / 127 with m = (y > 0 ? g : 0) * row_scale[r], and the column sums of the masked
+//                     gradient (the bias gradient), summed in a fixed order (block partials, then one pass over them)
+//   relu_grad_quant : int8 m / scale, same layout rules as tango_quantize
+namespace tango {
+
+__global__ void __launch_bounds__(256) relu_grad_stats_kernel(const float *__restrict__ g, int64_t ldg,
+                                                              const float *__restrict__ y, int64_t ldy, int64_t rows,
+                                                              int64_t cols, const float *__restrict__ row_scale,
+                                                              float *__restrict__ scale, float *__restrict__ partial,
+                                                              int cw, int64_t rows_per_block) {
+    __shared__ float s_part[256];
+    const int tx = threadIdx.x % cw, ty = threadIdx.x / cw, nty = 256 / cw;
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
+    const int64_t r1 = min(rows, r0 + rows_per_block);
+    float amax = 0.f;
+    for (int64_t c0 = 0; c0 < cols; c0 += cw) {
+        const int64_t c = c0 + tx;
+        float sum = 0.f;
+        if (c < cols) {
+            for (int64_t r = r0 + ty; r < r1; r += nty) {
+                const float v = __ldcs(y + r * ldy + c) > 0.f ? __ldcs(g + r * ldg + c) : 0.f;
+                sum = __fadd_rn(sum, v);
+                float a = fabsf(v);
+                if (row_scale) a = __fmul_rn(a, fabsf(__ldg(row_scale + r)));
+                amax = fmaxf(amax, a);
+            }
+        }
+        if (partial) {
+            __syncthreads();
+            s_part[threadIdx.x] = sum;
+            __syncthreads();
+            if (ty == 0 && c < cols) {
+                float t = 0.f;
+                for (int k = 0; k < nty; ++k) t = __fadd_rn(t, s_part[k * cw + tx]);
+                partial[(int64_t)blockIdx.x * cols + c] = t;
+            }
+        }
+    }
+    block_absmax_to_scale(amax, scale);
+}
+
+__global__ void __launch_bounds__(256) colsum_finish_kernel(const float *__restrict__ partial, int nblocks,
+                                                            int64_t cols, float *__restrict__ colsum) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float t = 0.f;
+    for (int b = 0; b < nblocks; ++b) t = __fadd_rn(t, partial[(int64_t)b * cols + c]);
+    colsum[c] = t;
+}
+
+template <bool VEC4>
+__global__ void __launch_bounds__(256) relu_grad_quant_kernel(const float *__restrict__ g, int64_t ldg,
+                                                              const float *__restrict__ y, int64_t ldy, int64_t rows,
+                                                              int64_t cols, const float *__restrict__ row_scale,
+                                                              const float *__restrict__ scale, int8_t *__restrict__ q,
+                                                              int64_t ldq, int mode, uint64_t seed, uint64_t call) {
+    const float inv = inv_scale(__ldg(scale));
+    const int64_t groups = ldq >> 4, total = rows * groups;   // ldq % 16 == 0
+    const Philox ph{(uint32_t)seed, (uint32_t)(seed >> 32)};
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / groups, c0 = (i - r * groups) << 4;
+        const float rs = row_scale ? __ldg(row_scale + r) : 1.f;
+        float v[16];
+        if (VEC4 && c0 + 16 <= cols) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 a = __ldcs(reinterpret_cast<const float4 *>(g + r * ldg + c0 + 4 * k));
+                const float4 m = __ldcs(reinterpret_cast<const float4 *>(y + r * ldy + c0 + 4 * k));
+                v[4 * k] = m.x > 0.f ? a.x : 0.f; v[4 * k + 1] = m.y > 0.f ? a.y : 0.f;
+                v[4 * k + 2] = m.z > 0.f ? a.z : 0.f; v[4 * k + 3] = m.w > 0.f ? a.w : 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+                v[k] = (c0 + k < cols && y[r * ldy + c0 + k] > 0.f) ? g[r * ldg + c0 + k] : 0.f;
+        }
+        uint32_t packed[4] = {0, 0, 0, 0};
+        uint64_t cached_blk = ~0ull;
+        uint4 rnd = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float t = row_scale ? __fmul_rn(v[k], rs) : v[k];
+            t = __fmul_rn(t, inv);
+            float u = 0.f;
+            if (mode == TANGO_ROUND_STOCHASTIC) u = sr_uniform(ph, (uint64_t)(r * cols + c0 + k), call, cached_blk, rnd);
+            const int qi = (c0 + k < cols) ? round_to_i8(t, mode, u) : 0;
+            packed[k >> 2] |= ((uint32_t)qi & 0xffu) << (8 * (k & 3));
+        }
+        __stcs(reinterpret_cast<uint4 *>(q + r * ldq + c0), make_uint4(packed[0], packed[1], packed[2], packed[3]));
+    }
+}
+
+static int stats_blocks(int64_t rows) {
+    int64_t b = ceil_div(rows, 64);
+    if (b > kNumSMs * 4) b = kNumSMs * 4;
+    return (int)(b < 1 ? 1 : b);
+}
+
+}  // namespace tango
+
+extern "C" int64_t tango_relu_grad_stats_scratch_bytes(int64_t rows, int64_t cols) {
+    if (rows < 0 || cols < 0) return 0;
+    return (int64_t)stats_blocks(rows) * cols * (int64_t)sizeof(float);
+}
+
+extern "C" int tango_relu_grad_stats(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows,
+                                     int64_t cols, const float *row_scale, float *scale, float *colsum, void *scratch,
+                                     int64_t scratch_bytes, tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (rows < 0 || cols < 0 || ldg < cols || ldy < cols || !scale) return TANGO_EINVAL;
+    TANGO_CUDA_TRY(cudaMemsetAsync(scale, 0, sizeof(float), stream));
+    if (colsum && cols > 0 && rows == 0) TANGO_CUDA_TRY(cudaMemsetAsync(colsum, 0, sizeof(float) * (size_t)cols, stream));
+    if (rows == 0 || cols == 0) return TANGO_OK;
+    if (!g || !y) return TANGO_EINVAL;
+    const int nb = stats_blocks(rows);
+    if (colsum && (!scratch || scratch_bytes < tango_relu_grad_stats_scratch_bytes(rows, cols))) return TANGO_ESIZE;
+    int cw = 1;
+    while (cw < cols && cw < 256) cw <<= 1;
+    const int64_t rpb = ceil_div(rows, nb);
+    relu_grad_stats_kernel<<<nb, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale,
+                                                   colsum ? (float *)scratch : nullptr, cw, rpb);
+    TANGO_LAUNCH_CHECK();
+    if (colsum) {
+        colsum_finish_kernel<<<(unsigned)ceil_div(cols, 256), 256, 0, stream>>>((const float *)scratch, nb, cols, colsum);
+        TANGO_LAUNCH_CHECK();
+    }
+    return TANGO_OK;
+}
+
+extern "C" int tango_quantize_relu_grad(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows,
+                                        int64_t cols, const float *row_scale, const float *scale, int8_t *q,
+                                        int64_t ldq, int mode, uint64_t seed, uint64_t call, tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (rows < 0 || cols < 0 || ldg < cols || ldy < cols || ldq < cols || mode < 0 || mode > 2) return TANGO_EINVAL;
+    if (rows == 0 || ldq == 0) return TANGO_OK;
+    if (!g || !y || !q || !scale) return TANGO_EINVAL;
+    if (ldq % 16 != 0 || !aligned(q, 16)) return TANGO_EALIGN;
+    const bool vec = ldg % 4 == 0 && ldy % 4 == 0 && aligned(g, 16) && aligned(y, 16);
+    const int grid = stream_grid(rows * (ldq / 16), 256, 16);
+    if (vec) relu_grad_quant_kernel<true><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call);
+    else relu_grad_quant_kernel<false><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}

@@ -108,16 +108,29 @@ def _aggregate(dg: DistGraph, part: RowPartition, x_local: torch.Tensor, scale_l
     x_local = x_local.contiguous()
     if scale_local is None:
         scale_local = K._get_scale(x_local, in_row_scale)
-    shared = dg.scale_mode == "global"
-    if shared:
-        scale_local = scale_local.clone()
-        dist.all_reduce(scale_local, op=dist.ReduceOp.MAX)
+    scale_local = _agree_on_scale(dg, scale_local)
     q = K.alloc_int8(x_local.shape, x_local.device)
     call = K.next_call() if mode == K.ROUND_STOCHASTIC else 0
     K._quantize_into(q, x_local, scale_local, mode, seed, call, in_row_scale)
+    return _aggregate_quantized(dg, part, q, scale_local, x_local.shape[1], row_scale, bias, relu)
+
+
+def _agree_on_scale(dg: DistGraph, scale_local: torch.Tensor) -> torch.Tensor:
+    """global scale mode: the largest local scale becomes everybody's scale (one-float all-reduce)."""
+    if dg.scale_mode != "global":
+        return scale_local
+    s = scale_local.clone()
+    dist.all_reduce(s, op=dist.ReduceOp.MAX)
+    return s
+
+
+def _aggregate_quantized(dg: DistGraph, part: RowPartition, q: torch.Tensor, scale_local: torch.Tensor, f: int,
+                         row_scale=None, bias=None, relu=False):
+    """All-gather the int8 shard `q` (and its scale in shard mode) and aggregate this rank's rows."""
+    from . import kernels as K
+    shared = dg.scale_mode == "global"
     q_all, scales = all_gather_quantized(_padded_storage(q), scale_local, dg.shard_rows, gather_scales=not shared)
-    f = x_local.shape[1]
-    out = torch.empty((dg.n_local, f), dtype=torch.float32, device=x_local.device)
+    out = torch.empty((dg.n_local, f), dtype=torch.float32, device=q.device)
     feats = q_all[:, :f] if q_all.shape[1] != f else q_all
     if shared:
         K._csr_spmm(out, part.indptr_flat, part.indices, feats, scale_local, part.schedule_flat, 1, row_scale, bias,
@@ -159,9 +172,17 @@ class _dist_gcn_conv_fused(Function):
         dg = ctx.dg
         Xq, sX, Wq, sW, out = ctx.saved_tensors
         mode_q, seed = config.mode_for("quantize"), config.seed()
-        g1 = torch.where(out > 0, d_out, torch.zeros((), device=d_out.device)) if ctx.relu else d_out.contiguous()
-        db = g1.sum(0) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
-        dH = _aggregate(dg, dg.bwd, g1, None, None, None, False, in_row_scale=dg.in_norm)
+        want_db = ctx.has_bias and ctx.needs_input_grad[3]
+        if ctx.relu:
+            call = K.next_call() if mode_q == K.ROUND_STOCHASTIC else 0
+            s_loc, db = K.relu_grad_stats(d_out, out, dg.in_norm, want_db)
+            s_loc = _agree_on_scale(dg, s_loc)
+            dZq = K.relu_grad_quant(d_out, out, dg.in_norm, s_loc, mode_q, seed, call)
+            dH = _aggregate_quantized(dg, dg.bwd, dZq, s_loc, d_out.shape[1])
+        else:
+            g1 = d_out.contiguous()
+            db = g1.sum(0) if want_db else None
+            dH = _aggregate(dg, dg.bwd, g1, None, None, None, False, in_row_scale=dg.in_norm)
         sdH = K._get_scale(dH)
         if dg.scale_mode == "global":
             dist.all_reduce(sdH, op=dist.ReduceOp.MAX)

@@ -74,12 +74,17 @@ class _gcn_conv_fused(Function):
     def backward(ctx, d_out):
         Xq, sX, Wq, sW, out_norm, in_norm, out = ctx.saved_tensors
         mode_q, seed = config.mode_for("quantize"), config.seed()
-        g1 = torch.where(out > 0, d_out, torch.zeros((), device=d_out.device)) if ctx.relu else d_out.contiguous()
-        db = g1.sum(0) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
-        sdZ = kernels._get_scale(g1, in_norm)
-        dZq = kernels.alloc_int8(g1.shape, g1.device)
+        want_db = ctx.has_bias and ctx.needs_input_grad[3]
         call = kernels.next_call() if mode_q == kernels.ROUND_STOCHASTIC else 0
-        kernels._quantize_into(dZq, g1, sdZ, mode_q, seed, call, in_norm)
+        if ctx.relu:
+            # ReLU mask, bias gradient, right norm, absmax and quantisation in two passes over (d_out, out)
+            dZq, sdZ, db = kernels.relu_grad_quantize(d_out, out, in_norm, want_db, mode_q, seed, call)
+        else:
+            g1 = d_out.contiguous()
+            db = g1.sum(0) if want_db else None
+            sdZ = kernels._get_scale(g1, in_norm)
+            dZq = kernels.alloc_int8(g1.shape, g1.device)
+            kernels._quantize_into(dZq, g1, sdZ, mode_q, seed, call, in_norm)
         dH = kernels.csr_SPMM(ctx.g, dZq, sdZ, True)
         dHq, sdH = kernels.quantize(dH, mode=mode_q, seed=seed)
         dX, dW = kernels.QGEMM_backward(dHq, Xq, Wq, sdH, sX, sW, ctx.needs_input_grad[1], ctx.needs_input_grad[2])

@@ -527,3 +527,40 @@ def gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, slope: float = 0.2):
               "gat_edge_softmax_bwd")
     launch_counter[0] += 1
     return dz
+
+
+def relu_grad_stats(g: torch.Tensor, y: torch.Tensor, row_scale: Optional[torch.Tensor] = None,
+                    want_colsum: bool = True):
+    """(scale, column sums or None) of the masked gradient (y > 0 ? g : 0); the scale includes row_scale."""
+    g, rows, cols, ldg = _matrix(g)
+    y, _, _, ldy = _matrix(y)
+    scale = torch.empty(1, dtype=torch.float32, device=g.device)
+    colsum = torch.empty(cols, dtype=torch.float32, device=g.device) if want_colsum else None
+    nbytes = lib.tango_relu_grad_stats_scratch_bytes(rows, cols) if want_colsum else 0
+    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=g.device)
+    with torch.cuda.device(g.device):
+        check(lib.tango_relu_grad_stats(_p(g), ldg, _p(y), ldy, rows, cols, _p(row_scale), _p(scale), _p(colsum),
+                                        _p(scratch), nbytes, _stream()), "relu_grad_stats")
+    launch_counter[0] += 2 if want_colsum else 1
+    return scale, colsum
+
+
+def relu_grad_quant(g: torch.Tensor, y: torch.Tensor, row_scale: Optional[torch.Tensor], scale: torch.Tensor,
+                    mode: int = ROUND_NEAREST, seed: int = 0, call: int = 0) -> torch.Tensor:
+    """int8 of (y > 0 ? g : 0) * row_scale / scale, rows padded to 16 bytes."""
+    g, rows, cols, ldg = _matrix(g)
+    y, _, _, ldy = _matrix(y)
+    q = alloc_int8((rows, cols), g.device)
+    with torch.cuda.device(g.device):
+        check(lib.tango_quantize_relu_grad(_p(g), ldg, _p(y), ldy, rows, cols, _p(row_scale), _p(scale), _p(q),
+                                           q.stride(0), mode, seed, call, _stream()), "quantize_relu_grad")
+    launch_counter[0] += 1
+    return q
+
+
+def relu_grad_quantize(g: torch.Tensor, y: torch.Tensor, row_scale: Optional[torch.Tensor] = None,
+                       want_colsum: bool = True, mode: int = ROUND_NEAREST, seed: int = 0, call: int = 0):
+    """For the backward pass of y = relu(.): returns (int8 of (y > 0 ? g : 0) * row_scale / scale, scale, column sums
+    of the masked gradient or None) without materialising the masked gradient."""
+    scale, colsum = relu_grad_stats(g, y, row_scale, want_colsum)
+    return relu_grad_quant(g, y, row_scale, scale, mode, seed, call), scale, colsum
