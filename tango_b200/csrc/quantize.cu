@@ -253,36 +253,60 @@ extern "C" int tango_quantize_transpose(const float *x, int64_t nrow, int64_t nc
 //   relu_grad_quant : int8 m / scale, same layout rules as tango_quantize
 namespace tango {
 
+// Column c of the tile is owned by thread tx (VW consecutive columns per thread: 4 with 128-bit loads, else 1), rows
+// are dealt to the ty groups; four row-steps are kept in flight per thread.
+template <int VW>
 __global__ void __launch_bounds__(256) relu_grad_stats_kernel(const float *__restrict__ g, int64_t ldg,
                                                               const float *__restrict__ y, int64_t ldy, int64_t rows,
                                                               int64_t cols, const float *__restrict__ row_scale,
                                                               float *__restrict__ scale, float *__restrict__ partial,
                                                               int cw, int64_t rows_per_block) {
-    __shared__ float s_part[256];
+    __shared__ float s_part[256 * VW];
     const int tx = threadIdx.x % cw, ty = threadIdx.x / cw, nty = 256 / cw;
     const int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
     const int64_t r1 = min(rows, r0 + rows_per_block);
     float amax = 0.f;
-    for (int64_t c0 = 0; c0 < cols; c0 += cw) {
-        const int64_t c = c0 + tx;
-        float sum = 0.f;
+    for (int64_t c0 = 0; c0 < cols; c0 += (int64_t)cw * VW) {
+        const int64_t c = c0 + (int64_t)tx * VW;
+        float sum[VW];
+#pragma unroll
+        for (int k = 0; k < VW; ++k) sum[k] = 0.f;
         if (c < cols) {
+#pragma unroll 4
             for (int64_t r = r0 + ty; r < r1; r += nty) {
-                const float v = __ldcs(y + r * ldy + c) > 0.f ? __ldcs(g + r * ldg + c) : 0.f;
-                sum = __fadd_rn(sum, v);
-                float a = fabsf(v);
-                if (row_scale) a = __fmul_rn(a, fabsf(__ldg(row_scale + r)));
-                amax = fmaxf(amax, a);
+                float gv[VW], yv[VW];
+                if (VW == 4) {
+                    const float4 a = __ldcs(reinterpret_cast<const float4 *>(g + r * ldg + c));
+                    const float4 m = __ldcs(reinterpret_cast<const float4 *>(y + r * ldy + c));
+                    gv[0] = a.x; gv[VW > 1 ? 1 : 0] = a.y; gv[VW > 2 ? 2 : 0] = a.z; gv[VW > 3 ? 3 : 0] = a.w;
+                    yv[0] = m.x; yv[VW > 1 ? 1 : 0] = m.y; yv[VW > 2 ? 2 : 0] = m.z; yv[VW > 3 ? 3 : 0] = m.w;
+                } else {
+                    gv[0] = __ldcs(g + r * ldg + c);
+                    yv[0] = __ldcs(y + r * ldy + c);
+                }
+                const float rs = row_scale ? fabsf(__ldg(row_scale + r)) : 1.f;
+#pragma unroll
+                for (int k = 0; k < VW; ++k) {
+                    const float v = yv[k] > 0.f ? gv[k] : 0.f;
+                    sum[k] = __fadd_rn(sum[k], v);
+                    float a = fabsf(v);
+                    if (row_scale) a = __fmul_rn(a, rs);
+                    amax = fmaxf(amax, a);
+                }
             }
         }
         if (partial) {
             __syncthreads();
-            s_part[threadIdx.x] = sum;
+#pragma unroll
+            for (int k = 0; k < VW; ++k) s_part[threadIdx.x * VW + k] = sum[k];
             __syncthreads();
             if (ty == 0 && c < cols) {
-                float t = 0.f;
-                for (int k = 0; k < nty; ++k) t = __fadd_rn(t, s_part[k * cw + tx]);
-                partial[(int64_t)blockIdx.x * cols + c] = t;
+#pragma unroll
+                for (int k = 0; k < VW; ++k) {
+                    float t = 0.f;
+                    for (int j = 0; j < nty; ++j) t = __fadd_rn(t, s_part[(j * cw + tx) * VW + k]);
+                    partial[(int64_t)blockIdx.x * cols + c + k] = t;
+                }
             }
         }
     }
@@ -342,7 +366,7 @@ __global__ void __launch_bounds__(256) relu_grad_quant_kernel(const float *__res
 
 static int stats_blocks(int64_t rows) {
     int64_t b = ceil_div(rows, 64);
-    if (b > kNumSMs * 4) b = kNumSMs * 4;
+    if (b > kNumSMs * 8) b = kNumSMs * 8;
     return (int)(b < 1 ? 1 : b);
 }
 
@@ -364,11 +388,14 @@ extern "C" int tango_relu_grad_stats(const float *g, int64_t ldg, const float *y
     if (!g || !y) return TANGO_EINVAL;
     const int nb = stats_blocks(rows);
     if (colsum && (!scratch || scratch_bytes < tango_relu_grad_stats_scratch_bytes(rows, cols))) return TANGO_ESIZE;
+    const bool vec = cols % 4 == 0 && ldg % 4 == 0 && ldy % 4 == 0 && aligned(g, 16) && aligned(y, 16);
+    const int64_t tcols = vec ? cols / 4 : cols;   // columns in units of one thread's share
     int cw = 1;
-    while (cw < cols && cw < 256) cw <<= 1;
+    while (cw < tcols && cw < 256) cw <<= 1;
     const int64_t rpb = ceil_div(rows, nb);
-    relu_grad_stats_kernel<<<nb, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale,
-                                                   colsum ? (float *)scratch : nullptr, cw, rpb);
+    float *part = colsum ? (float *)scratch : nullptr;
+    if (vec) relu_grad_stats_kernel<4><<<nb, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, part, cw, rpb);
+    else relu_grad_stats_kernel<1><<<nb, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, part, cw, rpb);
     TANGO_LAUNCH_CHECK();
     if (colsum) {
         colsum_finish_kernel<<<(unsigned)ceil_div(cols, 256), 256, 0, stream>>>((const float *)scratch, nb, cols, colsum);
