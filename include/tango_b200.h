@@ -116,10 +116,12 @@ int tango_qgemm_forward(const float *x, int64_t ldx_f, const float *row_scale, c
                         int8_t *wq, int64_t ldwq, const float *bias, float *y, int64_t ldy, float *scale_y, int mode,
                         uint64_t seed, uint64_t call, int *status, tango_stream_t stream);
 
-/* dX[M,K] = float(dYq[M,N] . Wq[N,K]) * (sdy[0]*sw[0]).
+/* dX[M,K] = float(dYq[M,N] . Wq[N,K]) * (sdy[0]*sw[0]), then row r times row_scale[r] if row_scale != NULL (the
+ * backward of a left normalisation folded into the epilogue).
  * Replaces QGEMM_backward_gradX (cuda/src/cuda.cpp:191, cuda/src/QGEMM_backward.cu:21-48). */
 int tango_qgemm_dx(const int8_t *dyq, int64_t lddy, const int8_t *wq, int64_t ldw, int64_t m, int64_t n, int64_t k,
-                   const float *sdy, const float *sw, float *dx, int64_t lddx, int *status, tango_stream_t stream);
+                   const float *sdy, const float *sw, const float *row_scale, float *dx, int64_t lddx, int *status,
+                   tango_stream_t stream);
 
 /* dW[N,K] = float(dYq^T[N,M] . Xq[M,K]) * (sdy[0]*sx[0]); split over M with int32 atomics into `workspace`
  * (tango_qgemm_dw_workspace_bytes; contents on entry are irrelevant), then dequantised.

@@ -55,7 +55,7 @@ _SIGS = {
     "tango_qgemm_nt": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, P, c_int64, P, P, P], c_int),
     "tango_qgemm_forward": ([P, c_int64, P, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, c_int64, P, P,
                              c_int64, P, c_int, c_uint64, c_uint64, P, P], c_int),
-    "tango_qgemm_dx": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, P], c_int),
+    "tango_qgemm_dx": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, P, c_int64, P, P], c_int),
     "tango_qgemm_dw": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, c_int64, P, P], c_int),
     "tango_qgemm_dw_noalloc": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, P], c_int),
     "tango_qgemm_dw_noalloc_max_elems": ([], c_int64),

@@ -42,6 +42,7 @@ struct GemmParams {
     int32_t *ws;
     int64_t ldws;
     const float *sa, *sb, *bias;
+    const float *out_row_scale;  // optional: output row r is multiplied by out_row_scale[r] after dequantisation
     float *absmax;
     int *status;
     uint32_t tmem_cols;
@@ -270,6 +271,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                             for (int i = 0; i < 16; ++i) {
                                 const int col = col0 + half * 16 + i;
                                 float v = __fmul_rn((float)(int)r[i], sc);
+                                if (p.out_row_scale && row < p.M) v = __fmul_rn(v, __ldg(p.out_row_scale + row));
                                 if (p.bias && col < p.N) v = __fadd_rn(v, __ldg(p.bias + col));
                                 if (col < p.N && row < p.M) amax = fmaxf(amax, fabsf(v));
                                 r[i] = __float_as_uint(v);
@@ -491,6 +493,8 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m0 = mt * kTileM;
             const int row = m0 + q * 32 + lane;
+            const bool has_rs = p.out_row_scale != nullptr;
+            const float rs_row = (has_rs && row < p.M) ? __ldg(p.out_row_scale + row) : 1.f;
             const uint32_t tbase = tmem_base + buf * acc_cols + ((uint32_t)(q * 32) << 16);
             uint32_t nxt[16];
             if (half * 16 < p.n_tile) tmem_ld16_nowait(tbase + (uint32_t)(half * 16), nxt);
@@ -505,6 +509,7 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     float v = __fmul_rn((float)(int)r[i], sc);
+                    if (has_rs) v = __fmul_rn(v, rs_row);
                     if (has_bias && (full_cols || col0 + i < p.N)) v = __fadd_rn(v, __ldg(p.bias + col0 + i));
                     if (want_max && row < p.M && (full_cols || col0 + i < p.N)) amax = fmaxf(amax, fabsf(v));
                     r[i] = __float_as_uint(v);
@@ -637,6 +642,7 @@ struct GemmCall {
     int mode; int splits;
     float *out; int64_t ldo; int32_t *ws; int64_t ldws;
     const float *sa, *sb, *bias; float *absmax; int *status;
+    const float *out_row_scale = nullptr;
 };
 
 static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
@@ -661,6 +667,7 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
     if (p.stages > 6) p.stages = 6;
     p.mode = c.mode; p.out = c.out; p.ldo = c.ldo; p.ws = c.ws; p.ldws = c.ldws;
     p.sa = c.sa; p.sb = c.sb; p.bias = c.bias; p.absmax = c.absmax; p.status = c.status;
+    p.out_row_scale = c.out_row_scale;
     p.tmem_cols = 32;
     while ((int)p.tmem_cols < p.n_tile) p.tmem_cols <<= 1;
     if (c.K <= 0) return TANGO_EINVAL;
@@ -745,13 +752,14 @@ extern "C" int tango_qgemm_forward(const float *x, int64_t ldx_f, const float *r
 }
 
 extern "C" int tango_qgemm_dx(const int8_t *dyq, int64_t lddy, const int8_t *wq, int64_t ldw, int64_t m, int64_t n,
-                              int64_t k, const float *sdy, const float *sw, float *dx, int64_t lddx, int *status,
-                              tango_stream_t stream) {
+                              int64_t k, const float *sdy, const float *sw, const float *row_scale, float *dx,
+                              int64_t lddx, int *status, tango_stream_t stream) {
     if (m < 0 || n <= 0 || k < 0 || lddy < n || ldw < k || lddx < k) return TANGO_EINVAL;
     if (m == 0 || k == 0) return TANGO_OK;
     if (!dyq || !wq || !sdy || !sw || !dx) return TANGO_EINVAL;
     // D[m, k] = A[m, n] . B[n, k]: reduction n; B is stored with the reduction index as its row
     GemmCall c{dyq, lddy, 0, wq, ldw, 1, m, k, n, 0, 1, dx, lddx, nullptr, 0, sdy, sw, nullptr, nullptr, status};
+    c.out_row_scale = row_scale;
     return launch_gemm(c, (cudaStream_t)stream);
 }
 

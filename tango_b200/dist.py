@@ -187,9 +187,8 @@ class _dist_gcn_conv_fused(Function):
         if dg.scale_mode == "global":
             dist.all_reduce(sdH, op=dist.ReduceOp.MAX)
         dHq, _ = K.quantize(dH, sdH, mode=mode_q, seed=seed)
-        dX, dW = K.QGEMM_backward(dHq, Xq, Wq, sdH, sX, sW, ctx.needs_input_grad[1], ctx.needs_input_grad[2])
-        if dX is not None:
-            dX = dX * dg.out_norm.unsqueeze(1)
+        dX, dW = K.QGEMM_backward(dHq, Xq, Wq, sdH, sX, sW, ctx.needs_input_grad[1], ctx.needs_input_grad[2],
+                                  dx_row_scale=dg.out_norm)
         return None, dX, dW, db, None
 
 

@@ -87,9 +87,8 @@ class _gcn_conv_fused(Function):
             kernels._quantize_into(dZq, g1, sdZ, mode_q, seed, call, in_norm)
         dH = kernels.csr_SPMM(ctx.g, dZq, sdZ, True)
         dHq, sdH = kernels.quantize(dH, mode=mode_q, seed=seed)
-        dX, dW = kernels.QGEMM_backward(dHq, Xq, Wq, sdH, sX, sW, ctx.needs_input_grad[1], ctx.needs_input_grad[2])
-        if dX is not None:
-            dX = dX * out_norm.unsqueeze(1)
+        dX, dW = kernels.QGEMM_backward(dHq, Xq, Wq, sdH, sX, sW, ctx.needs_input_grad[1], ctx.needs_input_grad[2],
+                                        dx_row_scale=out_norm)   # backward of the left norm, in the GEMM epilogue
         return None, dX, dW, db, None, None, None
 
 

@@ -199,14 +199,14 @@ def _qgemm_nt(Y, X_q, W_q, scaleX, scaleW, bias=None, scaleY=None):
     launch_counter[0] += 1
 
 
-def _qgemm_gradX(dX, dY_q, W_q, scaledY, scaleW):
+def _qgemm_gradX(dX, dY_q, W_q, scaledY, scaleW, row_scale=None):
     _, m, n, lddy = _matrix(dY_q)
     _, n2, k, ldw = _matrix(W_q)
     assert n == n2
     _, _, _, lddx = _matrix(dX)
     st = _status_word(dX.device)
     with torch.cuda.device(dX.device):
-        check(lib.tango_qgemm_dx(_p(dY_q), lddy, _p(W_q), ldw, m, n, k, _p(scaledY), _p(scaleW), _p(dX), lddx, _p(st),
+        check(lib.tango_qgemm_dx(_p(dY_q), lddy, _p(W_q), ldw, m, n, k, _p(scaledY), _p(scaleW), _p(row_scale), _p(dX), lddx, _p(st),
                                  _stream()), "QGEMM_backward_gradX")
     launch_counter[0] += 1
 
@@ -427,14 +427,14 @@ def QGEMM_forward(x, x_, scaleX, w, w_, scaleW, bias=None, isReduce=False, mode:
     return (out_fp, scale_out) if isReduce else out_fp
 
 
-def QGEMM_backward(dY, X, W, scaledY, scaleX, scaleW, X_need=True, W_need=True):
-    """cuda/kernels.py:97-111."""
+def QGEMM_backward(dY, X, W, scaledY, scaleX, scaleW, X_need=True, W_need=True, dx_row_scale=None):
+    """cuda/kernels.py:97-111.  dx_row_scale (optional, [M]) multiplies row r of dX in the GEMM epilogue."""
     assert scaledY.is_cuda and dY.is_cuda
     dX, dW = None, None
     if X_need:
         assert W.is_cuda and scaleW.is_cuda
         dX = torch.empty(X.shape, dtype=torch.float32, device=X.device)
-        cuda_kernels.QGEMM_backward_gradX(dX, dY, W, scaledY, scaleW)
+        cuda_kernels.QGEMM_backward_gradX(dX, dY, W, scaledY, scaleW, dx_row_scale)
     if W_need:
         assert X.is_cuda and scaleX.is_cuda
         dW = torch.empty(W.shape, dtype=torch.float32, device=X.device)
