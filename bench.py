@@ -321,11 +321,11 @@ def run_ours(args):
         roof = {"kernel": "spmm_kernel<16,copy_u> F=256 (layer-1 aggregation)", "bound": "hbm", "achieved": ach,
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                 # dram__bytes_read+write of one ncu capture on a 20.2 M-edge copy of the graph (397 MB), plus 4 B for
-                # every further edge of the index stream (profiles/spmm_copy_u_f256_ncu.md)
+                # every further edge of the index stream
                 "traffic": 397_105_920 + 4 * max(0, n_edges - 20_232_965),
                 "peak_source": peak_kind, "kernel_ms": k_ms, "algorithmic_bytes": alg,
                 "gathered_bytes_per_s_GB": touched / (k_ms * 1e-3) / 1e9,
-                "note": "gathers of E*F bytes are served by L2; see DESIGN.md"}
+                "note": "the E*F gathered bytes are served by L2; HBM sees each feature row about once"}
 
     cpu_base = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline and not name.startswith("gat"):

@@ -109,7 +109,7 @@ int tango_qgemm_nt(const int8_t *xq, int64_t ldx, const int8_t *wq, int64_t ldw,
  * mode and the scales sx, sw, writes the int8 copies xq, wq that the backward pass re-uses, and computes the GEMM
  * above.  Stochastic mode draws X with `call`, W with `call`+1.  (The reference quantizes on load inside the GEMM,
  * cuda/src/iterator.h:155-164; here the quantizer is a separate streaming kernel in front of the TMA-fed GEMM -- a
- * quantize-on-load producer for the tcgen05 kernel was built and measured 3x slower, see DESIGN.md.)
+ * quantize-on-load producer for the tcgen05 kernel was built, was bit-exact and measured 3x slower.)
  * Replaces QGEMM_forward (cuda/src/cuda.cpp:183, cuda/kernels.py:79-94). */
 int tango_qgemm_forward(const float *x, int64_t ldx_f, const float *row_scale, const float *w, int64_t ldw_f,
                         int64_t m, int64_t n, int64_t k, const float *sx, const float *sw, int8_t *xq, int64_t ldxq,
