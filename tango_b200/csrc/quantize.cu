@@ -313,13 +313,24 @@ __global__ void __launch_bounds__(256) relu_grad_stats_kernel(const float *__res
     block_absmax_to_scale(amax, scale);
 }
 
-__global__ void __launch_bounds__(256) colsum_finish_kernel(const float *__restrict__ partial, int nblocks,
-                                                            int64_t cols, float *__restrict__ colsum) {
-    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
+// Adds the per-block partial column sums in a fixed order (32 interleaved chains per column, then the 32 chain totals
+// in order), so the bias gradient does not depend on scheduling.
+__global__ void __launch_bounds__(1024) colsum_finish_kernel(const float *__restrict__ partial, int nblocks,
+                                                             int64_t cols, float *__restrict__ colsum) {
+    __shared__ float part[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t c = (int64_t)blockIdx.x * 32 + tx;
     float t = 0.f;
-    for (int b = 0; b < nblocks; ++b) t = __fadd_rn(t, partial[(int64_t)b * cols + c]);
-    colsum[c] = t;
+    if (c < cols)
+        for (int b = ty; b < nblocks; b += 32) t = __fadd_rn(t, partial[(int64_t)b * cols + c]);
+    part[ty][tx] = t;
+    __syncthreads();
+    if (ty == 0 && c < cols) {
+        float r = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) r = __fadd_rn(r, part[k][tx]);
+        colsum[c] = r;
+    }
 }
 
 template <bool VEC4>
@@ -398,7 +409,7 @@ extern "C" int tango_relu_grad_stats(const float *g, int64_t ldg, const float *y
     else relu_grad_stats_kernel<1><<<nb, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, part, cw, rpb);
     TANGO_LAUNCH_CHECK();
     if (colsum) {
-        colsum_finish_kernel<<<(unsigned)ceil_div(cols, 256), 256, 0, stream>>>((const float *)scratch, nb, cols, colsum);
+        colsum_finish_kernel<<<(unsigned)ceil_div(cols, 32), 1024, 0, stream>>>((const float *)scratch, nb, cols, colsum);
         TANGO_LAUNCH_CHECK();
     }
     return TANGO_OK;

@@ -86,7 +86,7 @@ __device__ __forceinline__ void accumulate_one(int (&acc)[VEC], const VecLoad<VE
 // word holds one feature of the four neighbours; one 4-way dp4a against (1,1,1,1) -- or against the four neighbours'
 // int8 weights -- then adds all four into the int32 accumulator: 12 instructions per 16 gathered bytes.
 template <int VEC>
-__device__ __forceinline__ void accumulate_four(int (&acc)[VEC], const VecLoad<VEC> (&v)[4], uint32_t wvec) {
+__device__ __forceinline__ void accumulate_four(int (&acc)[VEC], const VecLoad<VEC> *v, uint32_t wvec) {
 #pragma unroll
     for (int wp = 0; wp < VEC / 4; ++wp) {
         const uint32_t a = v[0].w[wp], b = v[1].w[wp], c = v[2].w[wp], d = v[3].w[wp];
@@ -103,7 +103,7 @@ __device__ __forceinline__ void accumulate_four(int (&acc)[VEC], const VecLoad<V
 // On return every lane of group 0 (lane < G) holds the full sum for its bytes.  Lanes whose bytes lie beyond the
 // feature width run the same instruction stream on the row's first bytes (their sums are never stored), so the hot
 // loop over full batches of 32 neighbours carries no predicates at all.
-template <int VEC, int MODE>
+template <int VEC, int MODE, bool DEEP = false>
 __device__ __forceinline__ void gather_segment(int (&acc)[VEC], int beg, int end, int off, bool active,
                                                const SpmmArgs &a) {
     const int lane = threadIdx.x & 31;
@@ -119,6 +119,46 @@ __device__ __forceinline__ void gather_segment(int (&acc)[VEC], int beg, int end
     const uint32_t ld = (uint32_t)a.ld;   // 32 x 32 -> 64-bit products: one wide multiply per gathered row
     const int H = a.H;
     int j0 = beg;
+    if (DEEP && kFour && G == 4) {
+        // ---- narrow rows (four lanes per neighbour): a batch of 32 ids is only four gathers per lane, so two batches
+        // are taken together to keep eight gathers in flight per lane.
+        int nxt_a = 0, nxt_b = 0, nxt_ea = 0, nxt_eb = 0;
+        if (j0 + 64 <= end) {
+            nxt_a = a.indices ? __ldg(a.indices + j0 + lane) : j0 + lane;
+            nxt_b = a.indices ? __ldg(a.indices + j0 + 32 + lane) : j0 + 32 + lane;
+            if (MODE != MODE_COPY) {
+                nxt_ea = a.edge_ids ? __ldg(a.edge_ids + j0 + lane) : j0 + lane;
+                nxt_eb = a.edge_ids ? __ldg(a.edge_ids + j0 + 32 + lane) : j0 + 32 + lane;
+            }
+        }
+        for (; j0 + 64 <= end; j0 += 64) {
+            const int idx_a = nxt_a, idx_b = nxt_b, eid_a = nxt_ea, eid_b = nxt_eb;
+            if (j0 + 128 <= end) {
+                nxt_a = a.indices ? __ldg(a.indices + j0 + 64 + lane) : j0 + 64 + lane;
+                nxt_b = a.indices ? __ldg(a.indices + j0 + 96 + lane) : j0 + 96 + lane;
+                if (MODE != MODE_COPY) {
+                    nxt_ea = a.edge_ids ? __ldg(a.edge_ids + j0 + 64 + lane) : j0 + 64 + lane;
+                    nxt_eb = a.edge_ids ? __ldg(a.edge_ids + j0 + 96 + lane) : j0 + 96 + lane;
+                }
+            }
+            VecLoad<VEC> v[8];
+            uint32_t wv0 = 0x01010101u, wv1 = 0x01010101u;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int src_lane = grp + (u & 3) * 8;
+                const int idx = __shfl_sync(0xffffffffu, u < 4 ? idx_a : idx_b, src_lane);
+                v[u].load(base + (uint64_t)(uint32_t)idx * ld);
+                if (MODE == MODE_WEIGHT_LANE) {
+                    const int eid = __shfl_sync(0xffffffffu, u < 4 ? eid_a : eid_b, src_lane);
+                    const uint32_t wb = (uint32_t)(uint8_t)__ldg(wbase + (uint64_t)(uint32_t)eid * (uint32_t)H);
+                    if (u < 4) wv0 = (u == 0) ? wb : (wv0 | (wb << (8 * u)));
+                    else wv1 = (u == 4) ? wb : (wv1 | (wb << (8 * (u - 4))));
+                }
+            }
+            accumulate_four<VEC>(acc, v, wv0);
+            accumulate_four<VEC>(acc, v + 4, wv1);
+        }
+    }
     if (kFour && G >= U) {
         // ---- full batches: every shuffled index is valid, four loads in flight per lane, no predicates.
         // The indices of the next batch are fetched while the current one is processed.
@@ -203,14 +243,17 @@ __device__ __forceinline__ float finish_value(float v, int64_t row, int col, con
     return v;
 }
 
-template <int VEC, int MODE>
+template <int VEC, int MODE, bool DEEP = false>
 #ifndef SPMM_THREADS
 #define SPMM_THREADS 128
 #endif
 #ifndef SPMM_MINB
 #define SPMM_MINB 8
 #endif
-__global__ void __launch_bounds__(SPMM_THREADS, SPMM_MINB) spmm_kernel(const SpmmArgs a) {
+#ifndef SPMM_MINB_DEEP
+#define SPMM_MINB_DEEP 6
+#endif
+__global__ void __launch_bounds__(SPMM_THREADS, DEEP ? SPMM_MINB_DEEP : SPMM_MINB) spmm_kernel(const SpmmArgs a) {
     const int lane = threadIdx.x & 31;
     const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int sub = lane % a.G;
@@ -222,7 +265,7 @@ __global__ void __launch_bounds__(SPMM_THREADS, SPMM_MINB) spmm_kernel(const Spm
             const int off = fb + sub * VEC;
             const bool active = off < a.f_pad;
             int acc[VEC];
-            gather_segment<VEC, MODE>(acc, u.y, u.z, off, active, a);
+            gather_segment<VEC, MODE, DEEP>(acc, u.y, u.z, off, active, a);
             if (active && lane < a.G) {
 #pragma unroll
                 for (int i = 0; i < VEC; ++i)
@@ -243,7 +286,7 @@ __global__ void __launch_bounds__(SPMM_THREADS, SPMM_MINB) spmm_kernel(const Spm
             for (int i = 0; i < VEC; ++i) facc[i] = 0.f;
             for (int k = 0; k < a.nseg; ++k) {
                 int acc[VEC];
-                gather_segment<VEC, MODE>(acc, __ldg(ip + k), __ldg(ip + k + 1), off, active, a);
+                gather_segment<VEC, MODE, DEEP>(acc, __ldg(ip + k), __ldg(ip + k + 1), off, active, a);
                 const float sc = __ldg(a.scales + k);
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) facc[i] = __fadd_rn(facc[i], __fmul_rn((float)acc[i], sc));
@@ -380,6 +423,12 @@ static int pow2_ceil(int x) {
     return p;
 }
 
+#ifdef SPMM_NO_DEEP
+constexpr bool kDeepNarrow = false;
+#else
+constexpr bool kDeepNarrow = true;
+#endif
+
 template <int MODE>
 static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t stream) {
     if (a.n_rows == 0 || a.f == 0) return TANGO_OK;
@@ -427,7 +476,9 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
         else if (vec == 4) TANGO_SPMM_LAUNCH(4, MODE_WEIGHT_ELEM);
         else TANGO_SPMM_LAUNCH(1, MODE_WEIGHT_LANE);  // VEC == 1: a lane holds one byte, always inside one head
     } else {
-        if (vec == 16) TANGO_SPMM_LAUNCH(16, MODE);
+        if (vec == 16 && a.G == 4 && kDeepNarrow) {
+            if (blocks > 0) spmm_kernel<16, MODE, true><<<(unsigned)blocks, SPMM_THREADS, 0, stream>>>(a);
+        } else if (vec == 16) TANGO_SPMM_LAUNCH(16, MODE);
         else if (vec == 4) TANGO_SPMM_LAUNCH(4, MODE);
         else TANGO_SPMM_LAUNCH(1, MODE);
     }
