@@ -232,6 +232,21 @@ int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *indices, co
                                const int8_t *erq, int h, const float *sl, const float *sr, float slope, const float *a,
                                const float *da, float *dz, tango_stream_t stream);
 
+/* Edge softmax of plain fp32 scores: for every destination row v (CSC order) and head h
+ *   a[eid(j),h] = softmax_j( z[eid(j),h] * zmul )     over the incoming edges j of v,
+ * z and a fp32 [E, H] in edge-id order (edge_ids == NULL: slot j is edge j), h <= 8; zmul folds a constant factor
+ * such as HGT's 1/sqrt(d_k) into the pass.  Same row schedule arguments as tango_gat_edge_softmax.  Replaces
+ * dgl.ops.edge_softmax(g, t, norm_by='dst') (evaluation/test_HGT.py:59-60, evaluation/test_gat.py:146). */
+int tango_edge_softmax(const int32_t *indptr, const int32_t *edge_ids, const int32_t *row_order,
+                       int64_t n_block_rows, int64_t n_rows, const float *z, int h, float zmul, float *a,
+                       tango_stream_t stream);
+
+/* Gradient of tango_edge_softmax with respect to z: dz[eid(j),h] = a_j * (da_j - sum_k a_k da_k) * zmul.
+ * Replaces the autograd backward of dgl.ops.edge_softmax. */
+int tango_edge_softmax_bwd(const int32_t *indptr, const int32_t *edge_ids, const int32_t *row_order,
+                           int64_t n_block_rows, int64_t n_rows, int h, float zmul, const float *a, const float *da,
+                           float *dz, tango_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,7 +1,11 @@
-// Fused attention-weight pass of a GAT layer and its gradient.
+// Edge softmax over the incoming edges of every destination, forward and gradient, in two flavours.
 //
-// forward : a[e,h]  = softmax over the incoming edges of dst(e) of leaky_relu(el_q[src(e),h]*sl + er_q[dst(e),h]*sr)
-// backward: dz[e,h] = a * (da - sum_row a*da) * (z > 0 ? 1 : slope)   (PyTorch's LeakyReLU gradient convention at 0)
+// fused GAT attention:
+//   forward : a[e,h]  = softmax over the incoming edges of dst(e) of leaky_relu(el_q[src(e),h]*sl + er_q[dst(e),h]*sr)
+//   backward: dz[e,h] = a * (da - sum_row a*da) * (z > 0 ? 1 : slope)   (PyTorch's LeakyReLU gradient convention at 0)
+// plain scores (zin given):
+//   forward : a[e,h]  = softmax over the incoming edges of dst(e) of zin[e,h] * zmul
+//   backward: dz[e,h] = a * (da - sum_row a*da) * zmul
 //
 // A destination row is owned by a thread team: a whole CTA for the rows at the head of the degree-sorted order (a
 // power-law graph has rows with 10^5 incoming edges; one warp would serialise them), a warp for the rest.  All heads
@@ -24,6 +28,8 @@ struct GatArgs {
     float *att;          // forward: output; backward: input
     const float *datt;   // backward
     float *dz;           // backward
+    const float *zin;    // plain-score flavour: fp32 scores [E, H] in edge-id order (elq / erq / sl / sr unused)
+    float zmul;          // factor applied to zin before the softmax
 };
 
 __device__ __forceinline__ float leaky(float z, float slope) { return z >= 0.f ? z : __fmul_rn(z, slope); }
@@ -32,6 +38,17 @@ __device__ __forceinline__ float leaky(float z, float slope) { return z >= 0.f ?
 template <int HT>
 __device__ __forceinline__ void edge_logits(const GatArgs &a, int j, const float (&er)[kMaxHeads], float sl,
                                             float (&z)[kMaxHeads]) {
+    if (a.zin) {
+        const int64_t eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
+        if (HT == 4) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(a.zin + eid * 4));
+            z[0] = __fmul_rn(v.x, a.zmul); z[1] = __fmul_rn(v.y, a.zmul);
+            z[2] = __fmul_rn(v.z, a.zmul); z[3] = __fmul_rn(v.w, a.zmul);
+        } else {
+            for (int h = 0; h < a.H; ++h) z[h] = __fmul_rn(__ldg(a.zin + eid * a.H + h), a.zmul);
+        }
+        return;
+    }
     const int64_t s = __ldg(a.indices + j);
     if (HT == 4) {
         const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(a.elq + s * 4));
@@ -86,13 +103,13 @@ __device__ __forceinline__ void team_softmax_merge(float &m, float &s, float *sm
 
 template <int NT, int HT>
 __device__ __forceinline__ void softmax_row(const GatArgs &a, int64_t row, int tid, float *smem) {
-    const float sl = __ldg(a.sl), sr = __ldg(a.sr);
+    const float sl = a.zin ? 0.f : __ldg(a.sl), sr = a.zin ? 0.f : __ldg(a.sr);
     const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
     const int H = HT ? HT : a.H;
     float er[kMaxHeads], m[kMaxHeads], s[kMaxHeads];
 #pragma unroll
     for (int h = 0; h < kMaxHeads; ++h) {
-        er[h] = h < H ? __fmul_rn((float)__ldg(a.erq + row * H + h), sr) : 0.f;
+        er[h] = (h < H && !a.zin) ? __fmul_rn((float)__ldg(a.erq + row * H + h), sr) : 0.f;
         m[h] = -INFINITY; s[h] = 0.f;
     }
     for (int j = beg + tid; j < end; j += NT) {
@@ -128,13 +145,14 @@ __device__ __forceinline__ void softmax_row(const GatArgs &a, int64_t row, int t
 
 template <int NT, int HT>
 __device__ __forceinline__ void softmax_bwd_row(const GatArgs &a, int64_t row, int tid, float *smem) {
-    const float sl = __ldg(a.sl), sr = __ldg(a.sr);
+    const bool plain = a.zin != nullptr;   // backward of the plain flavour: zin is only a marker, never read
+    const float sl = plain ? 0.f : __ldg(a.sl), sr = plain ? 0.f : __ldg(a.sr);
     const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
     const int H = HT ? HT : a.H;
     float er[kMaxHeads], dot[kMaxHeads];
 #pragma unroll
     for (int h = 0; h < kMaxHeads; ++h) {
-        er[h] = h < H ? __fmul_rn((float)__ldg(a.erq + row * H + h), sr) : 0.f;
+        er[h] = (h < H && !plain) ? __fmul_rn((float)__ldg(a.erq + row * H + h), sr) : 0.f;
         dot[h] = 0.f;
     }
     for (int j = beg + tid; j < end; j += NT) {
@@ -152,22 +170,27 @@ __device__ __forceinline__ void softmax_bwd_row(const GatArgs &a, int64_t row, i
         if (h < H) dot[h] = team_sum<NT>(dot[h], smem);
     for (int j = beg + tid; j < end; j += NT) {
         float z[kMaxHeads];
-        edge_logits<HT>(a, j, er, sl, z);   // leaky(z) has the sign of z
+        if (!plain) edge_logits<HT>(a, j, er, sl, z);   // leaky(z) has the sign of z
         const int64_t eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
         if (HT == 4) {
             const float4 p = __ldg(reinterpret_cast<const float4 *>(a.att + eid * 4));
             const float4 g = __ldg(reinterpret_cast<const float4 *>(a.datt + eid * 4));
             float4 o = make_float4(p.x * (g.x - dot[0]), p.y * (g.y - dot[1]), p.z * (g.z - dot[2]),
                                    p.w * (g.w - dot[3]));
-            if (!(z[0] > 0.f)) o.x *= a.slope;
-            if (!(z[1] > 0.f)) o.y *= a.slope;
-            if (!(z[2] > 0.f)) o.z *= a.slope;
-            if (!(z[3] > 0.f)) o.w *= a.slope;
+            if (plain) {
+                o.x *= a.zmul; o.y *= a.zmul; o.z *= a.zmul; o.w *= a.zmul;
+            } else {
+                if (!(z[0] > 0.f)) o.x *= a.slope;
+                if (!(z[1] > 0.f)) o.y *= a.slope;
+                if (!(z[2] > 0.f)) o.z *= a.slope;
+                if (!(z[3] > 0.f)) o.w *= a.slope;
+            }
             *reinterpret_cast<float4 *>(a.dz + eid * 4) = o;
         } else {
             for (int h = 0; h < H; ++h) {
                 float o = __ldg(a.att + eid * H + h) * (__ldg(a.datt + eid * H + h) - dot[h]);
-                if (!(z[h] > 0.f)) o *= a.slope;
+                if (plain) o *= a.zmul;
+                else if (!(z[h] > 0.f)) o *= a.slope;
                 a.dz[eid * H + h] = o;
             }
         }
@@ -199,7 +222,8 @@ static int launch_gat(GatArgs &a, cudaStream_t stream) {
     if (a.n_block_rows < 0 || a.n_block_rows > a.n_rows) return TANGO_EINVAL;
     const int64_t blocks = a.n_block_rows + ceil_div(a.n_rows - a.n_block_rows, 8);
     if (blocks > 0x7fffffff) return TANGO_ESIZE;
-    const bool h4 = a.H == 4 && aligned(a.att, 16) && aligned(a.elq, 4) && (!BWD || (aligned(a.datt, 16) && aligned(a.dz, 16)));
+    const bool h4 = a.H == 4 && aligned(a.att, 16) && (a.zin ? aligned(a.zin, 16) : aligned(a.elq, 4)) &&
+                    (!BWD || (aligned(a.datt, 16) && aligned(a.dz, 16)));
     if (h4) gat_softmax_kernel<4, BWD><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else gat_softmax_kernel<0, BWD><<<(unsigned)blocks, 256, 0, stream>>>(a);
     TANGO_LAUNCH_CHECK();
@@ -215,7 +239,8 @@ extern "C" int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indi
                                       const int8_t *elq, const int8_t *erq, int h, const float *sl, const float *sr,
                                       float slope, float *a, tango_stream_t stream) {
     if (n_rows > 0 && (!indptr || !indices || !elq || !erq || !sl || !sr || !a)) return TANGO_EINVAL;
-    GatArgs g{indptr, indices, edge_ids, row_order, n_rows, n_block_rows, elq, erq, h, sl, sr, slope, a, nullptr, nullptr};
+    GatArgs g{indptr, indices, edge_ids, row_order, n_rows, n_block_rows, elq, erq, h, sl, sr, slope, a, nullptr, nullptr,
+              nullptr, 1.f};
     return launch_gat<false>(g, (cudaStream_t)stream);
 }
 
@@ -226,6 +251,24 @@ extern "C" int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *
                                           tango_stream_t stream) {
     if (n_rows > 0 && (!indptr || !indices || !elq || !erq || !sl || !sr || !a || !da || !dz)) return TANGO_EINVAL;
     GatArgs g{indptr, indices, edge_ids, row_order, n_rows, n_block_rows, elq, erq, h, sl, sr, slope,
-              const_cast<float *>(a), da, dz};
+              const_cast<float *>(a), da, dz, nullptr, 1.f};
+    return launch_gat<true>(g, (cudaStream_t)stream);
+}
+
+extern "C" int tango_edge_softmax(const int32_t *indptr, const int32_t *edge_ids, const int32_t *row_order,
+                                  int64_t n_block_rows, int64_t n_rows, const float *z, int h, float zmul, float *a,
+                                  tango_stream_t stream) {
+    if (n_rows > 0 && (!indptr || !z || !a)) return TANGO_EINVAL;
+    GatArgs g{indptr, nullptr, edge_ids, row_order, n_rows, n_block_rows, nullptr, nullptr, h, nullptr, nullptr, 1.f,
+              a, nullptr, nullptr, z, zmul};
+    return launch_gat<false>(g, (cudaStream_t)stream);
+}
+
+extern "C" int tango_edge_softmax_bwd(const int32_t *indptr, const int32_t *edge_ids, const int32_t *row_order,
+                                      int64_t n_block_rows, int64_t n_rows, int h, float zmul, const float *a,
+                                      const float *da, float *dz, tango_stream_t stream) {
+    if (n_rows > 0 && (!indptr || !a || !da || !dz)) return TANGO_EINVAL;
+    GatArgs g{indptr, nullptr, edge_ids, row_order, n_rows, n_block_rows, nullptr, nullptr, h, nullptr, nullptr, 1.f,
+              const_cast<float *>(a), da, dz, a, zmul};
     return launch_gat<true>(g, (cudaStream_t)stream);
 }

@@ -1,8 +1,11 @@
 """The evaluation models of the reference (QGraphConv / GCN from evaluation/test_gcn.py:40-175, QGATConv / GAT from
-evaluation/test_gat.py:30-224) re-hosted on the DGL-free `Graph`, built only from the quantized operators of this
-package.  They are the callers of the hot path: the epoch benchmark and the end-to-end parity tests run them.
+evaluation/test_gat.py:30-224, HGT from evaluation/test_HGT.py:27-67, the link-prediction GCN and its scorer from
+evaluation/link_pred_gcn.py:113-165) re-hosted on the DGL-free `Graph`, built only from the quantized operators of
+this package.  They are the callers of the hot path: the epoch benchmark and the end-to-end parity tests run them.
 """
 from __future__ import annotations
+
+import math
 
 import torch
 import torch.nn as nn
@@ -11,7 +14,7 @@ from torch.autograd.function import Function, once_differentiable
 
 from . import config, kernels
 from .QLinear import QLinear, Qlinear_func, Qlinear_func_reduce
-from .SDDMM import sddmm_u_add_v
+from .SDDMM import sddmm_u_add_v, sddmm_u_dot_v
 from .SPMM import spmm_copy_u, spmm_u_mul_e
 
 
@@ -173,37 +176,27 @@ class GCN(nn.Module):
 
 # ---------------------------------------------------------------------------------------------------- GAT
 class _edge_softmax_fn(Function):
-    """Softmax of edge scores over the incoming edges of every destination, per head (the reference calls
-    dgl.ops.edge_softmax, evaluation/test_gat.py:146).  fp32, as in the reference."""
+    """Softmax of edge scores (times a constant factor) over the incoming edges of every destination, per head (the
+    reference calls dgl.ops.edge_softmax, evaluation/test_gat.py:146, evaluation/test_HGT.py:60).  fp32, as in the
+    reference; one team-per-row kernel per direction."""
 
     @staticmethod
-    def forward(ctx, g, e):
-        _, dst = g.coo
-        shape = e.shape
-        e2 = e.reshape(shape[0], -1)
-        n = g.num_nodes()
-        idx = dst.long().unsqueeze(1).expand_as(e2)
-        m = torch.full((n, e2.shape[1]), float("-inf"), device=e.device).scatter_reduce(0, idx, e2, "amax")
-        ex = torch.exp(e2 - m[dst.long()])
-        s = torch.zeros((n, e2.shape[1]), device=e.device).index_add_(0, dst.long(), ex)
-        a = ex / s[dst.long()]
+    def forward(ctx, g, e, factor):
+        a = kernels.edge_softmax_fwd(g, e, factor)
         ctx.save_for_backward(a)
-        ctx.g = g
-        return a.reshape(shape)
+        ctx.g, ctx.factor = g, factor
+        return a
 
     @staticmethod
     @once_differentiable
     def backward(ctx, da):
         (a,) = ctx.saved_tensors
-        _, dst = ctx.g.coo
-        da2 = da.reshape(a.shape)
-        t = a * da2
-        acc = torch.zeros((ctx.g.num_nodes(), a.shape[1]), device=a.device).index_add_(0, dst.long(), t)
-        return None, (t - a * acc[dst.long()]).reshape(da.shape)
+        return None, kernels.edge_softmax_bwd(ctx.g, a, da, ctx.factor), None
 
 
-def edge_softmax(g, e):
-    return _edge_softmax_fn.apply(g, e)
+def edge_softmax(g, e, factor: float = 1.0):
+    """softmax over each destination's incoming edges of e * factor."""
+    return _edge_softmax_fn.apply(g, e, factor)
 
 
 class _gat_attention_fused(Function):
@@ -322,3 +315,75 @@ class GAT(nn.Module):
         for l in range(self.num_layers - 1):
             h = self.gat_layers[l](self.g, h).flatten(1)
         return self.gat_layers[-1](self.g, h).mean(1)
+
+
+# ---------------------------------------------------------------------------------------------------- HGT
+class HGT(nn.Module):
+    """Single-relation heterogeneous-graph-transformer layer of evaluation/test_HGT.py:27-67: six QLinear
+    projections, int8 per-head dot-product scores (sddmm_u_dot_v), 1/sqrt(d_k), edge softmax over each destination's
+    incoming edges (fp32, as in the reference), int8 attention-weighted aggregation (spmm_u_mul_e)."""
+
+    def __init__(self, in_dim, out_dim, n_heads, dropout=0.2, use_norm=False):
+        super().__init__()
+        assert out_dim % n_heads == 0, "out_dim must be a multiple of n_heads"
+        self.in_dim, self.out_dim, self.n_heads = in_dim, out_dim, n_heads
+        self.d_k = out_dim // n_heads
+        self.sqrt_dk = math.sqrt(self.d_k)
+        self.q_linear = QLinear(in_dim, out_dim)
+        self.k_linear = QLinear(in_dim, out_dim)
+        self.v_linear = QLinear(in_dim, out_dim)
+        self.msg_linear = QLinear(out_dim, out_dim)
+        self.attn_linear = QLinear(out_dim, out_dim)
+        self.a_linear = QLinear(out_dim, out_dim)
+        self.norm = nn.LayerNorm(out_dim) if use_norm else nn.Identity()
+
+    def forward(self, g, h):
+        k = self.attn_linear(self.k_linear(h)).view(-1, self.n_heads, self.d_k)
+        v = self.msg_linear(self.v_linear(h)).view(-1, self.n_heads, self.d_k)
+        q = self.q_linear(h).view(-1, self.n_heads, self.d_k)
+        t = sddmm_u_dot_v.apply(g, k, q)
+        attn = edge_softmax(g, t, 1.0 / self.sqrt_dk)     # the reference divides t by sqrt(d_k) first
+        out = spmm_u_mul_e.apply(g, v, attn).view(-1, self.out_dim)
+        return self.a_linear(out)
+
+
+# ---------------------------------------------------------------------------------------------------- link prediction
+def construct_negative_graph(graph, k, generator=None):
+    """k random destinations per source of every edge (evaluation/link_pred_gcn.py:160-165) as a `Graph` over the
+    same nodes, preprocessed for the quantized operators."""
+    from .graph import Graph
+    from .util import graph_preprocess
+    src, _ = graph.coo
+    neg_src = src.long().repeat_interleave(k)
+    neg_dst = torch.randint(0, graph.num_nodes(), (neg_src.numel(),), device=src.device, generator=generator)
+    return graph_preprocess(Graph(neg_src, neg_dst, graph.num_nodes()))
+
+
+class LinkPredGCN(nn.Module):
+    """GCN encoder plus dot-product edge scorer (evaluation/link_pred_gcn.py:113-147): node embeddings from
+    QGraphConv layers on the positive graph, then score[e] = <h[src(e)], h[dst(e)]> on int8 operands for the edges
+    of the positive and of the negative graph.  Returns (pos_score [E+,1,1], neg_score [E-,1,1])."""
+
+    def __init__(self, in_feats, n_hidden, n_classes, n_layers, activation=F.relu, dropout=0.0):
+        super().__init__()
+        self.layers = nn.ModuleList([QGraphConv(in_feats, n_hidden, activation=activation)])
+        for _ in range(n_layers - 1):
+            self.layers.append(QGraphConv(n_hidden, n_hidden, activation=activation))
+        self.layers.append(QGraphConv(n_hidden, n_classes))
+        self.dropout = nn.Dropout(p=dropout)
+
+    def forward(self, features, pos_graph, neg_graph):
+        h = features
+        for i, layer in enumerate(self.layers):
+            if i != 0:
+                h = self.dropout(h)
+            h = layer(pos_graph, h)
+        h = h.unsqueeze(1)
+        return sddmm_u_dot_v.apply(pos_graph, h, h), sddmm_u_dot_v.apply(neg_graph, h, h)
+
+
+def link_pred_loss(pos_score, neg_score):
+    """Binary cross-entropy on the logits, positives labelled 1 and negatives 0 (evaluation/link_pred_gcn.py:150-157)."""
+    score = torch.cat([pos_score, neg_score])
+    label = torch.cat([torch.ones_like(pos_score), torch.zeros_like(neg_score)])
+    return F.binary_cross_entropy_with_logits(score, label)

@@ -529,6 +529,44 @@ def gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, slope: float = 0.2):
     return dz
 
 
+def edge_softmax_fwd(g, z: torch.Tensor, zmul: float = 1.0) -> torch.Tensor:
+    """Softmax of fp32 edge scores z [E, H, ...] (times zmul) over the incoming edges of every destination; the
+    reference calls dgl.ops.edge_softmax (evaluation/test_HGT.py:60).  Returns fp32 of z's shape."""
+    assert z.is_cuda and z.dtype == torch.float32
+    indptr, _, edge_ids = _bundle(g, False)
+    z2 = z.reshape(z.shape[0], -1).contiguous()
+    h = z2.shape[1]
+    assert z2.shape[0] == g.num_edges(), "one score row per edge"
+    if h > 8:
+        raise ValueError("edge_softmax: at most 8 heads")
+    a = torch.empty_like(z2)
+    with torch.cuda.device(z.device):
+        sched = _schedule(g, False)
+        order = sched.row_order if sched is not None else None
+        check(lib.tango_edge_softmax(_p(indptr), _p(edge_ids), _p(order),
+                                     sched.n_block_rows if sched is not None else 0, g.num_nodes(), _p(z2), h,
+                                     float(zmul), _p(a), _stream()), "edge_softmax")
+    launch_counter[0] += 1
+    return a.view(z.shape)
+
+
+def edge_softmax_bwd(g, a: torch.Tensor, da: torch.Tensor, zmul: float = 1.0) -> torch.Tensor:
+    """Gradient of `edge_softmax_fwd` with respect to z."""
+    indptr, _, edge_ids = _bundle(g, False)
+    a2 = a.reshape(a.shape[0], -1).contiguous()
+    da2 = da.reshape(a2.shape).contiguous()
+    h = a2.shape[1]
+    dz = torch.empty_like(a2)
+    with torch.cuda.device(a.device):
+        sched = _schedule(g, False)
+        order = sched.row_order if sched is not None else None
+        check(lib.tango_edge_softmax_bwd(_p(indptr), _p(edge_ids), _p(order),
+                                         sched.n_block_rows if sched is not None else 0, g.num_nodes(), h, float(zmul),
+                                         _p(a2), _p(da2), _p(dz), _stream()), "edge_softmax_bwd")
+    launch_counter[0] += 1
+    return dz.view(a.shape)
+
+
 def relu_grad_stats(g: torch.Tensor, y: torch.Tensor, row_scale: Optional[torch.Tensor] = None,
                     want_colsum: bool = True):
     """(scale, column sums or None) of the masked gradient (y > 0 ? g : 0); the scale includes row_scale."""

@@ -249,3 +249,72 @@ def test_relu_grad_fusion_kernels(cuda):
         q2, s2, cs2 = K.relu_grad_quantize(torch.from_numpy(g).cuda(), torch.from_numpy(y).cuda(),
                                            torch.from_numpy(rs).cuda(), True, 2, 11, 3)
         assert torch.equal(cs, cs2) and torch.equal(q, q2)          # fixed summation order: run-to-run identical
+
+
+def test_hgt_layer_close_to_fp32(cuda):
+    """HGT layer (six QLinear, int8 u_dot_v scores, edge softmax, int8 u_mul_e) against the same layer in fp32."""
+    from tango_b200.gnn import HGT
+    g = _setup(900, 12000, 17)
+    n = g.num_nodes()
+    src, dst = [t.long() for t in g.coo]
+    torch.manual_seed(9)
+    x = torch.randn(n, 64, device="cuda", requires_grad=True)
+    m = HGT(64, 32, 4).cuda()
+    out = m(g, x)
+    out.square().mean().backward()
+    assert out.shape == (n, 32) and torch.isfinite(out).all()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in m.parameters())
+
+    def lin(layer, t):
+        return F.linear(t, layer.weight, layer.bias)
+
+    xr = x.detach().clone().requires_grad_(True)
+    k = lin(m.attn_linear, lin(m.k_linear, xr)).view(n, 4, 8)
+    v = lin(m.msg_linear, lin(m.v_linear, xr)).view(n, 4, 8)
+    q = lin(m.q_linear, xr).view(n, 4, 8)
+    t = (k[src] * q[dst]).sum(-1, keepdim=True) / m.sqrt_dk
+    a = B.edge_softmax(dst.cpu(), t.detach().cpu(), n).cuda()
+    ref = lin(m.a_linear, torch.zeros(n, 4, 8, device="cuda").index_add_(0, dst, v[src] * a).view(n, 32))
+    # six chained int8 GEMMs and two int8 graph operators: per-tensor quantisation error accumulates to a few percent
+    rel = ((out - ref).norm() / ref.norm()).item()
+    cos = torch.nn.functional.cosine_similarity(out.flatten(), ref.flatten(), dim=0).item()
+    assert rel < 0.1 and cos > 0.995, (rel, cos)
+    # the graph part alone, fed with the layer's own (quantized-GEMM) projections, is much tighter
+    with torch.no_grad():
+        kq = m.attn_linear(m.k_linear(x)).view(n, 4, 8)
+        vq = m.msg_linear(m.v_linear(x)).view(n, 4, 8)
+        qq = m.q_linear(x).view(n, 4, 8)
+        tq = (kq[src] * qq[dst]).sum(-1, keepdim=True) / m.sqrt_dk
+        aq = B.edge_softmax(dst.cpu(), tq.cpu(), n).cuda()
+        agg_ref = torch.zeros(n, 4, 8, device="cuda").index_add_(0, dst, vq[src] * aq)
+        from tango_b200.gnn import edge_softmax
+        import tango_b200 as T
+        agg = T.spmm_u_mul_e.apply(g, vq, edge_softmax(g, T.sddmm_u_dot_v.apply(g, kq, qq), 1.0 / m.sqrt_dk))
+        rel_g = ((agg - agg_ref).norm() / agg_ref.norm()).item()
+        assert rel_g < 0.05, rel_g
+
+
+def test_link_prediction_scores_and_loss(cuda):
+    """GCN encoder + int8 u_dot_v scorer on a positive and a sampled negative graph against fp32 scores."""
+    from tango_b200.gnn import LinkPredGCN, construct_negative_graph, link_pred_loss
+    g = _setup(700, 8000, 19)
+    n = g.num_nodes()
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    neg = construct_negative_graph(g, 2, generator=gen)
+    assert neg.num_edges() == 2 * g.num_edges() and neg.num_nodes() == n
+    torch.manual_seed(4)
+    x = torch.randn(n, 32, device="cuda")
+    m = LinkPredGCN(32, 16, 16, 1).cuda()
+    pos, ngs = m(x, g, neg)
+    assert pos.shape == (g.num_edges(), 1, 1) and ngs.shape == (neg.num_edges(), 1, 1)
+    loss = link_pred_loss(pos, ngs)
+    loss.backward()
+    assert torch.isfinite(loss) and all(torch.isfinite(p.grad).all() for p in m.parameters())
+    with torch.no_grad():
+        h = x
+        for layer in m.layers:
+            h = layer(g, h)
+        for graph, score in ((g, pos), (neg, ngs)):
+            s, d = [t.long() for t in graph.coo]
+            ref = (h[s] * h[d]).sum(-1)
+            assert (score.flatten() - ref).abs().max() / ref.abs().max() < 0.05

@@ -314,6 +314,41 @@ def test_gat_edge_softmax(cuda):
     np.testing.assert_allclose(sums, 1.0, rtol=1e-5)
 
 
+@pytest.mark.parametrize("heads,order", [(4, "dst"), (4, "append"), (1, "dst"), (3, "append"), (8, "dst")])
+def test_edge_softmax_plain_scores(cuda, heads, order):
+    """Plain fp32 edge softmax (HGT's use) against the oracle, forward and gradient, with and without the edge-id
+    indirection, incl. a destination with tens of thousands of incoming edges (CTA-per-row path)."""
+    import tango_b200 as T
+    from tango_b200 import kernels as K
+    from tango_b200.graph import Graph, rmat_graph
+    if order == "dst" and heads == 4:
+        n = 3000                                             # star: node 0 receives an edge from everybody, 10 times
+        src = torch.cat([torch.arange(n).repeat(10), torch.arange(n)])
+        dst = torch.cat([torch.zeros(10 * n, dtype=torch.long), (torch.arange(n) * 7 + 1) % n])
+        g = Graph(src, dst, n).to("cuda")
+    else:
+        g = rmat_graph(400, 5000, 37, device="cuda", edge_order=order)
+    T.graph_preprocess(g)
+    (_, csc, src_np, dst_np) = _np_graph(g)
+    e = g.num_edges()
+    rng = np.random.default_rng(heads)
+    z = (rng.standard_normal((e, heads)) * 3).astype(np.float32)
+    zmul = 0.35
+    a = K.edge_softmax_fwd(g, _dev(z).view(e, heads, 1), zmul)
+    assert a.shape == (e, heads, 1)
+    ref = O.edge_softmax(csc[0], csc[2], (z * np.float32(zmul)).astype(np.float32))
+    np.testing.assert_allclose(a.cpu().numpy().reshape(e, heads), ref, rtol=1e-4, atol=1e-7)
+    # gradient against autograd of the same formula
+    da = torch.from_numpy(rng.standard_normal((e, heads)).astype(np.float32)).cuda()
+    dz = K.edge_softmax_bwd(g, a, da.view(e, heads, 1), zmul).reshape(e, heads)
+    zt = _dev(z).requires_grad_(True)
+    dstl = torch.from_numpy(dst_np).long().cuda()
+    ex = torch.exp(zt * zmul - 2.0)
+    ssum = torch.zeros(g.num_nodes(), heads, device="cuda").index_add_(0, dstl, ex)
+    (ex / ssum[dstl] * da).sum().backward()
+    assert (dz - zt.grad).abs().max() < 1e-4 * max(1.0, zt.grad.abs().max().item())
+
+
 # ------------------------------------------------------------------------------------------------ empty inputs
 def test_empty_graph_and_rows(cuda):
     from tango_b200 import kernels as K
