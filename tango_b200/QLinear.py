@@ -9,15 +9,47 @@ from torch.autograd.function import Function, once_differentiable
 from . import config, kernels
 
 
+# The few most recently quantized activations: (tensor kept alive so its address cannot be recycled, version, key,
+# Xq, sX), newest last.  Four entries cover HGT's interleaved k / attn / v / msg / q projections.
+_shared_input = []
+_SHARED_SLOTS = 4
+
+
+def clear_shared_input() -> None:
+    _shared_input.clear()
+
+
+def _input_key(X, mode):
+    return (X.data_ptr(), tuple(X.shape), tuple(X.stride()), X.device, mode, config.seed())
+
+
 def _forward_common(ctx, X, W, b, want_scale):
     """Forward of cuda/QLinear.py:28-35,52-60: absmax scales of X and W, fused quantize + GEMM (+ output scale),
-    and the quantized operands cached for the backward pass."""
-    sX = kernels.cuda_kernels.get_scale(X)
+    and the quantized operands cached for the backward pass.  With config.share_quantized_inputs() a layer whose
+    input is the tensor the previous layer just quantized (same memory, same version) re-uses that int8 copy."""
+    mode = config.mode_for("gemm_fwd")
     sW = kernels.cuda_kernels.get_scale(W)
-    Xq = kernels.alloc_int8(X.shape, X.device)
-    Wq = kernels.alloc_int8(W.shape, X.device)
-    res = kernels.QGEMM_forward(X, Xq, sX, W, Wq, sW, b, want_scale, mode=config.mode_for("gemm_fwd"),
-                                seed=config.seed())
+    hit = None
+    if config.sharing_quantized_inputs() and mode != kernels.ROUND_STOCHASTIC:
+        key = _input_key(X, mode)
+        for ent in _shared_input:
+            if ent[1] == X._version and ent[2] == key:
+                hit = ent
+    if hit is not None:
+        Xq, sX = hit[3], hit[4]
+        Wq, _ = kernels.quantize(W, sW, mode=mode, seed=config.seed())
+        out = torch.empty((X.size(0), W.size(0)), dtype=torch.float32, device=X.device)
+        sY = torch.zeros_like(sX) if want_scale else None
+        kernels._qgemm_nt(out, Xq, Wq, sX, sW, b, sY)
+        res = (out, sY) if want_scale else out
+    else:
+        sX = kernels.cuda_kernels.get_scale(X)
+        Xq = kernels.alloc_int8(X.shape, X.device)
+        Wq = kernels.alloc_int8(W.shape, X.device)
+        res = kernels.QGEMM_forward(X, Xq, sX, W, Wq, sW, b, want_scale, mode=mode, seed=config.seed())
+        if config.sharing_quantized_inputs() and mode != kernels.ROUND_STOCHASTIC:
+            _shared_input.append((X, X._version, _input_key(X, mode), Xq, sX))
+            del _shared_input[:-_SHARED_SLOTS]
     ctx.backward_cache = (Xq, sX, Wq, sW, b)
     return res
 

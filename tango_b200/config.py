@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from ._lib import ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_TRUNC
 
-_state = {"rounding": "reference", "seed": 0}
+_state = {"rounding": "reference", "seed": 0, "share_quantized_inputs": False}
 
 
 def set_rounding(mode: str = "reference", seed: int = 0) -> None:
@@ -32,3 +32,19 @@ def mode_for(site: str) -> int:
     if r == "reference":
         return ROUND_TRUNC if site == "gemm_fwd" else ROUND_NEAREST
     return {"nearest": ROUND_NEAREST, "trunc": ROUND_TRUNC, "stochastic": ROUND_STOCHASTIC}[r]
+
+
+def share_quantized_inputs(enable: bool = True) -> None:
+    """When on, consecutive QLinear layers that read the same activation tensor (HGT's q / k / v projections) share
+    one absmax pass and one int8 copy of it instead of quantizing it once per layer.  The reference quantizes per
+    layer (cuda/QLinear.py:28-35); with a deterministic rounding mode the results are bit-identical either way.
+    The tensor is recognised by address, shape and autograd version counter, so writes that bypass the counter
+    (`tensor.data`) are not seen; stochastic rounding never shares."""
+    _state["share_quantized_inputs"] = bool(enable)
+    if not enable:
+        from .QLinear import clear_shared_input
+        clear_shared_input()
+
+
+def sharing_quantized_inputs() -> bool:
+    return _state["share_quantized_inputs"]

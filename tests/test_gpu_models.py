@@ -318,3 +318,38 @@ def test_link_prediction_scores_and_loss(cuda):
             s, d = [t.long() for t in graph.coo]
             ref = (h[s] * h[d]).sum(-1)
             assert (score.flatten() - ref).abs().max() / ref.abs().max() < 0.05
+
+
+def test_shared_quantized_inputs_are_bit_identical_and_save_launches(cuda):
+    """HGT's q / k / v projections read the same tensor: sharing its int8 copy changes no bit and skips passes."""
+    import tango_b200 as T
+    from tango_b200 import config, kernels as K
+    from tango_b200.gnn import HGT
+    g = _setup(600, 7000, 29)
+    torch.manual_seed(2)
+    x = torch.randn(g.num_nodes(), 64, device="cuda", requires_grad=True)
+    m = HGT(64, 32, 4).cuda()
+
+    def run():
+        x.grad = None
+        m.zero_grad()
+        K.launch_counter[0] = 0
+        out = m(g, x)
+        out.square().mean().backward()
+        return out.detach().clone(), x.grad.clone(), [p.grad.clone() for p in m.parameters()], K.launch_counter[0]
+
+    out0, gx0, gp0, n0 = run()
+    config.share_quantized_inputs(True)
+    try:
+        out1, gx1, gp1, n1 = run()
+        with torch.no_grad():
+            x.add_(1.0)                       # in-place change: the cached copy must not be used for the new values
+            out2 = m(g, x).detach()
+    finally:
+        config.share_quantized_inputs(False)
+    assert torch.equal(out0, out1) and torch.equal(gx0, gx1)
+    assert all(torch.equal(a, b) for a, b in zip(gp0, gp1))
+    assert n1 < n0
+    with torch.no_grad():
+        ref2 = m(g, x).detach()
+    assert torch.equal(out2, ref2)
