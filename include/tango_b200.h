@@ -202,6 +202,19 @@ int tango_sddmm_dot(const int32_t *src, const int32_t *dst, int64_t n_edges, con
                     const int8_t *vq, int64_t ldv, int h, int d, const float *su, const float *sv, float *out,
                     float *out_absmax, tango_stream_t stream);
 
+/* The same product, walked row by row of a CSR/CSC instead of edge by edge: for every slot j of row r
+ *   out[eid(j), h] = float(sum_d Uq[indices[j],h,d] * Vq[r,h,d]) * (su[0]*sv[0])
+ * (edge_ids == NULL: slot j is edge j).  With the CSC (rows = destinations, indices = sources) this is exactly
+ * tango_sddmm_dot; V's row stays in registers and only U is gathered, so half as many bytes move, and rows longer
+ * than plan->split_threshold are cut into the plan's slices (no scratch needed; plan may be NULL).  Needs rows of
+ * both operands padded to 16 (or 4) bytes with zero pad, h*d <= 512, and for h > 1 a head width d that is a
+ * power-of-two multiple of 16 (or 4) bytes; otherwise returns TANGO_EALIGN and the caller uses tango_sddmm_dot.
+ * Replaces mySDDMM_int8 with op "dot" (cuda/src/cuda.cpp:201, cuda/src/SDDMM.cu:8-47,124-153). */
+int tango_sddmm_dot_rows(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids, int64_t n_rows,
+                         const int8_t *uq, int64_t ldu, const int8_t *vq, int64_t ldv, int h, int d, const float *su,
+                         const float *sv, float *out, float *out_absmax, const tango_spmm_plan *plan /* host */,
+                         tango_stream_t stream);
+
 /* out[e,:] = op(float(Uq[src[e],:])*su[0], float(Vq[dst[e],:])*sv[0]) over `dim` features; out is [E, dim] contiguous.
  * Replaces mySDDMM_int8 with op add/sub/mul/div (cuda/src/cuda.cpp:201, cuda/src/SDDMM.cu:49-100,154-176). */
 int tango_sddmm_elementwise(int op, const int32_t *src, const int32_t *dst, int64_t n_edges, const int8_t *uq,

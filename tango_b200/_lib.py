@@ -13,6 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("TANGO_B200_LIB") or os.path.join(_HERE, "lib", "libtango_b200.so")
 
 TANGO_OK = 0
+TANGO_EALIGN = -2
 TANGO_ETIMEOUT = -4
 ROUND_TRUNC, ROUND_NEAREST, ROUND_STOCHASTIC = 0, 1, 2
 OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3}
@@ -64,6 +65,7 @@ _SIGS = {
     "tango_spmm_u_mul_e": ([P, P, P, c_int64, P, c_int64, c_int, c_int, P, P, P, c_int64, POINTER(SpmmPlan), P], c_int),
     "tango_spmm_incidence": ([P, P, c_int64, P, c_int64, c_int64, P, P, c_int64, POINTER(SpmmPlan), P], c_int),
     "tango_sddmm_dot": ([P, P, c_int64, P, c_int64, P, c_int64, c_int, c_int, P, P, P, P, P], c_int),
+    "tango_sddmm_dot_rows": ([P, P, P, c_int64, P, c_int64, P, c_int64, c_int, c_int, P, P, P, P, P, P], c_int),
     "tango_sddmm_elementwise": ([c_int, P, P, c_int64, P, c_int64, P, c_int64, c_int64, P, P, P, P, P], c_int),
     "tango_gat_edge_softmax": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P], c_int),
     "tango_gat_edge_softmax_bwd": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P, P], c_int),

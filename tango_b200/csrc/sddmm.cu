@@ -116,6 +116,126 @@ __global__ void __launch_bounds__(256) sddmm_dot_kernel(const DotArgs a) {
     }
 }
 
+// ---- row-wise dot: out[eid(j), h] = <U[indices[j], h, :], V[row, h, :]> for every slot j of a CSR/CSC row.
+// The fixed operand's row is loaded once per row and stays in registers; only the other operand is gathered, which
+// halves the gathered bytes of the endpoint-list kernel above, and the index stream is read once, coalesced.  A warp
+// owns a row (or a slice of a long row: slices need no merging, every edge has its own output); G lanes share a
+// neighbour, 32 / G neighbours per step, four steps in flight.  A head occupies LH = D / VEC adjacent lanes (or the
+// whole group when there is one head) and is reduced with log2(LH) shuffles.
+struct DotRowArgs {
+    const int32_t *indptr, *indices, *edge_ids, *row_order;
+    const int32_t *units;   // (row, begin, end, -) slices of the rows longer than split_threshold
+    int64_t n_units, n_rows;
+    int split_threshold;    // rows longer than this are covered by units (0: none)
+    const int8_t *u, *v;    // u is gathered through indices, v is read at the row
+    int64_t ldu, ldv;
+    int H, f, f_pad, G, LH;
+    const float *su, *sv;
+    float *out;
+    float *out_absmax;
+};
+
+template <int VEC>
+__device__ __forceinline__ void dot_row_segment(const DotRowArgs &a, int64_t row, int beg, int end, float sc,
+                                                float &amax) {
+    typedef typename DotVec<VEC>::T V;
+    const int lane = threadIdx.x & 31;
+    const int G = a.G, NB = 32 / G, grp = lane / G, sub = lane % G;
+    const bool active = sub * VEC < a.f_pad;
+    const int off = active ? sub * VEC : 0;
+    V vr = V();
+    if (active) vr = __ldg(reinterpret_cast<const V *>(a.v + row * a.ldv + off));
+    const int8_t *ubase = a.u + off;
+    const uint32_t ld = (uint32_t)a.ldu;
+    const int head = (sub * VEC) / (a.LH * VEC);            // LH lanes per head
+    const bool writer = active && (sub % a.LH) == 0 && head < a.H;
+    constexpr int U = 4;
+    int j0 = beg;
+    int nxt_idx = 0, nxt_eid = 0;
+    if (j0 + 32 <= end) {
+        nxt_idx = __ldg(a.indices + j0 + lane);
+        nxt_eid = a.edge_ids ? __ldg(a.edge_ids + j0 + lane) : j0 + lane;
+    }
+    if (G >= U) {
+        for (; j0 + 32 <= end; j0 += 32) {
+            const int my_idx = nxt_idx, my_eid = nxt_eid;
+            if (j0 + 64 <= end) {
+                nxt_idx = __ldg(a.indices + j0 + 32 + lane);
+                nxt_eid = a.edge_ids ? __ldg(a.edge_ids + j0 + 32 + lane) : j0 + 32 + lane;
+            }
+            for (int s = 0, lane0 = grp; s < G; s += U, lane0 += U * NB) {
+                V ur[U];
+                int eid[U];
+#pragma unroll
+                for (int k = 0; k < U; ++k) {
+                    const int src_lane = lane0 + k * NB;
+                    const int idx = __shfl_sync(0xffffffffu, my_idx, src_lane);
+                    eid[k] = __shfl_sync(0xffffffffu, my_eid, src_lane);
+                    ur[k] = __ldg(reinterpret_cast<const V *>(ubase + (uint64_t)(uint32_t)idx * ld));
+                }
+#pragma unroll
+                for (int k = 0; k < U; ++k) {
+                    int acc = active ? dot_regs<VEC>(ur[k], vr) : 0;
+                    for (int o = a.LH >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    if (writer) {
+                        const float r = __fmul_rn((float)acc, sc);
+                        __stcs(a.out + (int64_t)eid[k] * a.H + head, r);
+                        amax = fmaxf(amax, fabsf(r));
+                    }
+                }
+            }
+        }
+    }
+    // ragged tail, and every batch when fewer than four lanes share a neighbour
+    for (; j0 < end; j0 += 32) {
+        const int j = j0 + lane;
+        int my_idx = -1, my_eid = 0;
+        if (j < end) {
+            my_idx = __ldg(a.indices + j);
+            my_eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
+        }
+        const int steps = min(G, (end - j0 + NB - 1) / NB);
+        for (int s = 0; s < steps; ++s) {
+            const int src_lane = (s * NB + grp) & 31;
+            const int idx = __shfl_sync(0xffffffffu, my_idx, src_lane);
+            const int eid = __shfl_sync(0xffffffffu, my_eid, src_lane);
+            int acc = 0;
+            if (idx >= 0 && active)
+                acc = dot_regs<VEC>(__ldg(reinterpret_cast<const V *>(ubase + (uint64_t)(uint32_t)idx * ld)), vr);
+            for (int o = a.LH >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (writer && idx >= 0) {
+                const float r = __fmul_rn((float)acc, sc);
+                __stcs(a.out + (int64_t)eid * a.H + head, r);
+                amax = fmaxf(amax, fabsf(r));
+            }
+        }
+    }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(128, 8) sddmm_dot_rows_kernel(const DotRowArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const float sc = __fmul_rn(__ldg(a.su), __ldg(a.sv));
+    float amax = 0.f;
+    if (w < a.n_units) {
+        const int4 u = __ldg(reinterpret_cast<const int4 *>(a.units) + w);
+        dot_row_segment<VEC>(a, u.x, u.y, u.z, sc, amax);
+    } else if (w - a.n_units < a.n_rows) {
+        int64_t row = w - a.n_units;
+        if (a.row_order) row = __ldg(a.row_order + row);
+        const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
+        if (!(a.n_units > 0 && end - beg > a.split_threshold)) dot_row_segment<VEC>(a, row, beg, end, sc, amax);
+    }
+    if (a.out_absmax) {
+        amax = warp_max(amax);
+        if (lane == 0 && amax > 0.f) {
+            const float s = __fdiv_rn(amax, 127.0f);
+            if (s > __ldcg(a.out_absmax)) atomic_max_nonneg(a.out_absmax, s);
+        }
+    }
+}
+
 struct ElemArgs {
     const int32_t *src, *dst;
     int64_t n_edges;
@@ -220,6 +340,47 @@ extern "C" int tango_sddmm_dot(const int32_t *src, const int32_t *dst, int64_t n
     if (vec == 16) sddmm_dot_kernel<16><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else if (vec == 4) sddmm_dot_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else sddmm_dot_kernel<1><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
+}
+
+extern "C" int tango_sddmm_dot_rows(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                                    int64_t n_rows, const int8_t *uq, int64_t ldu, const int8_t *vq, int64_t ldv,
+                                    int h, int d, const float *su, const float *sv, float *out, float *out_absmax,
+                                    const tango_spmm_plan *plan, tango_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int64_t f = (int64_t)h * d;
+    if (n_rows < 0 || h < 1 || d < 1 || ldu < f || ldv < f || ldu > 0x7fffffff) return TANGO_EINVAL;
+    if (n_rows == 0) return TANGO_OK;
+    if (!indptr || !indices || !uq || !vq || !su || !sv || !out) return TANGO_EINVAL;
+    // one 16-byte (or 4-byte) piece per lane; a head must cover a power-of-two number of whole pieces
+    int vec = 0;
+    auto fits = [&](int v) {
+        if (ldu % v || ldv % v || !aligned(uq, v) || !aligned(vq, v)) return false;
+        if (round_up(f, v) > ldu || round_up(f, v) > ldv || round_up(f, v) > 32 * v) return false;
+        if (h == 1) return true;
+        const int lh = d / v;
+        return d % v == 0 && (lh & (lh - 1)) == 0;
+    };
+    if (fits(16)) vec = 16; else if (fits(4)) vec = 4;
+    if (vec == 0) return TANGO_EALIGN;   // the caller falls back to the endpoint-list kernel
+    DotRowArgs a{};
+    a.indptr = indptr; a.indices = indices; a.edge_ids = edge_ids; a.n_rows = n_rows;
+    a.u = uq; a.v = vq; a.ldu = ldu; a.ldv = ldv; a.H = h; a.f = (int)f; a.f_pad = (int)round_up(f, vec);
+    a.G = pow2_ceil(a.f_pad / vec);
+    a.LH = (h == 1) ? a.G : d / vec;
+    a.su = su; a.sv = sv; a.out = out; a.out_absmax = out_absmax;
+    if (plan) {
+        a.row_order = plan->row_order;
+        if (plan->n_units > 0) {
+            if (!plan->units || !aligned(plan->units, 16)) return TANGO_EINVAL;
+            a.units = plan->units; a.n_units = plan->n_units; a.split_threshold = plan->split_threshold;
+        }
+    }
+    const int64_t blocks = ceil_div(a.n_units + a.n_rows, 4);
+    if (blocks > 0x7fffffff) return TANGO_ESIZE;
+    if (vec == 16) sddmm_dot_rows_kernel<16><<<(unsigned)blocks, 128, 0, stream>>>(a);
+    else sddmm_dot_rows_kernel<4><<<(unsigned)blocks, 128, 0, stream>>>(a);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
 }

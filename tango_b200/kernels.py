@@ -284,6 +284,29 @@ def _incidence_spmm(out, indptr, edge_ids, E, scale, sched=None):
     del keep
 
 
+def _sddmm_dot_rows(out, scaleOut, indptr, indices, edge_ids, U, V, scaleU, scaleV, sched=None) -> bool:
+    """Row-wise dot SDDMM over a CSR/CSC bundle; False when the operand layout needs the endpoint-list kernel."""
+    h, d = U.shape[-2], U.shape[-1]
+    U2, _, _, ldu = _matrix(U)
+    V2, _, _, ldv = _matrix(V)
+    n_rows = indptr.numel() - 1
+    plan, keep = (None, ())
+    if sched is not None:
+        order = sched.row_order
+        plan_obj = SpmmPlan(sched.units.data_ptr() if sched.n_units else None, sched.n_units, None, 0, None, 0,
+                            sched.threshold, order.data_ptr() if order.numel() else None, -1)
+        plan, keep = ctypes.byref(plan_obj), (plan_obj,)
+    with torch.cuda.device(U.device):
+        rc = lib.tango_sddmm_dot_rows(_p(indptr), _pi(indices), _p(edge_ids), n_rows, _p(U2), ldu, _p(V2), ldv, h, d,
+                                      _p(scaleU), _p(scaleV), _p(out), _p(scaleOut), plan, _stream())
+    del keep
+    if rc == _lib.TANGO_EALIGN:
+        return False
+    check(rc, "mySDDMM_int8(dot, rows)")
+    launch_counter[0] += 1
+    return True
+
+
 def _sddmm(op: str, out, scaleOut, src, dst, U, V, scaleU, scaleV):
     n_edges = src.numel()
     launch_counter[0] += 1
@@ -406,7 +429,14 @@ def mySDDMM_int8(g, op, U, V, scaleU, scaleV, isReduce, reverse=False):
     out_shape = (src.size(0),) + infer_broadcast_shape(op, U.shape[1:], V.shape[1:])
     out = torch.empty(out_shape, dtype=torch.float32, device=src.device)
     scale = torch.zeros((1,), dtype=torch.float32, device=src.device) if isReduce else torch.Tensor()
-    cuda_kernels.mySDDMM_int8(op, out, scale, src, dst, U, V, scaleU, scaleV)
+    done = False
+    if (op == "dot" and src.numel() > 0 and U.shape[1:] == V.shape[1:] and U.dim() == 3
+            and U.shape[0] == g.num_nodes() == V.shape[0]):
+        # walk the rows of the fixed endpoint: V's row stays in registers, only U is gathered
+        indptr, indices, edge_ids = _bundle(g, reverse)
+        done = _sddmm_dot_rows(out, scale, indptr, indices, edge_ids, U, V, scaleU, scaleV, _schedule(g, reverse))
+    if not done:
+        cuda_kernels.mySDDMM_int8(op, out, scale, src, dst, U, V, scaleU, scaleV)
     if UV_unsqueezed:
         out = out.squeeze(1)
     return out, scale

@@ -269,6 +269,47 @@ def test_sddmm_dot(cuda, h, d):
     np.testing.assert_array_equal(out_r.cpu().numpy()[..., 0], O.sddmm_dot(dst, src, uq, vq, su, sv))
 
 
+@pytest.mark.parametrize("h,d,order", [(4, 64, "dst"), (1, 41, "append"), (4, 16, "append"), (8, 4, "dst")])
+def test_sddmm_dot_rows_matches_endpoint_kernel(cuda, h, d, order):
+    """The row-wise dot kernel (fixed operand in registers, long rows cut into slices) against the endpoint-list
+    kernel and the oracle, on a graph with a 30 000-edge hub row and on an arbitrarily numbered R-MAT graph."""
+    import tango_b200 as T
+    from tango_b200 import kernels as K
+    from tango_b200.graph import Graph, rmat_graph
+    if order == "dst":
+        n = 3000
+        src = torch.cat([torch.arange(n).repeat(10), torch.arange(n)])
+        dst = torch.cat([torch.zeros(10 * n, dtype=torch.long), (torch.arange(n) * 7 + 1) % n])
+        perm = torch.argsort(dst * n + src, stable=True)
+        g = Graph(src[perm], dst[perm], n).to("cuda")
+    else:
+        n = 500
+        g = rmat_graph(n, 9000, 41, device="cuda", edge_order="append")
+    T.graph_preprocess(g)
+    (_, _, src_np, dst_np) = _np_graph(g)
+    rng = np.random.default_rng(h * 100 + d)
+    uq = rng.integers(-127, 128, (n, h, d), dtype=np.int8)
+    vq = rng.integers(-127, 128, (n, h, d), dtype=np.int8)
+    u_t = K.alloc_int8(uq.shape, "cuda"); u_t.zero_(); u_t.copy_(_dev(uq))
+    v_t = K.alloc_int8(vq.shape, "cuda"); v_t.zero_(); v_t.copy_(_dev(vq))
+    for t in (u_t, v_t):
+        if t.stride(0) != h * d:
+            torch.as_strided(t, (n, t.stride(0) - h * d), (t.stride(0), 1), h * d).zero_()
+    su, sv = _scale_t(np.float32(0.02)), _scale_t(np.float32(0.005))
+    for reverse in (False, True):
+        K.launch_counter[0] = 0
+        out, sc = K.mySDDMM_int8(g, "dot", u_t, v_t, su, sv, True, reverse=reverse)
+        s_np, d_np = (dst_np, src_np) if reverse else (src_np, dst_np)
+        ref = O.sddmm_dot(s_np, d_np, uq, vq, np.float32(0.02), np.float32(0.005))
+        np.testing.assert_array_equal(out.cpu().numpy()[..., 0], ref)
+        assert sc.item() == O.absmax_scale(ref)
+        # the endpoint-list entry point on the same operands
+        out2 = torch.empty_like(out)
+        s_t, d_t = g.coo[::-1] if reverse else g.coo
+        K.cuda_kernels.mySDDMM_int8("dot", out2, torch.Tensor(), s_t, d_t, u_t, v_t, su, sv)
+        assert torch.equal(out, out2)
+
+
 def test_sddmm_recipe_fixture(cuda):
     """The 3-node / 4-edge input recipe the reference keeps under #ifdef TEST (cuda/src/SDDMM.cu:230-257)."""
     from tango_b200 import kernels as K
