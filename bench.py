@@ -354,6 +354,12 @@ def run_ours(args):
                 "peak_source": peak_kind, "kernel_ms": k_ms, "algorithmic_bytes": alg,
                 "gathered_bytes_per_s_GB": touched / (k_ms * 1e-3) / 1e9,
                 "note": "the E*F gathered bytes are served by L2; HBM sees each feature row about once"}
+        # the matching ceiling, measured now: random 256-byte rows of the same L2-resident table gathered into
+        # registers by a probe kernel that does nothing else
+        gp = _row_gather_peak(q, hidden)
+        if gp:
+            roof["l2_row_gather_peak_GB_s"] = gp
+            roof["frac_of_l2_row_gather_peak"] = roof["gathered_bytes_per_s_GB"] / gp
 
     cpu_base = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline and not name.startswith("gat"):
@@ -536,6 +542,30 @@ def run_primitives(args):
     report("sddmm add H=1 D=16", timeit(lambda: K.mySDDMM_int8(g, "add", q16, q16, s16, s16, False)),
            2 * nn_ * 16 + 8 * e + 4 * e * 16)
     print(json.dumps({"suite": "primitives", "status_word": K.device_status(), "n": len(out_lines)}), flush=True)
+
+
+def _row_gather_peak(q, width):
+    """GB/s at which tango_probe_row_gather reads random rows of the int8 table `q` (rows of `width` bytes)."""
+    import torch
+    from tango_b200._lib import lib
+    row_bytes = q.stride(0)
+    if row_bytes != width or row_bytes & (row_bytes - 1) or not 16 <= row_bytes <= 512:
+        return None
+    sink = torch.zeros(1, dtype=torch.int32, device=q.device)
+    st = torch.cuda.current_stream().cuda_stream
+    best = None
+    for ctas, threads in ((8, 256), (16, 128), (8, 128), (4, 256)):      # best of a few launch shapes
+        lib.tango_probe_row_gather(q.data_ptr(), q.shape[0], row_bytes, 50, ctas, threads, sink.data_ptr(), st)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        nbytes = lib.tango_probe_row_gather(q.data_ptr(), q.shape[0], row_bytes, 1000, ctas, threads, sink.data_ptr(), st)
+        e1.record()
+        torch.cuda.synchronize()
+        if nbytes > 0:
+            rate = nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9
+            best = rate if best is None else max(best, rate)
+    return best
 
 
 def main():

@@ -260,6 +260,17 @@ int tango_edge_softmax_bwd(const int32_t *indptr, const int32_t *edge_ids, const
                            int64_t n_block_rows, int64_t n_rows, int h, float zmul, const float *a, const float *da,
                            float *dz, tango_stream_t stream);
 
+/* ---------------------------------------------------------------- measurement aid */
+
+/* No counterpart in the reference.  Gathers pseudo-random rows (row_bytes a power of two in [16, 512]) of `table`
+ * [rows, row_bytes] into registers with 128-bit loads, eight in flight per lane, 148 x ctas_per_sm CTAs of `threads`
+ * threads (a multiple of 32, at most 256), and returns the number of bytes the launch gathers (or a negative
+ * TANGO_E* code).  Timing the launch with a table
+ * that fits in L2 gives the random-row gather ceiling that the aggregation kernels are compared with; `sink` is a
+ * 4-byte device word that is never actually written. */
+int64_t tango_probe_row_gather(const void *table, int64_t rows, int64_t row_bytes, int iters, int ctas_per_sm,
+                               int threads, uint32_t *sink, tango_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -419,3 +419,15 @@ def test_csc_numbered_graph_skips_edge_id_indirection(cuda):
         np.testing.assert_array_equal(out, O.spmm_u_mul_e(indptr, indices, eids, nq, eq, s))
     np.testing.assert_array_equal(K.incidence_SPMM(g, _dev(eq), _scale_t(s)).cpu().numpy(),
                                   O.spmm_incidence(csc[0], csc[2], eq, s))
+
+
+def test_row_gather_probe_runs_and_validates(cuda):
+    from tango_b200._lib import lib
+    table = torch.ones((1000, 256), dtype=torch.int8, device="cuda")
+    sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    nbytes = lib.tango_probe_row_gather(table.data_ptr(), 1000, 256, 3, 8, 256, sink.data_ptr(), st)
+    torch.cuda.synchronize()
+    assert nbytes == 148 * 8 * 256 * 3 * 8 * 16 and int(sink) == 0
+    assert lib.tango_probe_row_gather(table.data_ptr(), 1000, 48, 3, 8, 256, sink.data_ptr(), st) == -2     # not a power of two
+    assert lib.tango_probe_row_gather(None, 1000, 256, 3, 8, 256, sink.data_ptr(), st) == -1
