@@ -229,11 +229,13 @@ int tango_sddmm_elementwise(int op, const int32_t *src, const int32_t *dst, int6
  * i.e. the reference's sddmm_u_add_v -> LeakyReLU -> dgl edge_softmax chain (evaluation/test_gat.py:141-146,
  * cuda/SDDMM.py:10-20) in one pass; `a` is fp32 [E, H] in edge-id order; elq / erq are contiguous int8 [N, H], H <= 8.
  * Optional schedule: with row_order (rows by decreasing degree) the first n_block_rows rows get a whole CTA each, the
- * others a warp; row_order == NULL means one warp per row in natural order. */
+ * others a warp; row_order == NULL means one warp per row in natural order.  The optional *_absmax word of the four
+ * edge-softmax entry points (must hold 0) receives max|output|/127, i.e. the scale the quantizer of the next operator
+ * would otherwise compute with a pass of its own (get_scale, cuda/src/quantization.cu:79-93). */
 int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
                            const int32_t *row_order, int64_t n_block_rows, int64_t n_rows, const int8_t *elq,
                            const int8_t *erq, int h, const float *sl, const float *sr, float slope, float *a,
-                           tango_stream_t stream);
+                           float *a_absmax, tango_stream_t stream);
 
 /* Gradient of the pass above with respect to the edge logits: for every destination row and head
  *   dz[eid(j),h] = a_j * (da_j - sum_k a_k da_k) * (z_j > 0 ? 1 : slope)
@@ -243,7 +245,7 @@ int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indices, const 
 int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
                                const int32_t *row_order, int64_t n_block_rows, int64_t n_rows, const int8_t *elq,
                                const int8_t *erq, int h, const float *sl, const float *sr, float slope, const float *a,
-                               const float *da, float *dz, tango_stream_t stream);
+                               const float *da, float *dz, float *dz_absmax, tango_stream_t stream);
 
 /* Edge softmax of plain fp32 scores: for every destination row v (CSC order) and head h
  *   a[eid(j),h] = softmax_j( z[eid(j),h] * zmul )     over the incoming edges j of v,
@@ -252,13 +254,13 @@ int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *indices, co
  * dgl.ops.edge_softmax(g, t, norm_by='dst') (evaluation/test_HGT.py:59-60, evaluation/test_gat.py:146). */
 int tango_edge_softmax(const int32_t *indptr, const int32_t *edge_ids, const int32_t *row_order,
                        int64_t n_block_rows, int64_t n_rows, const float *z, int h, float zmul, float *a,
-                       tango_stream_t stream);
+                       float *a_absmax, tango_stream_t stream);
 
 /* Gradient of tango_edge_softmax with respect to z: dz[eid(j),h] = a_j * (da_j - sum_k a_k da_k) * zmul.
  * Replaces the autograd backward of dgl.ops.edge_softmax. */
 int tango_edge_softmax_bwd(const int32_t *indptr, const int32_t *edge_ids, const int32_t *row_order,
                            int64_t n_block_rows, int64_t n_rows, int h, float zmul, const float *a, const float *da,
-                           float *dz, tango_stream_t stream);
+                           float *dz, float *dz_absmax, tango_stream_t stream);
 
 /* ---------------------------------------------------------------- measurement aid */
 

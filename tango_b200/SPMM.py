@@ -51,9 +51,9 @@ class spmm_u_mul_e(Function):
     compat_dn_scale = False
 
     @staticmethod
-    def forward(ctx, g, N, E):
+    def forward(ctx, g, N, E, scaleE_=None):
         sN = cuda_kernels.get_scale(N)
-        sE = cuda_kernels.get_scale(E)
+        sE = cuda_kernels.get_scale(E) if scaleE_ is None else scaleE_     # producer already knows max|E|/127
         Eq, _ = _q(E.reshape(E.shape[0], -1), sE, 1)          # [E, H] int8, edge-id order (no transposed copy)
         Nq, _ = _q(N, sN)
         scale = sN * sE
@@ -74,4 +74,4 @@ class spmm_u_mul_e(Function):
             op = "dot" if reduce_last else "mul"
             dE, _ = mySDDMM_int8(g, op, Nq, dZq, sN, sdZ, False)
             dE = dE.reshape(eshape)
-        return None, dN, dE
+        return None, dN, dE, None

@@ -67,11 +67,11 @@ _SIGS = {
     "tango_sddmm_dot": ([P, P, c_int64, P, c_int64, P, c_int64, c_int, c_int, P, P, P, P, P], c_int),
     "tango_sddmm_dot_rows": ([P, P, P, c_int64, P, c_int64, P, c_int64, c_int, c_int, P, P, P, P, P, P], c_int),
     "tango_sddmm_elementwise": ([c_int, P, P, c_int64, P, c_int64, P, c_int64, c_int64, P, P, P, P, P], c_int),
-    "tango_gat_edge_softmax": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P], c_int),
-    "tango_gat_edge_softmax_bwd": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P, P], c_int),
+    "tango_gat_edge_softmax": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P], c_int),
+    "tango_gat_edge_softmax_bwd": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P, P, P], c_int),
     "tango_probe_row_gather": ([P, c_int64, c_int64, c_int, c_int, c_int, P, P], c_int64),
-    "tango_edge_softmax": ([P, P, P, c_int64, c_int64, P, c_int, c_float, P, P], c_int),
-    "tango_edge_softmax_bwd": ([P, P, P, c_int64, c_int64, c_int, c_float, P, P, P, P], c_int),
+    "tango_edge_softmax": ([P, P, P, c_int64, c_int64, P, c_int, c_float, P, P, P], c_int),
+    "tango_edge_softmax_bwd": ([P, P, P, c_int64, c_int64, c_int, c_float, P, P, P, P, P], c_int),
 }
 for _name, (_args, _res) in _SIGS.items():
     if not hasattr(lib, _name):

@@ -30,6 +30,7 @@ struct GatArgs {
     float *dz;           // backward
     const float *zin;    // plain-score flavour: fp32 scores [E, H] in edge-id order (elq / erq / sl / sr unused)
     float zmul;          // factor applied to zin before the softmax
+    float *out_absmax;   // optional: receives max|output| / 127 (forward: of a, backward: of dz); must hold 0
 };
 
 __device__ __forceinline__ float leaky(float z, float slope) { return z >= 0.f ? z : __fmul_rn(z, slope); }
@@ -45,7 +46,10 @@ __device__ __forceinline__ void edge_logits(const GatArgs &a, int j, const float
             z[0] = __fmul_rn(v.x, a.zmul); z[1] = __fmul_rn(v.y, a.zmul);
             z[2] = __fmul_rn(v.z, a.zmul); z[3] = __fmul_rn(v.w, a.zmul);
         } else {
-            for (int h = 0; h < a.H; ++h) z[h] = __fmul_rn(__ldg(a.zin + eid * a.H + h), a.zmul);
+            const int H = HT ? HT : a.H;
+#pragma unroll
+            for (int h = 0; h < kMaxHeads; ++h)
+                if (h < H) z[h] = __fmul_rn(__ldg(a.zin + eid * H + h), a.zmul);
         }
         return;
     }
@@ -56,8 +60,10 @@ __device__ __forceinline__ void edge_logits(const GatArgs &a, int j, const float
         for (int h = 0; h < 4; ++h)
             z[h] = leaky(__fadd_rn(__fmul_rn((float)(int8_t)(w >> (8 * h)), sl), er[h]), a.slope);
     } else {
-        for (int h = 0; h < a.H; ++h)
-            z[h] = leaky(__fadd_rn(__fmul_rn((float)__ldg(a.elq + s * a.H + h), sl), er[h]), a.slope);
+        const int H = HT ? HT : a.H;
+#pragma unroll
+        for (int h = 0; h < kMaxHeads; ++h)
+            if (h < H) z[h] = leaky(__fadd_rn(__fmul_rn((float)__ldg(a.elq + s * H + h), sl), er[h]), a.slope);
     }
 }
 
@@ -102,7 +108,7 @@ __device__ __forceinline__ void team_softmax_merge(float &m, float &s, float *sm
 }
 
 template <int NT, int HT>
-__device__ __forceinline__ void softmax_row(const GatArgs &a, int64_t row, int tid, float *smem) {
+__device__ __forceinline__ void softmax_row(const GatArgs &a, int64_t row, int tid, float *smem, float &amax) {
     const float sl = a.zin ? 0.f : __ldg(a.sl), sr = a.zin ? 0.f : __ldg(a.sr);
     const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
     const int H = HT ? HT : a.H;
@@ -134,17 +140,25 @@ __device__ __forceinline__ void softmax_row(const GatArgs &a, int64_t row, int t
         edge_logits<HT>(a, j, er, sl, z);
         const int64_t eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
         if (HT == 4) {
-            *reinterpret_cast<float4 *>(a.att + eid * 4) =
-                make_float4(__expf(z[0] - m[0]) * inv[0], __expf(z[1] - m[1]) * inv[1], __expf(z[2] - m[2]) * inv[2],
-                            __expf(z[3] - m[3]) * inv[3]);
+            const float4 o = make_float4(__expf(z[0] - m[0]) * inv[0], __expf(z[1] - m[1]) * inv[1],
+                                         __expf(z[2] - m[2]) * inv[2], __expf(z[3] - m[3]) * inv[3]);
+            *reinterpret_cast<float4 *>(a.att + eid * 4) = o;
+            amax = fmaxf(fmaxf(amax, fmaxf(o.x, o.y)), fmaxf(o.z, o.w));
         } else {
-            for (int h = 0; h < H; ++h) a.att[eid * H + h] = __expf(z[h] - m[h]) * inv[h];
+#pragma unroll
+            for (int h = 0; h < kMaxHeads; ++h) {
+                if (h < H) {
+                    const float o = __expf(z[h] - m[h]) * inv[h];
+                    a.att[eid * H + h] = o;
+                    amax = fmaxf(amax, o);
+                }
+            }
         }
     }
 }
 
 template <int NT, int HT>
-__device__ __forceinline__ void softmax_bwd_row(const GatArgs &a, int64_t row, int tid, float *smem) {
+__device__ __forceinline__ void softmax_bwd_row(const GatArgs &a, int64_t row, int tid, float *smem, float &amax) {
     const bool plain = a.zin != nullptr;   // backward of the plain flavour: zin is only a marker, never read
     const float sl = plain ? 0.f : __ldg(a.sl), sr = plain ? 0.f : __ldg(a.sr);
     const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
@@ -162,7 +176,9 @@ __device__ __forceinline__ void softmax_bwd_row(const GatArgs &a, int64_t row, i
             const float4 g = __ldg(reinterpret_cast<const float4 *>(a.datt + eid * 4));
             dot[0] += p.x * g.x; dot[1] += p.y * g.y; dot[2] += p.z * g.z; dot[3] += p.w * g.w;
         } else {
-            for (int h = 0; h < H; ++h) dot[h] += __ldg(a.att + eid * H + h) * __ldg(a.datt + eid * H + h);
+#pragma unroll
+            for (int h = 0; h < kMaxHeads; ++h)
+                if (h < H) dot[h] += __ldg(a.att + eid * H + h) * __ldg(a.datt + eid * H + h);
         }
     }
 #pragma unroll
@@ -186,12 +202,17 @@ __device__ __forceinline__ void softmax_bwd_row(const GatArgs &a, int64_t row, i
                 if (!(z[3] > 0.f)) o.w *= a.slope;
             }
             *reinterpret_cast<float4 *>(a.dz + eid * 4) = o;
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(o.x), fabsf(o.y))), fmaxf(fabsf(o.z), fabsf(o.w)));
         } else {
-            for (int h = 0; h < H; ++h) {
-                float o = __ldg(a.att + eid * H + h) * (__ldg(a.datt + eid * H + h) - dot[h]);
-                if (plain) o *= a.zmul;
-                else if (!(z[h] > 0.f)) o *= a.slope;
-                a.dz[eid * H + h] = o;
+#pragma unroll
+            for (int h = 0; h < kMaxHeads; ++h) {
+                if (h < H) {
+                    float o = __ldg(a.att + eid * H + h) * (__ldg(a.datt + eid * H + h) - dot[h]);
+                    if (plain) o *= a.zmul;
+                    else if (!(z[h] > 0.f)) o *= a.slope;
+                    a.dz[eid * H + h] = o;
+                    amax = fmaxf(amax, fabsf(o));
+                }
             }
         }
     }
@@ -201,16 +222,25 @@ __device__ __forceinline__ void softmax_bwd_row(const GatArgs &a, int64_t row, i
 template <int HT, bool BWD>
 __global__ void __launch_bounds__(256) gat_softmax_kernel(const GatArgs a) {
     __shared__ float smem[64];
+    float amax = 0.f;
     if ((int64_t)blockIdx.x < a.n_block_rows) {
         const int64_t row = a.row_order ? (int64_t)__ldg(a.row_order + blockIdx.x) : (int64_t)blockIdx.x;
-        if (BWD) softmax_bwd_row<256, HT>(a, row, threadIdx.x, smem);
-        else softmax_row<256, HT>(a, row, threadIdx.x, smem);
+        if (BWD) softmax_bwd_row<256, HT>(a, row, threadIdx.x, smem, amax);
+        else softmax_row<256, HT>(a, row, threadIdx.x, smem, amax);
     } else {
         const int64_t i = a.n_block_rows + ((int64_t)blockIdx.x - a.n_block_rows) * 8 + (threadIdx.x >> 5);
-        if (i >= a.n_rows) return;
-        const int64_t row = a.row_order ? (int64_t)__ldg(a.row_order + i) : i;
-        if (BWD) softmax_bwd_row<32, HT>(a, row, threadIdx.x & 31, smem);
-        else softmax_row<32, HT>(a, row, threadIdx.x & 31, smem);
+        if (i < a.n_rows) {
+            const int64_t row = a.row_order ? (int64_t)__ldg(a.row_order + i) : i;
+            if (BWD) softmax_bwd_row<32, HT>(a, row, threadIdx.x & 31, smem, amax);
+            else softmax_row<32, HT>(a, row, threadIdx.x & 31, smem, amax);
+        }
+    }
+    if (a.out_absmax) {
+        amax = warp_max(amax);
+        if ((threadIdx.x & 31) == 0 && amax > 0.f) {
+            const float s = __fdiv_rn(amax, 127.0f);
+            if (s > __ldcg(a.out_absmax)) atomic_max_nonneg(a.out_absmax, s);
+        }
     }
 }
 
@@ -225,6 +255,8 @@ static int launch_gat(GatArgs &a, cudaStream_t stream) {
     const bool h4 = a.H == 4 && aligned(a.att, 16) && (a.zin ? aligned(a.zin, 16) : aligned(a.elq, 4)) &&
                     (!BWD || (aligned(a.datt, 16) && aligned(a.dz, 16)));
     if (h4) gat_softmax_kernel<4, BWD><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else if (a.H == 1) gat_softmax_kernel<1, BWD><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else if (a.H == 2) gat_softmax_kernel<2, BWD><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else gat_softmax_kernel<0, BWD><<<(unsigned)blocks, 256, 0, stream>>>(a);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
@@ -237,10 +269,10 @@ using namespace tango;
 extern "C" int tango_gat_edge_softmax(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
                                       const int32_t *row_order, int64_t n_block_rows, int64_t n_rows,
                                       const int8_t *elq, const int8_t *erq, int h, const float *sl, const float *sr,
-                                      float slope, float *a, tango_stream_t stream) {
+                                      float slope, float *a, float *a_absmax, tango_stream_t stream) {
     if (n_rows > 0 && (!indptr || !indices || !elq || !erq || !sl || !sr || !a)) return TANGO_EINVAL;
     GatArgs g{indptr, indices, edge_ids, row_order, n_rows, n_block_rows, elq, erq, h, sl, sr, slope, a, nullptr, nullptr,
-              nullptr, 1.f};
+              nullptr, 1.f, a_absmax};
     return launch_gat<false>(g, (cudaStream_t)stream);
 }
 
@@ -248,27 +280,27 @@ extern "C" int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *
                                           const int32_t *row_order, int64_t n_block_rows, int64_t n_rows,
                                           const int8_t *elq, const int8_t *erq, int h, const float *sl,
                                           const float *sr, float slope, const float *a, const float *da, float *dz,
-                                          tango_stream_t stream) {
+                                          float *dz_absmax, tango_stream_t stream) {
     if (n_rows > 0 && (!indptr || !indices || !elq || !erq || !sl || !sr || !a || !da || !dz)) return TANGO_EINVAL;
     GatArgs g{indptr, indices, edge_ids, row_order, n_rows, n_block_rows, elq, erq, h, sl, sr, slope,
-              const_cast<float *>(a), da, dz, nullptr, 1.f};
+              const_cast<float *>(a), da, dz, nullptr, 1.f, dz_absmax};
     return launch_gat<true>(g, (cudaStream_t)stream);
 }
 
 extern "C" int tango_edge_softmax(const int32_t *indptr, const int32_t *edge_ids, const int32_t *row_order,
                                   int64_t n_block_rows, int64_t n_rows, const float *z, int h, float zmul, float *a,
-                                  tango_stream_t stream) {
+                                  float *a_absmax, tango_stream_t stream) {
     if (n_rows > 0 && (!indptr || !z || !a)) return TANGO_EINVAL;
     GatArgs g{indptr, nullptr, edge_ids, row_order, n_rows, n_block_rows, nullptr, nullptr, h, nullptr, nullptr, 1.f,
-              a, nullptr, nullptr, z, zmul};
+              a, nullptr, nullptr, z, zmul, a_absmax};
     return launch_gat<false>(g, (cudaStream_t)stream);
 }
 
 extern "C" int tango_edge_softmax_bwd(const int32_t *indptr, const int32_t *edge_ids, const int32_t *row_order,
                                       int64_t n_block_rows, int64_t n_rows, int h, float zmul, const float *a,
-                                      const float *da, float *dz, tango_stream_t stream) {
+                                      const float *da, float *dz, float *dz_absmax, tango_stream_t stream) {
     if (n_rows > 0 && (!indptr || !a || !da || !dz)) return TANGO_EINVAL;
     GatArgs g{indptr, nullptr, edge_ids, row_order, n_rows, n_block_rows, nullptr, nullptr, h, nullptr, nullptr, 1.f,
-              const_cast<float *>(a), da, dz, a, zmul};
+              const_cast<float *>(a), da, dz, a, zmul, dz_absmax};
     return launch_gat<true>(g, (cudaStream_t)stream);
 }

@@ -393,6 +393,83 @@ __global__ void __launch_bounds__(128) spmm_short_kernel(const SpmmArgs a) {
     }
 }
 
+// ---- incidence sums over contiguous edge rows: when slot j of a row IS edge j (edge ids follow the row order) and
+// the edge features are packed [E, F] with F dividing 16, the edges of a row are one contiguous byte range.  It is
+// streamed with aligned 128-bit loads, four in flight per lane; byte b of an aligned chunk belongs to column b % F.
+template <int F>
+__device__ __forceinline__ void add_chunk(int (&acc)[F], const uint4 &w) {
+    if (F == 1) {
+        acc[0] = __dp4a((int)w.x, 0x01010101, acc[0]); acc[0] = __dp4a((int)w.y, 0x01010101, acc[0]);
+        acc[0] = __dp4a((int)w.z, 0x01010101, acc[0]); acc[0] = __dp4a((int)w.w, 0x01010101, acc[0]);
+    } else if (F == 4) {
+        const uint32_t t0 = __byte_perm(w.x, w.y, 0x5140), t1 = __byte_perm(w.z, w.w, 0x5140);
+        const uint32_t t2 = __byte_perm(w.x, w.y, 0x7362), t3 = __byte_perm(w.z, w.w, 0x7362);
+        acc[0 % F] = __dp4a((int)__byte_perm(t0, t1, 0x5410), 0x01010101, acc[0 % F]);
+        acc[1 % F] = __dp4a((int)__byte_perm(t0, t1, 0x7632), 0x01010101, acc[1 % F]);
+        acc[2 % F] = __dp4a((int)__byte_perm(t2, t3, 0x5410), 0x01010101, acc[2 % F]);
+        acc[3 % F] = __dp4a((int)__byte_perm(t2, t3, 0x7632), 0x01010101, acc[3 % F]);
+    } else {
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i % F] += (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
+    }
+}
+
+template <int F>
+__device__ __forceinline__ void contig_segment(int (&acc)[F], int beg, int end, const SpmmArgs &a) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int c = 0; c < F; ++c) acc[c] = 0;
+    const int64_t b0 = (int64_t)beg * F, b1 = (int64_t)end * F;
+    const int64_t a0 = min(b1, (b0 + 15) & ~(int64_t)15), a1 = max(a0, b1 & ~(int64_t)15);
+    // ragged head [b0, a0) and tail [a1, b1): fewer than 16 bytes each; both start on a multiple of F
+    const int nh = (int)(a0 - b0), nt = (int)(b1 - a1);
+    if (lane < nh || lane < nt) {
+        const int vh = lane < nh ? (int)__ldg(a.feat + b0 + lane) : 0;
+        const int vt = lane < nt ? (int)__ldg(a.feat + a1 + lane) : 0;
+#pragma unroll
+        for (int c = 0; c < F; ++c)
+            if (lane % F == c) acc[c] += vh + vt;
+    }
+    const uint4 *chunks = reinterpret_cast<const uint4 *>(a.feat);
+    const int64_t c1 = a1 >> 4;
+    for (int64_t c = (a0 >> 4) + lane; c < c1; c += 128) {
+        uint4 w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) w[u] = (c + 32 * u < c1) ? __ldcs(chunks + c + 32 * u) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) add_chunk<F>(acc, w[u]);
+    }
+#pragma unroll
+    for (int c = 0; c < F; ++c)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+}
+
+template <int F>
+__global__ void __launch_bounds__(128) incidence_contig_kernel(const SpmmArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int acc[F];
+    if (w < a.n_units) {
+        const int4 u = __ldg(reinterpret_cast<const int4 *>(a.units) + w);
+        contig_segment<F>(acc, u.y, u.z, a);
+#pragma unroll
+        for (int c = 0; c < F; ++c)
+            if (lane == c && acc[c] != 0) atomicAdd(a.ws + (int64_t)u.w * a.ws_ld + c, acc[c]);
+    } else if (w - a.n_units < a.n_rows) {
+        int64_t row = w - a.n_units;
+        if (a.row_order) row = __ldg(a.row_order + row);
+        const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
+        if (a.n_heavy > 0 && end - beg > a.split_threshold) return;   // finished by spmm_finalize_kernel
+        contig_segment<F>(acc, beg, end, a);
+        const float sc = __ldg(a.scales);
+#pragma unroll
+        for (int c = 0; c < F; ++c)
+            if (lane == c) a.out[row * a.ldo + c] = __fadd_rn(0.f, __fmul_rn((float)acc[c], sc));
+    }
+}
+
 // Finishes the rows that were cut into units: one thread per (heavy row, feature byte).
 __global__ void __launch_bounds__(256) spmm_finalize_kernel(const SpmmArgs a) {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -500,6 +577,40 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
     return TANGO_OK;
 }
 
+// Contiguous incidence sums (see incidence_contig_kernel); returns false when the layout does not qualify.
+static bool try_incidence_contig(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t stream, int &rc) {
+    const int f = a.f;
+    if (a.indices || a.ld != f || !(f == 1 || f == 2 || f == 4 || f == 8 || f == 16) || !aligned(a.feat, 16)) return false;
+    rc = TANGO_OK;
+    a.n_long = a.n_rows;
+    if (plan) a.row_order = plan->row_order;
+    if (plan && plan->n_units > 0) {
+        if (!plan->units || !plan->heavy_rows || !plan->ws || plan->ws_ld < f || plan->n_heavy <= 0 ||
+            !aligned(plan->units, 16)) { rc = TANGO_EINVAL; return true; }
+        a.units = plan->units; a.n_units = plan->n_units; a.heavy_rows = plan->heavy_rows;
+        a.n_heavy = plan->n_heavy; a.ws = plan->ws; a.ws_ld = plan->ws_ld; a.split_threshold = plan->split_threshold;
+        if (cudaMemsetAsync(a.ws, 0, sizeof(int32_t) * (size_t)(a.n_heavy * a.ws_ld), stream) != cudaSuccess) {
+            rc = TANGO_ECUDA; return true;
+        }
+    }
+    const int64_t blocks = ceil_div(a.n_units + a.n_rows, 4);
+    if (blocks > 0x7fffffff) { rc = TANGO_ESIZE; return true; }
+    switch (f) {
+        case 1: incidence_contig_kernel<1><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+        case 2: incidence_contig_kernel<2><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+        case 4: incidence_contig_kernel<4><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+        case 8: incidence_contig_kernel<8><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+        default: incidence_contig_kernel<16><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+    }
+    if (cudaPeekAtLastError() != cudaSuccess) { rc = TANGO_ECUDA; return true; }
+    if (a.n_units > 0) {
+        const int64_t fb = ceil_div(a.n_heavy * a.f, 256);
+        spmm_finalize_kernel<<<(unsigned)fb, 256, 0, stream>>>(a);
+        if (cudaPeekAtLastError() != cudaSuccess) rc = TANGO_ECUDA;
+    }
+    return true;
+}
+
 }  // namespace tango
 
 using namespace tango;
@@ -545,5 +656,7 @@ extern "C" int tango_spmm_incidence(const int32_t *indptr, const int32_t *edge_i
     a.indptr = indptr; a.indices = edge_ids; a.edge_ids = nullptr; a.n_rows = n_rows; a.nseg = 1;
     a.feat = zq; a.ld = ldz; a.f = (int)f; a.H = 1; a.D = (int)f;
     a.scales = scale; a.out = out; a.ldo = ldo;
+    int rc = TANGO_OK;
+    if (try_incidence_contig(a, plan, (cudaStream_t)stream, rc)) return rc;
     return launch_spmm<MODE_COPY>(a, plan, (cudaStream_t)stream);
 }

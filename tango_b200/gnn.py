@@ -182,21 +182,24 @@ class _edge_softmax_fn(Function):
 
     @staticmethod
     def forward(ctx, g, e, factor):
-        a = kernels.edge_softmax_fwd(g, e, factor)
+        a, sa = kernels.edge_softmax_fwd(g, e, factor, want_scale=True)
         ctx.save_for_backward(a)
         ctx.g, ctx.factor = g, factor
-        return a
+        ctx.mark_non_differentiable(sa)
+        return a, sa
 
     @staticmethod
     @once_differentiable
-    def backward(ctx, da):
+    def backward(ctx, da, _dsa):
         (a,) = ctx.saved_tensors
         return None, kernels.edge_softmax_bwd(ctx.g, a, da, ctx.factor), None
 
 
-def edge_softmax(g, e, factor: float = 1.0):
-    """softmax over each destination's incoming edges of e * factor."""
-    return _edge_softmax_fn.apply(g, e, factor)
+def edge_softmax(g, e, factor: float = 1.0, return_scale: bool = False):
+    """softmax over each destination's incoming edges of e * factor; with return_scale also max|a|/127, which the
+    kernel produces on the way and the consuming spmm_u_mul_e would otherwise recompute."""
+    a, sa = _edge_softmax_fn.apply(g, e, factor)
+    return (a, sa) if return_scale else a
 
 
 class _gat_attention_fused(Function):
@@ -215,18 +218,19 @@ class _gat_attention_fused(Function):
         n, h = el.shape[0], el.shape[1]
         elq, sl = kernels.quantize(el.reshape(n, h), mode=mode, seed=seed, align=1)
         erq, sr = kernels.quantize(er.reshape(n, h), mode=mode, seed=seed, align=1)
-        a = kernels.gat_edge_softmax(g, elq, erq, sl, sr, slope)
+        a, sa = kernels.gat_edge_softmax(g, elq, erq, sl, sr, slope, want_scale=True)
         ctx.g, ctx.slope, ctx.shapes = g, slope, (el.shape, er.shape)
         ctx.save_for_backward(elq, erq, sl, sr, a)
-        return a.view(a.shape[0], h, 1)
+        ctx.mark_non_differentiable(sa)
+        return a.view(a.shape[0], h, 1), sa
 
     @staticmethod
     @once_differentiable
-    def backward(ctx, da):
+    def backward(ctx, da, _dsa):
         elq, erq, sl, sr, a = ctx.saved_tensors
         g = ctx.g
-        dz = kernels.gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, ctx.slope)
-        dzq, sdz = kernels.quantize(dz, mode=config.mode_for("quantize"), seed=config.seed(), align=1)
+        dz, sdz = kernels.gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, ctx.slope, want_scale=True)
+        dzq, sdz = kernels.quantize(dz, sdz, mode=config.mode_for("quantize"), seed=config.seed(), align=1)
         d_el = kernels.incidence_SPMM(g, dzq, sdz, True).view(ctx.shapes[0]) if ctx.needs_input_grad[1] else None
         d_er = kernels.incidence_SPMM(g, dzq, sdz).view(ctx.shapes[1]) if ctx.needs_input_grad[2] else None
         return None, d_el, d_er, None
@@ -275,12 +279,15 @@ class QGATConv(nn.Module):
         ft = self.fc(h).view(*prefix, self._num_heads, self._out_feats)
         el = (ft * self.attn_l).sum(dim=-1).unsqueeze(-1)
         er = (ft * self.attn_r).sum(dim=-1).unsqueeze(-1)
+        sa = None
         if self._fused:
-            a = self.attn_drop(_gat_attention_fused.apply(graph, el, er, self._slope))
+            a, sa = _gat_attention_fused.apply(graph, el, er, self._slope)
+            if self.training and self.attn_drop.p > 0:
+                a, sa = self.attn_drop(a), None       # dropout rescales a: its absmax has to be taken again
         else:
             e = self.leaky_relu(sddmm_u_add_v.apply(graph, el, er))
             a = self.attn_drop(edge_softmax(graph, e))
-        rst = spmm_u_mul_e.apply(graph, ft, a)
+        rst = spmm_u_mul_e.apply(graph, ft, a, sa)
         if self.res_fc is not None:
             rst = rst + self.res_fc(h).view(*prefix, -1, self._out_feats)
         if self.bias is not None:
@@ -342,8 +349,8 @@ class HGT(nn.Module):
         v = self.msg_linear(self.v_linear(h)).view(-1, self.n_heads, self.d_k)
         q = self.q_linear(h).view(-1, self.n_heads, self.d_k)
         t = sddmm_u_dot_v.apply(g, k, q)
-        attn = edge_softmax(g, t, 1.0 / self.sqrt_dk)     # the reference divides t by sqrt(d_k) first
-        out = spmm_u_mul_e.apply(g, v, attn).view(-1, self.out_dim)
+        attn, s_attn = edge_softmax(g, t, 1.0 / self.sqrt_dk, True)   # the reference divides t by sqrt(d_k) first
+        out = spmm_u_mul_e.apply(g, v, attn, s_attn).view(-1, self.out_dim)
         return self.a_linear(out)
 
 

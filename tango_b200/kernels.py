@@ -280,7 +280,9 @@ def _incidence_spmm(out, indptr, edge_ids, E, scale, sched=None):
     with torch.cuda.device(E.device):
         check(lib.tango_spmm_incidence(_p(indptr), _p(edge_ids), n_rows, _p(E), ldz, f, _p(scale), _p(out), ldo, plan,
                                        _stream()), "incidence_SPMM")
-    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0) + (sched is not None and sched.n_long < sched.row_order.numel())
+    contiguous = edge_ids is None and ldz == f and f in (1, 2, 4, 8, 16)    # streamed by the contiguous-row kernel
+    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0) + (
+        not contiguous and sched is not None and sched.n_long < sched.row_order.numel())
     del keep
 
 
@@ -523,43 +525,51 @@ def multi_cusparse_SPMV(g, N_T, E_T, scale, reverse=False):
     return multi_cusparse_SPMM(g, N_T, E_T, scale, reverse)
 
 
-def gat_edge_softmax(g, elq, erq, sl, sr, slope: float = 0.2):
-    """Fused u_add_v -> LeakyReLU -> edge softmax over incoming edges; returns fp32 [E, H] in edge-id order."""
+def _scale_word(device, want: bool):
+    return torch.zeros(1, dtype=torch.float32, device=device) if want else None
+
+
+def gat_edge_softmax(g, elq, erq, sl, sr, slope: float = 0.2, want_scale: bool = False):
+    """Fused u_add_v -> LeakyReLU -> edge softmax over incoming edges; returns fp32 [E, H] in edge-id order (and,
+    with want_scale, max|a|/127 from the kernel's epilogue)."""
     indptr, indices, edge_ids = _bundle(g, False)
     h = elq.shape[1]
     elq = elq.reshape(elq.shape[0], -1).contiguous()
     erq = erq.reshape(erq.shape[0], -1).contiguous()
     a = torch.empty((g.num_edges(), h), dtype=torch.float32, device=elq.device)
+    sa = _scale_word(elq.device, want_scale)
     with torch.cuda.device(elq.device):
         sched = _schedule(g, False)
         order = sched.row_order if sched is not None else None
         check(lib.tango_gat_edge_softmax(_p(indptr), _p(indices), _p(edge_ids), _p(order),
                                          sched.n_block_rows if sched is not None else 0, g.num_nodes(), _p(elq), _p(erq), h,
-                                         _p(sl), _p(sr), float(slope), _p(a), _stream()), "gat_edge_softmax")
+                                         _p(sl), _p(sr), float(slope), _p(a), _p(sa), _stream()), "gat_edge_softmax")
     launch_counter[0] += 1
-    return a
+    return (a, sa) if want_scale else a
 
 
-def gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, slope: float = 0.2):
-    """Gradient of `gat_edge_softmax` with respect to the edge logits (before the LeakyReLU); fp32 [E, H]."""
+def gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, slope: float = 0.2, want_scale: bool = False):
+    """Gradient of `gat_edge_softmax` with respect to the edge logits (before the LeakyReLU); fp32 [E, H] (and, with
+    want_scale, max|dz|/127)."""
     indptr, indices, edge_ids = _bundle(g, False)
     h = elq.shape[1]
     elq = elq.reshape(elq.shape[0], -1).contiguous()
     erq = erq.reshape(erq.shape[0], -1).contiguous()
     a, da = a.reshape(-1, h).contiguous(), da.reshape(-1, h).contiguous()
     dz = torch.empty_like(a)
+    sdz = _scale_word(elq.device, want_scale)
     with torch.cuda.device(elq.device):
         sched = _schedule(g, False)
         order = sched.row_order if sched is not None else None
         check(lib.tango_gat_edge_softmax_bwd(_p(indptr), _p(indices), _p(edge_ids), _p(order),
                                              sched.n_block_rows if sched is not None else 0, g.num_nodes(), _p(elq), _p(erq), h,
-                                             _p(sl), _p(sr), float(slope), _p(a), _p(da), _p(dz), _stream()),
+                                             _p(sl), _p(sr), float(slope), _p(a), _p(da), _p(dz), _p(sdz), _stream()),
               "gat_edge_softmax_bwd")
     launch_counter[0] += 1
-    return dz
+    return (dz, sdz) if want_scale else dz
 
 
-def edge_softmax_fwd(g, z: torch.Tensor, zmul: float = 1.0) -> torch.Tensor:
+def edge_softmax_fwd(g, z: torch.Tensor, zmul: float = 1.0, want_scale: bool = False):
     """Softmax of fp32 edge scores z [E, H, ...] (times zmul) over the incoming edges of every destination; the
     reference calls dgl.ops.edge_softmax (evaluation/test_HGT.py:60).  Returns fp32 of z's shape."""
     assert z.is_cuda and z.dtype == torch.float32
@@ -570,31 +580,33 @@ def edge_softmax_fwd(g, z: torch.Tensor, zmul: float = 1.0) -> torch.Tensor:
     if h > 8:
         raise ValueError("edge_softmax: at most 8 heads")
     a = torch.empty_like(z2)
+    sa = _scale_word(z.device, want_scale)
     with torch.cuda.device(z.device):
         sched = _schedule(g, False)
         order = sched.row_order if sched is not None else None
         check(lib.tango_edge_softmax(_p(indptr), _p(edge_ids), _p(order),
                                      sched.n_block_rows if sched is not None else 0, g.num_nodes(), _p(z2), h,
-                                     float(zmul), _p(a), _stream()), "edge_softmax")
+                                     float(zmul), _p(a), _p(sa), _stream()), "edge_softmax")
     launch_counter[0] += 1
-    return a.view(z.shape)
+    return (a.view(z.shape), sa) if want_scale else a.view(z.shape)
 
 
-def edge_softmax_bwd(g, a: torch.Tensor, da: torch.Tensor, zmul: float = 1.0) -> torch.Tensor:
+def edge_softmax_bwd(g, a: torch.Tensor, da: torch.Tensor, zmul: float = 1.0, want_scale: bool = False):
     """Gradient of `edge_softmax_fwd` with respect to z."""
     indptr, _, edge_ids = _bundle(g, False)
     a2 = a.reshape(a.shape[0], -1).contiguous()
     da2 = da.reshape(a2.shape).contiguous()
     h = a2.shape[1]
     dz = torch.empty_like(a2)
+    sdz = _scale_word(a.device, want_scale)
     with torch.cuda.device(a.device):
         sched = _schedule(g, False)
         order = sched.row_order if sched is not None else None
         check(lib.tango_edge_softmax_bwd(_p(indptr), _p(edge_ids), _p(order),
                                          sched.n_block_rows if sched is not None else 0, g.num_nodes(), h, float(zmul),
-                                         _p(a2), _p(da2), _p(dz), _stream()), "edge_softmax_bwd")
+                                         _p(a2), _p(da2), _p(dz), _p(sdz), _stream()), "edge_softmax_bwd")
     launch_counter[0] += 1
-    return dz.view(a.shape)
+    return (dz.view(a.shape), sdz) if want_scale else dz.view(a.shape)
 
 
 def relu_grad_stats(g: torch.Tensor, y: torch.Tensor, row_scale: Optional[torch.Tensor] = None,

@@ -228,6 +228,39 @@ def test_incidence_spmm(cuda, dim):
     np.testing.assert_array_equal(out.cpu().numpy(), out_in)
 
 
+@pytest.mark.parametrize("dim", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("star", [False, True])
+def test_incidence_spmm_contiguous_rows(cuda, dim, star):
+    """Edges numbered in CSC order: the in-edge sums stream contiguous byte ranges (aligned 128-bit loads, ragged
+    head and tail, hub rows cut into slices); must equal the oracle and the indirect (edge_ids) kernel bit for bit."""
+    import tango_b200 as T
+    from tango_b200 import kernels as K
+    from tango_b200.graph import Graph, rmat_graph
+    if star:
+        n = 3000
+        src = torch.cat([torch.arange(n).repeat(10), torch.arange(n)])
+        dst = torch.cat([torch.zeros(10 * n, dtype=torch.long), (torch.arange(n) * 7 + 1) % n])
+        perm = torch.argsort(dst * n + src, stable=True)
+        g = Graph(src[perm], dst[perm], n).to("cuda")
+    else:
+        n = 700
+        g = rmat_graph(n, 9000, 43, device="cuda", edge_order="dst")
+    T.graph_preprocess(g)
+    assert K._bundle(g, False)[2] is None                    # identity numbering detected
+    (csr, csc, src_np, dst_np) = _np_graph(g)
+    E = g.num_edges()
+    zq = np.random.default_rng(dim).integers(-127, 128, (E, dim), dtype=np.int8)
+    s = np.float32(0.02)
+    out_in = K.incidence_SPMM(g, _dev(zq), _scale_t(s)).cpu().numpy()
+    np.testing.assert_array_equal(out_in, O.spmm_incidence(csc[0], csc[2], zq, s))
+    out_out = K.incidence_SPMM(g, _dev(zq), _scale_t(s), True).cpu().numpy()
+    np.testing.assert_array_equal(out_out, O.spmm_incidence(csr[0], csr[2], zq, s))
+    # the indirect kernel on the same data (explicit edge ids)
+    out2 = torch.empty((n, dim), device="cuda")
+    K._incidence_spmm(out2, g.adj_csc[0], g.adj_csc[2], _dev(zq), _scale_t(s), K._schedule(g, False))
+    np.testing.assert_array_equal(out2.cpu().numpy(), out_in)
+
+
 def test_spmm_segmented_per_shard_scales(cuda):
     """Row-partitioned form: nseg segments per row, one scale per source shard."""
     from tango_b200 import kernels as K
@@ -347,7 +380,9 @@ def test_gat_edge_softmax(cuda):
     el = rng.integers(-127, 128, (200, 4), dtype=np.int8)
     er = rng.integers(-127, 128, (200, 4), dtype=np.int8)
     sl, sr = np.float32(0.02), np.float32(0.015)
-    a = K.gat_edge_softmax(g, _dev(el), _dev(er), _scale_t(sl), _scale_t(sr), 0.2).cpu().numpy()
+    a, sa = K.gat_edge_softmax(g, _dev(el), _dev(er), _scale_t(sl), _scale_t(sr), 0.2, want_scale=True)
+    assert sa.item() == (a.max() / 127).item()               # the epilogue's scale is the quantizer's scale
+    a = a.cpu().numpy()
     z = O.leaky_relu(O.sddmm_elementwise("add", src, dst, el, er, sl, sr), 0.2)
     ref = O.edge_softmax(csc[0], csc[2], z)
     np.testing.assert_allclose(a, ref, rtol=1e-4, atol=1e-6)   # fp32 exp: tolerance, not bit-exact
@@ -375,13 +410,15 @@ def test_edge_softmax_plain_scores(cuda, heads, order):
     rng = np.random.default_rng(heads)
     z = (rng.standard_normal((e, heads)) * 3).astype(np.float32)
     zmul = 0.35
-    a = K.edge_softmax_fwd(g, _dev(z).view(e, heads, 1), zmul)
-    assert a.shape == (e, heads, 1)
+    a, sa = K.edge_softmax_fwd(g, _dev(z).view(e, heads, 1), zmul, want_scale=True)
+    assert a.shape == (e, heads, 1) and sa.item() == K.cuda_kernels.get_scale(a).item()
     ref = O.edge_softmax(csc[0], csc[2], (z * np.float32(zmul)).astype(np.float32))
     np.testing.assert_allclose(a.cpu().numpy().reshape(e, heads), ref, rtol=1e-4, atol=1e-7)
     # gradient against autograd of the same formula
     da = torch.from_numpy(rng.standard_normal((e, heads)).astype(np.float32)).cuda()
-    dz = K.edge_softmax_bwd(g, a, da.view(e, heads, 1), zmul).reshape(e, heads)
+    dz, sdz = K.edge_softmax_bwd(g, a, da.view(e, heads, 1), zmul, want_scale=True)
+    assert sdz.item() == K.cuda_kernels.get_scale(dz).item()
+    dz = dz.reshape(e, heads)
     zt = _dev(z).requires_grad_(True)
     dstl = torch.from_numpy(dst_np).long().cuda()
     ex = torch.exp(zt * zmul - 2.0)
