@@ -188,6 +188,11 @@ def run_ours(args):
     name = args.workload
     n, _, in_feats, hidden, classes, _ = WORKLOADS[name]
     T.config.set_rounding(args.rounding, seed=1234)
+    step_counter = None
+    if args.rounding == "stochastic":
+        # read by the quantizers on the device, bumped inside the step: every replay of the captured graph rounds anew
+        step_counter = torch.zeros(1, dtype=torch.int64, device=dev)
+        T.config.set_step_counter(step_counter)
     g = build_graph(name, dev)
     n_edges = g.num_edges()
     torch.manual_seed(6)
@@ -213,6 +218,8 @@ def run_ours(args):
     d_feats, d_labels = h_feats.to(dev), h_labels.to(dev)
 
     def step(feats, labels):
+        if step_counter is not None:
+            step_counter.add_(1)
         opt.zero_grad(set_to_none=True)
         logits = model(feats)
         loss = F.cross_entropy(logits, labels, reduction="none").sum() / n

@@ -67,11 +67,14 @@ int tango_absmax_scale(const float *x, int64_t rows, int64_t cols, int64_t ld, c
 
 /* q[r,c] = round_mode(x[r,c] * (1/scale[0])) clamped to [-127,127]; columns [cols, ldq) of q are set to 0.
  * row_scale (optional) multiplies x[r,:] first.  `seed`/`call` key the stochastic stream; the random
- * number of element (r,c) depends only on (seed, call, r*cols + c).
+ * number of element (r,c) depends only on (seed, call, r*cols + c).  `step` (optional, here and in the two entry
+ * points below that take it) points to a device word whose value, shifted left by 32, is added to `call` when the
+ * kernel runs: scalar arguments are frozen when a launch is captured in a CUDA graph, a device word is not, so a
+ * training loop that replays a graph bumps that word once per step to draw fresh random numbers.
  * Replaces quantize (cuda/src/cuda.cpp:185, cuda/src/quantization.cu:17-43). */
 int tango_quantize(const float *x, int64_t rows, int64_t cols, int64_t ldx, const float *row_scale,
                    const float *scale, int8_t *q, int64_t ldq, int mode, uint64_t seed, uint64_t call,
-                   tango_stream_t stream);
+                   const uint64_t *step, tango_stream_t stream);
 
 /* out[c, r] = nearest(x[r, c] / scale[0]) for x fp32 [nrow, ncol] contiguous -> int8 [ncol, nrow] contiguous.
  * Replaces transpose_quant (cuda/src/cuda.cpp:187, cuda/src/quantization.cu:95-167). */
@@ -91,7 +94,7 @@ int tango_relu_grad_stats(const float *g, int64_t ldg, const float *y, int64_t l
                           tango_stream_t stream);
 int tango_quantize_relu_grad(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows, int64_t cols,
                              const float *row_scale, const float *scale, int8_t *q, int64_t ldq, int mode,
-                             uint64_t seed, uint64_t call, tango_stream_t stream);
+                             uint64_t seed, uint64_t call, const uint64_t *step, tango_stream_t stream);
 
 /* ---------------------------------------------------------------- int8 GEMMs (tcgen05 kind::i8) */
 
@@ -114,7 +117,7 @@ int tango_qgemm_nt(const int8_t *xq, int64_t ldx, const int8_t *wq, int64_t ldw,
 int tango_qgemm_forward(const float *x, int64_t ldx_f, const float *row_scale, const float *w, int64_t ldw_f,
                         int64_t m, int64_t n, int64_t k, const float *sx, const float *sw, int8_t *xq, int64_t ldxq,
                         int8_t *wq, int64_t ldwq, const float *bias, float *y, int64_t ldy, float *scale_y, int mode,
-                        uint64_t seed, uint64_t call, int *status, tango_stream_t stream);
+                        uint64_t seed, uint64_t call, const uint64_t *step, int *status, tango_stream_t stream);
 
 /* dX[M,K] = float(dYq[M,N] . Wq[N,K]) * (sdy[0]*sw[0]), then row r times row_scale[r] if row_scale != NULL (the
  * backward of a left normalisation folded into the epilogue).

@@ -46,16 +46,16 @@ _SIGS = {
     "tango_strerror": ([c_int], c_char_p),
     "tango_last_cuda_error": ([], c_int),
     "tango_absmax_scale": ([P, c_int64, c_int64, c_int64, P, P, P], c_int),
-    "tango_quantize": ([P, c_int64, c_int64, c_int64, P, P, P, c_int64, c_int, c_uint64, c_uint64, P], c_int),
+    "tango_quantize": ([P, c_int64, c_int64, c_int64, P, P, P, c_int64, c_int, c_uint64, c_uint64, P, P], c_int),
     "tango_quantize_transpose": ([P, c_int64, c_int64, P, P, P], c_int),
     "tango_relu_grad_stats_scratch_bytes": ([c_int64, c_int64], c_int64),
     "tango_relu_grad_stats": ([P, c_int64, P, c_int64, c_int64, c_int64, P, P, P, P, c_int64, P], c_int),
     "tango_quantize_relu_grad": ([P, c_int64, P, c_int64, c_int64, c_int64, P, P, P, c_int64, c_int, c_uint64,
-                                  c_uint64, P], c_int),
+                                  c_uint64, P, P], c_int),
     "tango_qgemm_dw_workspace_bytes": ([c_int64, c_int64], c_int64),
     "tango_qgemm_nt": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, P, c_int64, P, P, P], c_int),
     "tango_qgemm_forward": ([P, c_int64, P, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, c_int64, P, P,
-                             c_int64, P, c_int, c_uint64, c_uint64, P, P], c_int),
+                             c_int64, P, c_int, c_uint64, c_uint64, P, P, P], c_int),
     "tango_qgemm_dx": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, P, c_int64, P, P], c_int),
     "tango_qgemm_dw": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, c_int64, P, P], c_int),
     "tango_qgemm_dw_noalloc": ([P, c_int64, P, c_int64, c_int64, c_int64, c_int64, P, P, P, c_int64, P, P], c_int),

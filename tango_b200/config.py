@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from ._lib import ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_TRUNC
 
-_state = {"rounding": "reference", "seed": 0, "share_quantized_inputs": False}
+_state = {"rounding": "reference", "seed": 0, "share_quantized_inputs": False, "step_counter": None}
 
 
 def set_rounding(mode: str = "reference", seed: int = 0) -> None:
@@ -48,3 +48,18 @@ def share_quantized_inputs(enable: bool = True) -> None:
 
 def sharing_quantized_inputs() -> bool:
     return _state["share_quantized_inputs"]
+
+
+def set_step_counter(counter) -> None:
+    """A 1-element int64 CUDA tensor (or None) that the stochastic quantizers read on the device and add, shifted
+    left by 32, to their per-call counter.  A loop that replays a captured CUDA graph increments it once per step
+    (inside the graph: `counter.add_(1)`), so every replay draws new random numbers although the launch arguments
+    are frozen; without it a replayed step repeats the rounding noise of the captured one."""
+    if counter is not None:
+        import torch
+        assert counter.is_cuda and counter.dtype == torch.int64 and counter.numel() == 1
+    _state["step_counter"] = counter
+
+
+def step_counter():
+    return _state["step_counter"]

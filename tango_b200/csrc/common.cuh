@@ -87,6 +87,13 @@ __device__ __forceinline__ int round_to_i8(float t, int mode, float u) {
     return (int)r;
 }
 
+// Call counter of a stochastic-rounding draw: the host's per-call number in the low 32 bits plus, in the high 32 bits,
+// a step number read from device memory -- the one part of the counter that can change between replays of a captured
+// CUDA graph, whose scalar arguments are frozen at capture time.
+__device__ __forceinline__ uint64_t effective_call(uint64_t call, const unsigned long long *step) {
+    return step ? call + ((uint64_t)__ldg(step) << 32) : call;
+}
+
 // Stochastic-rounding uniform in [0,1) of flat element index `flat`: lane flat%4 of Philox block flat/4, keyed by
 // (seed, call).  `cached_blk` / `rnd` let consecutive elements of one thread share a block.
 __device__ __forceinline__ float sr_uniform(const Philox &ph, uint64_t flat, uint64_t call, uint64_t &cached_blk,

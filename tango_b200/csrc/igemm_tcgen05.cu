@@ -742,11 +742,11 @@ extern "C" int tango_qgemm_nt(const int8_t *xq, int64_t ldx, const int8_t *wq, i
 extern "C" int tango_qgemm_forward(const float *x, int64_t ldx_f, const float *row_scale, const float *w,
                                    int64_t ldw_f, int64_t m, int64_t n, int64_t k, const float *sx, const float *sw,
                                    int8_t *xq, int64_t ldxq, int8_t *wq, int64_t ldwq, const float *bias, float *y,
-                                   int64_t ldy, float *scale_y, int mode, uint64_t seed, uint64_t call, int *status,
-                                   tango_stream_t stream) {
-    int rc = tango_quantize(x, m, k, ldx_f, row_scale, sx, xq, ldxq, mode, seed, call, stream);
+                                   int64_t ldy, float *scale_y, int mode, uint64_t seed, uint64_t call,
+                                   const uint64_t *step, int *status, tango_stream_t stream) {
+    int rc = tango_quantize(x, m, k, ldx_f, row_scale, sx, xq, ldxq, mode, seed, call, step, stream);
     if (rc) return rc;
-    rc = tango_quantize(w, n, k, ldw_f, nullptr, sw, wq, ldwq, mode, seed, call + 1, stream);
+    rc = tango_quantize(w, n, k, ldw_f, nullptr, sw, wq, ldwq, mode, seed, call + 1, step, stream);
     if (rc) return rc;
     return tango_qgemm_nt(xq, ldxq, wq, ldwq, m, n, k, sx, sw, bias, y, ldy, scale_y, status, stream);
 }

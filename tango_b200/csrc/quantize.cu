@@ -50,7 +50,9 @@ template <int LW>
 __global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
                                                        int64_t ldx, const float *__restrict__ row_scale,
                                                        const float *__restrict__ scale, int8_t *__restrict__ q,
-                                                       int64_t ldq, int mode, uint64_t seed, uint64_t call) {
+                                                       int64_t ldq, int mode, uint64_t seed, uint64_t call0,
+    const unsigned long long *__restrict__ step) {
+    const uint64_t call = effective_call(call0, step);
     const float inv = inv_scale(__ldg(scale));
     const int64_t groups = (ldq + 15) >> 4, total = rows * groups;
     const Philox ph{(uint32_t)seed, (uint32_t)(seed >> 32)};
@@ -109,7 +111,9 @@ __global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__
 __global__ void __launch_bounds__(256) quantize_scalar_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
                                                               int64_t ldx, const float *__restrict__ row_scale,
                                                               const float *__restrict__ scale, int8_t *__restrict__ q,
-                                                              int64_t ldq, int mode, uint64_t seed, uint64_t call) {
+                                                              int64_t ldq, int mode, uint64_t seed, uint64_t call0,
+    const unsigned long long *__restrict__ step) {
+    const uint64_t call = effective_call(call0, step);
     const float inv = inv_scale(__ldg(scale));
     const int64_t total = rows * ldq;
     const Philox ph{(uint32_t)seed, (uint32_t)(seed >> 32)};
@@ -207,7 +211,8 @@ extern "C" int tango_absmax_scale(const float *x, int64_t rows, int64_t cols, in
 
 extern "C" int tango_quantize(const float *x, int64_t rows, int64_t cols, int64_t ldx, const float *row_scale,
                               const float *scale, int8_t *q, int64_t ldq, int mode, uint64_t seed, uint64_t call,
-                              tango_stream_t stream_) {
+                              const uint64_t *step_, tango_stream_t stream_) {
+    const unsigned long long *step = reinterpret_cast<const unsigned long long *>(step_);
     cudaStream_t stream = (cudaStream_t)stream_;
     if (rows < 0 || cols < 0 || ldx < cols || ldq < cols || mode < 0 || mode > 2) return TANGO_EINVAL;
     if (rows == 0 || ldq == 0) return TANGO_OK;
@@ -219,14 +224,14 @@ extern "C" int tango_quantize(const float *x, int64_t rows, int64_t cols, int64_
         const int lw = (aligned(x, 16) && (rows == 1 || ldx % 4 == 0)) ? 4 : (aligned(x, 8) && (rows == 1 || ldx % 2 == 0)) ? 2 : 1;
         const int grid = stream_grid(rows * ceil_div(ldq, 16), 256, 16);
         if (lw == 4)
-            quantize_kernel<4><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+            quantize_kernel<4><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step);
         else if (lw == 2)
-            quantize_kernel<2><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+            quantize_kernel<2><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step);
         else
-            quantize_kernel<1><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+            quantize_kernel<1><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step);
     } else {
         const int grid = stream_grid(rows * ldq, 256, 8);
-        quantize_scalar_kernel<<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call);
+        quantize_scalar_kernel<<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step);
     }
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
@@ -338,7 +343,9 @@ __global__ void __launch_bounds__(256) relu_grad_quant_kernel(const float *__res
                                                               const float *__restrict__ y, int64_t ldy, int64_t rows,
                                                               int64_t cols, const float *__restrict__ row_scale,
                                                               const float *__restrict__ scale, int8_t *__restrict__ q,
-                                                              int64_t ldq, int mode, uint64_t seed, uint64_t call) {
+                                                              int64_t ldq, int mode, uint64_t seed, uint64_t call0,
+    const unsigned long long *__restrict__ step) {
+    const uint64_t call = effective_call(call0, step);
     const float inv = inv_scale(__ldg(scale));
     const int64_t groups = ldq >> 4, total = rows * groups;   // ldq % 16 == 0
     const Philox ph{(uint32_t)seed, (uint32_t)(seed >> 32)};
@@ -417,7 +424,9 @@ extern "C" int tango_relu_grad_stats(const float *g, int64_t ldg, const float *y
 
 extern "C" int tango_quantize_relu_grad(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows,
                                         int64_t cols, const float *row_scale, const float *scale, int8_t *q,
-                                        int64_t ldq, int mode, uint64_t seed, uint64_t call, tango_stream_t stream_) {
+                                        int64_t ldq, int mode, uint64_t seed, uint64_t call, const uint64_t *step_,
+                                        tango_stream_t stream_) {
+    const unsigned long long *step = reinterpret_cast<const unsigned long long *>(step_);
     cudaStream_t stream = (cudaStream_t)stream_;
     if (rows < 0 || cols < 0 || ldg < cols || ldy < cols || ldq < cols || mode < 0 || mode > 2) return TANGO_EINVAL;
     if (rows == 0 || ldq == 0) return TANGO_OK;
@@ -425,8 +434,8 @@ extern "C" int tango_quantize_relu_grad(const float *g, int64_t ldg, const float
     if (ldq % 16 != 0 || !aligned(q, 16)) return TANGO_EALIGN;
     const bool vec = ldg % 4 == 0 && ldy % 4 == 0 && aligned(g, 16) && aligned(y, 16);
     const int grid = stream_grid(rows * (ldq / 16), 256, 16);
-    if (vec) relu_grad_quant_kernel<true><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call);
-    else relu_grad_quant_kernel<false><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call);
+    if (vec) relu_grad_quant_kernel<true><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call, step);
+    else relu_grad_quant_kernel<false><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call, step);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
 }

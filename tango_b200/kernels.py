@@ -19,7 +19,7 @@ from typing import Optional
 
 import torch
 
-from . import _lib
+from . import _lib, config
 from ._lib import ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_TRUNC, SpmmPlan, check, lib
 from .graph import SpmmSchedule
 
@@ -160,7 +160,7 @@ def _quantize_into(out: torch.Tensor, t: torch.Tensor, scale: torch.Tensor, mode
     assert o2.data_ptr() == out.data_ptr(), "output int8 tensor must be row-strided, not arbitrary-strided"
     with torch.cuda.device(t.device):
         check(lib.tango_quantize(_p(t), rows, cols, ldx, _p(row_scale), _p(scale), _p(out), ldq, mode, seed, call,
-                                 _stream()), "quantize")
+                                 _p(config.step_counter()), _stream()), "quantize")
     launch_counter[0] += 1
 
 
@@ -183,7 +183,8 @@ def _qgemm_forward(Y, X, X_q, W, W_q, bias, scaleY, scaleX, scaleW, mode=ROUND_T
     st = _status_word(X.device)
     with torch.cuda.device(X.device):
         check(lib.tango_qgemm_forward(_p(X), ldx, _p(row_scale), _p(W), ldw, m, n, k, _p(scaleX), _p(scaleW), _p(X_q), ldxq, _p(W_q),
-                                      ldwq, _p(bias), _p(Y), ldy, _p(scaleY), mode, seed, call, _p(st), _stream()),
+                                      ldwq, _p(bias), _p(Y), ldy, _p(scaleY), mode, seed, call, _p(config.step_counter()),
+                                      _p(st), _stream()),
               "QGEMM_forward")
     launch_counter[0] += 3
 
@@ -633,7 +634,8 @@ def relu_grad_quant(g: torch.Tensor, y: torch.Tensor, row_scale: Optional[torch.
     q = alloc_int8((rows, cols), g.device)
     with torch.cuda.device(g.device):
         check(lib.tango_quantize_relu_grad(_p(g), ldg, _p(y), ldy, rows, cols, _p(row_scale), _p(scale), _p(q),
-                                           q.stride(0), mode, seed, call, _stream()), "quantize_relu_grad")
+                                           q.stride(0), mode, seed, call, _p(config.step_counter()), _stream()),
+              "quantize_relu_grad")
     launch_counter[0] += 1
     return q
 

@@ -33,9 +33,9 @@ def test_version_and_strerror():
 def test_argument_validation_without_gpu():
     from tango_b200 import _lib
     L = _lib.lib
-    assert L.tango_quantize(None, -1, 4, 4, None, None, None, 4, 1, 0, 0, None) == -1          # negative rows
-    assert L.tango_quantize(None, 4, 4, 4, None, None, None, 4, 7, 0, 0, None) == -1           # bad mode
-    assert L.tango_quantize(None, 4, 8, 4, None, None, None, 8, 1, 0, 0, None) == -1           # ld < cols
+    assert L.tango_quantize(None, -1, 4, 4, None, None, None, 4, 1, 0, 0, None, None) == -1    # negative rows
+    assert L.tango_quantize(None, 4, 4, 4, None, None, None, 4, 7, 0, 0, None, None) == -1     # bad mode
+    assert L.tango_quantize(None, 4, 8, 4, None, None, None, 8, 1, 0, 0, None, None) == -1     # ld < cols
     assert L.tango_sddmm_elementwise(9, None, None, 1, None, 4, None, 4, 4, None, None, None, None, None) == -1
     assert L.tango_spmm_copy_u(None, None, 4, 0, None, 16, 16, None, None, None, 0, None, 16, None, None, None) == -1
     assert L.tango_qgemm_nt(None, 16, None, 16, 8, 8, 0, None, None, None, None, 8, None, None, None) == -1

@@ -106,6 +106,47 @@ def test_stochastic_rounding_is_unbiased_and_seeded(cuda):
     assert set(a[1:].unique().tolist()) == {38, 39}
 
 
+def test_stochastic_rounding_step_counter_survives_graph_replay(cuda):
+    """The device-side step word is added (shifted by 32) to the call counter: equal to the oracle with that counter,
+    and a captured CUDA graph that bumps the word draws new random numbers at every replay."""
+    from tango_b200 import config, kernels as K
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((64, 41)).astype(np.float32)
+    xd = _dev(x)
+    s = O.absmax_scale(x)
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+    config.set_step_counter(counter)
+    try:
+        counter.fill_(3)
+        q, _ = K.quantize(xd, None, mode=2, seed=77, call=5)
+        np.testing.assert_array_equal(q.cpu().numpy(), O.quantize(x, s, 2, seed=77, call=5 + (3 << 32)))
+        # graph: bump the word, then quantize; scalar arguments (call = 5) are frozen at capture time
+        counter.zero_()
+        st = _scale_t(s)
+        out = K.alloc_int8(x.shape, "cuda")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            K._quantize_into(out, xd, st, 2, 77, 5)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            counter.add_(1)
+            K._quantize_into(out, xd, st, 2, 77, 5)
+        seen = []
+        for k in range(1, 4):
+            graph.replay()
+            torch.cuda.synchronize()
+            assert int(counter) == k
+            got = out.cpu().numpy().copy()
+            np.testing.assert_array_equal(got, O.quantize(x, s, 2, seed=77, call=5 + (k << 32)))
+            seen.append(got)
+        assert not np.array_equal(seen[0], seen[1]) and not np.array_equal(seen[1], seen[2])
+    finally:
+        config.set_step_counter(None)
+
+
 def test_transpose_quant(cuda):
     from tango_b200 import kernels as K
     rng = np.random.default_rng(11)
