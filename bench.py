@@ -448,6 +448,17 @@ def run_case(args):
         torch.cuda.synchronize()
         print(json.dumps({"case": args.case, "nodes": n, "edges": g.num_edges(), "f": f,
                           "checksum": float(out.double().sum())}))
+    elif args.case == "sddmm_rows":
+        n, e, h, d = 232_965, 20_000_000, 4, 64
+        g = rmat_graph(n, e, 7, device=dev)
+        T.graph_preprocess(g)
+        uq, su = K.quantize(torch.randn((n, h, d), device=dev))
+        vq, sv = K.quantize(torch.randn((n, h, d), device=dev))
+        for _ in range(3):
+            out, _ = K.mySDDMM_int8(g, "dot", uq, vq, su, sv, False)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "nodes": n, "edges": g.num_edges(), "h": h, "d": d,
+                          "checksum": float(out.double().sum())}))
     elif args.case == "gemm":
         m, k, n = 65_536, 602, 256
         x, w, dy = torch.randn((m, k), device=dev), torch.randn((n, k), device=dev) * 0.04, torch.randn((m, n), device=dev)
@@ -590,7 +601,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of a CUDA graph")
     ap.add_argument("--suite", default=None, choices=["primitives"],
                     help="per-primitive numbers on the QLinear and SpMM/SDDMM configurations instead of the epoch")
-    ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, gemm) and exit")
+    ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, sddmm_rows, gemm) and exit")
     args = ap.parse_args()
     if args.suite == "primitives":
         run_primitives(args)

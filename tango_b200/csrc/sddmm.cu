@@ -135,7 +135,7 @@ struct DotRowArgs {
     float *out_absmax;
 };
 
-template <int VEC>
+template <int VEC, bool QUAD>
 __device__ __forceinline__ void dot_row_segment(const DotRowArgs &a, int64_t row, int beg, int end, float sc,
                                                 float &amax) {
     typedef typename DotVec<VEC>::T V;
@@ -149,6 +149,7 @@ __device__ __forceinline__ void dot_row_segment(const DotRowArgs &a, int64_t row
     const uint32_t ld = (uint32_t)a.ldu;
     const int head = (sub * VEC) / (a.LH * VEC);            // LH lanes per head
     const bool writer = active && (sub % a.LH) == 0 && head < a.H;
+    const bool quad_writer = (sub % a.LH) < 4 && head < a.H;   // QUAD: lane r of the head's first quad stores step r
     constexpr int U = 4;
     int j0 = beg;
     int nxt_idx = 0, nxt_eid = 0;
@@ -165,22 +166,40 @@ __device__ __forceinline__ void dot_row_segment(const DotRowArgs &a, int64_t row
             }
             for (int s = 0, lane0 = grp; s < G; s += U, lane0 += U * NB) {
                 V ur[U];
-                int eid[U];
 #pragma unroll
                 for (int k = 0; k < U; ++k) {
-                    const int src_lane = lane0 + k * NB;
-                    const int idx = __shfl_sync(0xffffffffu, my_idx, src_lane);
-                    eid[k] = __shfl_sync(0xffffffffu, my_eid, src_lane);
+                    const int idx = __shfl_sync(0xffffffffu, my_idx, lane0 + k * NB);
                     ur[k] = __ldg(reinterpret_cast<const V *>(ubase + (uint64_t)(uint32_t)idx * ld));
                 }
+                int p[U];
 #pragma unroll
-                for (int k = 0; k < U; ++k) {
-                    int acc = active ? dot_regs<VEC>(ur[k], vr) : 0;
-                    for (int o = a.LH >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                    if (writer) {
-                        const float r = __fmul_rn((float)acc, sc);
-                        __stcs(a.out + (int64_t)eid[k] * a.H + head, r);
+                for (int k = 0; k < U; ++k) p[k] = active ? dot_regs<VEC>(ur[k], vr) : 0;
+                if (QUAD) {
+                    // Four lanes or more per head: three exchanges leave lane r = sub % 4 of every aligned lane quad
+                    // with step r's sum over the quad (instead of 2 x 4 shuffles that leave 3 of 4 lanes idle), the
+                    // remaining lanes of the head are folded in, and every one of those four lanes stores one value.
+                    const bool b0 = sub & 1, b1 = sub & 2;
+                    const int s01 = (b0 ? p[1] : p[0]) + __shfl_xor_sync(0xffffffffu, b0 ? p[0] : p[1], 1);
+                    const int s23 = (b0 ? p[3] : p[2]) + __shfl_xor_sync(0xffffffffu, b0 ? p[2] : p[3], 1);
+                    int t = (b1 ? s23 : s01) + __shfl_xor_sync(0xffffffffu, b1 ? s01 : s23, 2);
+                    for (int o = 4; o < a.LH; o <<= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+                    const int e = __shfl_sync(0xffffffffu, my_eid, lane0 + (sub & 3) * NB);   // edge of step sub % 4
+                    if (quad_writer) {
+                        const float r = __fmul_rn((float)t, sc);
+                        __stcs(a.out + (int64_t)e * a.H + head, r);
                         amax = fmaxf(amax, fabsf(r));
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < U; ++k) {
+                        int acc = p[k];
+                        for (int o = a.LH >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                        const int e = __shfl_sync(0xffffffffu, my_eid, lane0 + k * NB);
+                        if (writer) {
+                            const float r = __fmul_rn((float)acc, sc);
+                            __stcs(a.out + (int64_t)e * a.H + head, r);
+                            amax = fmaxf(amax, fabsf(r));
+                        }
                     }
                 }
             }
@@ -212,7 +231,7 @@ __device__ __forceinline__ void dot_row_segment(const DotRowArgs &a, int64_t row
     }
 }
 
-template <int VEC>
+template <int VEC, bool QUAD>
 __global__ void __launch_bounds__(128, 8) sddmm_dot_rows_kernel(const DotRowArgs a) {
     const int lane = threadIdx.x & 31;
     const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -220,12 +239,12 @@ __global__ void __launch_bounds__(128, 8) sddmm_dot_rows_kernel(const DotRowArgs
     float amax = 0.f;
     if (w < a.n_units) {
         const int4 u = __ldg(reinterpret_cast<const int4 *>(a.units) + w);
-        dot_row_segment<VEC>(a, u.x, u.y, u.z, sc, amax);
+        dot_row_segment<VEC, QUAD>(a, u.x, u.y, u.z, sc, amax);
     } else if (w - a.n_units < a.n_rows) {
         int64_t row = w - a.n_units;
         if (a.row_order) row = __ldg(a.row_order + row);
         const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
-        if (!(a.n_units > 0 && end - beg > a.split_threshold)) dot_row_segment<VEC>(a, row, beg, end, sc, amax);
+        if (!(a.n_units > 0 && end - beg > a.split_threshold)) dot_row_segment<VEC, QUAD>(a, row, beg, end, sc, amax);
     }
     if (a.out_absmax) {
         amax = warp_max(amax);
@@ -379,8 +398,11 @@ extern "C" int tango_sddmm_dot_rows(const int32_t *indptr, const int32_t *indice
     }
     const int64_t blocks = ceil_div(a.n_units + a.n_rows, 4);
     if (blocks > 0x7fffffff) return TANGO_ESIZE;
-    if (vec == 16) sddmm_dot_rows_kernel<16><<<(unsigned)blocks, 128, 0, stream>>>(a);
-    else sddmm_dot_rows_kernel<4><<<(unsigned)blocks, 128, 0, stream>>>(a);
+    const bool quad = a.LH >= 4;
+    if (vec == 16 && quad) sddmm_dot_rows_kernel<16, true><<<(unsigned)blocks, 128, 0, stream>>>(a);
+    else if (vec == 16) sddmm_dot_rows_kernel<16, false><<<(unsigned)blocks, 128, 0, stream>>>(a);
+    else if (quad) sddmm_dot_rows_kernel<4, true><<<(unsigned)blocks, 128, 0, stream>>>(a);
+    else sddmm_dot_rows_kernel<4, false><<<(unsigned)blocks, 128, 0, stream>>>(a);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
 }
