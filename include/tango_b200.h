@@ -265,6 +265,38 @@ int tango_edge_softmax_bwd(const int32_t *indptr, const int32_t *edge_ids, const
                            int64_t n_block_rows, int64_t n_rows, int h, float zmul, const float *a, const float *da,
                            float *dz, float *dz_absmax, tango_stream_t stream);
 
+/* ---------------------------------------------------------------- multi-GPU exchange over peer memory */
+
+/* None of the entry points of this section has a counterpart in the reference, which is single-GPU.  They serve the
+ * row-partitioned aggregation (every GPU needs the int8 rows of all GPUs): instead of quantizing locally and then
+ * all-gathering, the quantizer stores every 16-byte piece of row r straight into the gathered table of every GPU of
+ * the node, at tables[k] + (row0 + r) * ldq (tables: DEVICE array of n_tables base pointers, peer memory mapped into
+ * this process, e.g. through CUDA IPC; row0 = first row of this rank's shard in the gathered table; ldq a multiple
+ * of 16).  Plain stores over NVLink, no multicast, no loads from peer memory.  Arguments otherwise as for
+ * tango_quantize / tango_quantize_relu_grad.  A tango_peer_sync on the same stream must follow before any GPU reads
+ * its table. */
+int tango_quantize_push(const float *x, int64_t rows, int64_t cols, int64_t ldx, const float *row_scale,
+                        const float *scale, int8_t *const *tables /* device */, int n_tables, int64_t row0,
+                        int64_t ldq, int mode, uint64_t seed, uint64_t call, const uint64_t *step,
+                        tango_stream_t stream);
+int tango_quantize_relu_grad_push(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows, int64_t cols,
+                                  const float *row_scale, const float *scale, int8_t *const *tables /* device */,
+                                  int n_tables, int64_t row0, int64_t ldq, int mode, uint64_t seed, uint64_t call,
+                                  const uint64_t *step, tango_stream_t stream);
+
+/* Lets kernels of the current device store to and load from memory of `peer_device` (cudaDeviceEnablePeerAccess;
+ * already enabled counts as success).  TANGO_EINVAL if the two devices cannot reach each other. */
+int tango_enable_peer_access(int peer_device);
+
+/* Barrier + all-reduce(max) of one non-negative float among the `world` GPUs of a node, in one single-CTA launch.
+ * slots: DEVICE array of `world` pointers, slots[k] = rank k's array of 2 * world 64-bit words (zero-initialised once,
+ * mapped by every rank); round_word: this rank's device word counting the rounds (zero-initialised; all ranks must
+ * call the same number of times); val_in / val_out may be NULL (pure barrier).  On return from the kernel everything
+ * that the other ranks wrote to this GPU's memory before their call is visible to later kernels of this stream.
+ * The wait is bounded (2 s); on expiry *status = TANGO_ETIMEOUT and the kernel returns. */
+int tango_peer_sync(uint64_t *const *slots /* device */, int rank, int world, uint64_t *round_word, const float *val_in,
+                    float *val_out, int *status, tango_stream_t stream);
+
 /* ---------------------------------------------------------------- measurement aid */
 
 /* No counterpart in the reference.  Gathers pseudo-random rows (row_bytes a power of two in [16, 512]) of `table`

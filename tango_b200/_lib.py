@@ -69,6 +69,12 @@ _SIGS = {
     "tango_sddmm_elementwise": ([c_int, P, P, c_int64, P, c_int64, P, c_int64, c_int64, P, P, P, P, P], c_int),
     "tango_gat_edge_softmax": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P], c_int),
     "tango_gat_edge_softmax_bwd": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P, P, P], c_int),
+    "tango_quantize_push": ([P, c_int64, c_int64, c_int64, P, P, P, c_int, c_int64, c_int64, c_int, c_uint64, c_uint64,
+                             P, P], c_int),
+    "tango_quantize_relu_grad_push": ([P, c_int64, P, c_int64, c_int64, c_int64, P, P, P, c_int, c_int64, c_int64, c_int,
+                                       c_uint64, c_uint64, P, P], c_int),
+    "tango_enable_peer_access": ([c_int], c_int),
+    "tango_peer_sync": ([P, c_int, c_int, P, P, P, P, P], c_int),
     "tango_probe_row_gather": ([P, c_int64, c_int64, c_int, c_int, c_int, P, P], c_int64),
     "tango_edge_softmax": ([P, P, P, c_int64, c_int64, P, c_int, c_float, P, P, P], c_int),
     "tango_edge_softmax_bwd": ([P, P, P, c_int64, c_int64, c_int, c_float, P, P, P, P, P], c_int),

@@ -15,7 +15,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libtango_b200.so")
-SOURCES = ["quantize.cu", "spmm.cu", "sddmm.cu", "gat_softmax.cu", "igemm_tcgen05.cu", "probe.cu"]
+SOURCES = ["quantize.cu", "spmm.cu", "sddmm.cu", "gat_softmax.cu", "igemm_tcgen05.cu", "probe.cu", "peer.cu"]
 
 
 def _nvcc() -> str:

@@ -45,13 +45,33 @@ __global__ void __launch_bounds__(256) absmax_kernel(const float *__restrict__ x
 
 // ---------------------------------------------------------------------------------------------- quantize
 
+// Optional destinations of a quantizer launch in a multi-GPU run: instead of (only) the local tensor q, every 16-byte
+// piece of row r is stored at bases[k] + (row0 + r) * ldq + c0 for k < n -- the same place in the gathered table of
+// every GPU of the node (peer memory mapped into this process; plain stores over NVLink).  n == 0: store to q.
+struct PushTargets {
+    int8_t *const *bases;
+    int n;
+    int64_t row0;
+};
+
+__device__ __forceinline__ void store_piece(int8_t *q, const PushTargets &push, int64_t r, int64_t ldq, int64_t c0,
+                                            const uint4 &piece) {
+    if (push.n == 0) {
+        __stcs(reinterpret_cast<uint4 *>(q + r * ldq + c0), piece);
+    } else {
+        for (int k = 0; k < push.n; ++k)
+            __stcs(reinterpret_cast<uint4 *>(push.bases[k] + (push.row0 + r) * ldq + c0), piece);
+    }
+}
+
 // One thread produces 16 consecutive output bytes of one row (a 128-bit store).  LW = floats per input load.
 template <int LW>
 __global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
                                                        int64_t ldx, const float *__restrict__ row_scale,
                                                        const float *__restrict__ scale, int8_t *__restrict__ q,
                                                        int64_t ldq, int mode, uint64_t seed, uint64_t call0,
-    const unsigned long long *__restrict__ step) {
+                                                       const unsigned long long *__restrict__ step,
+                                                       const PushTargets push) {
     const uint64_t call = effective_call(call0, step);
     const float inv = inv_scale(__ldg(scale));
     const int64_t groups = (ldq + 15) >> 4, total = rows * groups;
@@ -100,7 +120,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__
             packed[k >> 2] |= ((uint32_t)qi & 0xffu) << (8 * (k & 3));
         }
         if (c0 + 16 <= ldq) {
-            __stcs(reinterpret_cast<uint4 *>(q + r * ldq + c0), make_uint4(packed[0], packed[1], packed[2], packed[3]));
+            store_piece(q, push, r, ldq, c0, make_uint4(packed[0], packed[1], packed[2], packed[3]));
         } else {  // ragged end of a flat (single-row) tensor
             for (int k = 0; c0 + k < ldq; ++k) q[r * ldq + c0 + k] = (int8_t)(packed[k >> 2] >> (8 * (k & 3)));
         }
@@ -209,32 +229,50 @@ extern "C" int tango_absmax_scale(const float *x, int64_t rows, int64_t cols, in
     return TANGO_OK;
 }
 
-extern "C" int tango_quantize(const float *x, int64_t rows, int64_t cols, int64_t ldx, const float *row_scale,
-                              const float *scale, int8_t *q, int64_t ldq, int mode, uint64_t seed, uint64_t call,
-                              const uint64_t *step_, tango_stream_t stream_) {
+static int launch_quantize(const float *x, int64_t rows, int64_t cols, int64_t ldx, const float *row_scale,
+                           const float *scale, int8_t *q, int64_t ldq, int mode, uint64_t seed, uint64_t call,
+                           const uint64_t *step_, const PushTargets &push, cudaStream_t stream) {
     const unsigned long long *step = reinterpret_cast<const unsigned long long *>(step_);
-    cudaStream_t stream = (cudaStream_t)stream_;
     if (rows < 0 || cols < 0 || ldx < cols || ldq < cols || mode < 0 || mode > 2) return TANGO_EINVAL;
     if (rows == 0 || ldq == 0) return TANGO_OK;
-    if (!x || !q || !scale) return TANGO_EINVAL;
-    if (ldq == cols && ldx == cols && !row_scale) {  // contiguous in and out: one flat row (same flat element index)
+    if (!x || !scale || (push.n == 0 && !q)) return TANGO_EINVAL;
+    if (push.n > 0) {
+        if (!push.bases || push.row0 < 0) return TANGO_EINVAL;
+        if (ldq % 16 != 0) return TANGO_EALIGN;      // every piece of a pushed row is one aligned 128-bit store
+    } else if (ldq == cols && ldx == cols && !row_scale) {  // contiguous in and out: one flat row (same flat index)
         cols = rows * cols; rows = 1; ldx = ldq = cols;
     }
-    if ((ldq % 16 == 0 || rows == 1) && aligned(q, 16)) {
+    if (push.n > 0 || ((ldq % 16 == 0 || rows == 1) && aligned(q, 16))) {
         const int lw = (aligned(x, 16) && (rows == 1 || ldx % 4 == 0)) ? 4 : (aligned(x, 8) && (rows == 1 || ldx % 2 == 0)) ? 2 : 1;
         const int grid = stream_grid(rows * ceil_div(ldq, 16), 256, 16);
         if (lw == 4)
-            quantize_kernel<4><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step);
+            quantize_kernel<4><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step, push);
         else if (lw == 2)
-            quantize_kernel<2><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step);
+            quantize_kernel<2><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step, push);
         else
-            quantize_kernel<1><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step);
+            quantize_kernel<1><<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step, push);
     } else {
         const int grid = stream_grid(rows * ldq, 256, 8);
         quantize_scalar_kernel<<<grid, 256, 0, stream>>>(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step);
     }
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
+}
+
+extern "C" int tango_quantize(const float *x, int64_t rows, int64_t cols, int64_t ldx, const float *row_scale,
+                              const float *scale, int8_t *q, int64_t ldq, int mode, uint64_t seed, uint64_t call,
+                              const uint64_t *step, tango_stream_t stream) {
+    return launch_quantize(x, rows, cols, ldx, row_scale, scale, q, ldq, mode, seed, call, step, PushTargets{nullptr, 0, 0},
+                           (cudaStream_t)stream);
+}
+
+extern "C" int tango_quantize_push(const float *x, int64_t rows, int64_t cols, int64_t ldx, const float *row_scale,
+                                   const float *scale, int8_t *const *tables, int n_tables, int64_t row0, int64_t ldq,
+                                   int mode, uint64_t seed, uint64_t call, const uint64_t *step,
+                                   tango_stream_t stream) {
+    if (n_tables < 1 || n_tables > 64) return TANGO_EINVAL;
+    return launch_quantize(x, rows, cols, ldx, row_scale, scale, nullptr, ldq, mode, seed, call, step,
+                           PushTargets{tables, n_tables, row0}, (cudaStream_t)stream);
 }
 
 extern "C" int tango_quantize_transpose(const float *x, int64_t nrow, int64_t ncol, const float *scale, int8_t *out,
@@ -344,7 +382,8 @@ __global__ void __launch_bounds__(256) relu_grad_quant_kernel(const float *__res
                                                               int64_t cols, const float *__restrict__ row_scale,
                                                               const float *__restrict__ scale, int8_t *__restrict__ q,
                                                               int64_t ldq, int mode, uint64_t seed, uint64_t call0,
-    const unsigned long long *__restrict__ step) {
+                                                              const unsigned long long *__restrict__ step,
+                                                              const PushTargets push) {
     const uint64_t call = effective_call(call0, step);
     const float inv = inv_scale(__ldg(scale));
     const int64_t groups = ldq >> 4, total = rows * groups;   // ldq % 16 == 0
@@ -378,7 +417,7 @@ __global__ void __launch_bounds__(256) relu_grad_quant_kernel(const float *__res
             const int qi = (c0 + k < cols) ? round_to_i8(t, mode, u) : 0;
             packed[k >> 2] |= ((uint32_t)qi & 0xffu) << (8 * (k & 3));
         }
-        __stcs(reinterpret_cast<uint4 *>(q + r * ldq + c0), make_uint4(packed[0], packed[1], packed[2], packed[3]));
+        store_piece(q, push, r, ldq, c0, make_uint4(packed[0], packed[1], packed[2], packed[3]));
     }
 }
 
@@ -422,20 +461,38 @@ extern "C" int tango_relu_grad_stats(const float *g, int64_t ldg, const float *y
     return TANGO_OK;
 }
 
-extern "C" int tango_quantize_relu_grad(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows,
-                                        int64_t cols, const float *row_scale, const float *scale, int8_t *q,
-                                        int64_t ldq, int mode, uint64_t seed, uint64_t call, const uint64_t *step_,
-                                        tango_stream_t stream_) {
+static int launch_relu_grad_quant(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows, int64_t cols,
+                                  const float *row_scale, const float *scale, int8_t *q, int64_t ldq, int mode,
+                                  uint64_t seed, uint64_t call, const uint64_t *step_, const PushTargets &push,
+                                  cudaStream_t stream) {
     const unsigned long long *step = reinterpret_cast<const unsigned long long *>(step_);
-    cudaStream_t stream = (cudaStream_t)stream_;
     if (rows < 0 || cols < 0 || ldg < cols || ldy < cols || ldq < cols || mode < 0 || mode > 2) return TANGO_EINVAL;
     if (rows == 0 || ldq == 0) return TANGO_OK;
-    if (!g || !y || !q || !scale) return TANGO_EINVAL;
-    if (ldq % 16 != 0 || !aligned(q, 16)) return TANGO_EALIGN;
+    if (!g || !y || !scale || (push.n == 0 && !q)) return TANGO_EINVAL;
+    if (push.n > 0 && (!push.bases || push.row0 < 0)) return TANGO_EINVAL;
+    if (ldq % 16 != 0 || (push.n == 0 && !aligned(q, 16))) return TANGO_EALIGN;
     const bool vec = ldg % 4 == 0 && ldy % 4 == 0 && aligned(g, 16) && aligned(y, 16);
     const int grid = stream_grid(rows * (ldq / 16), 256, 16);
-    if (vec) relu_grad_quant_kernel<true><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call, step);
-    else relu_grad_quant_kernel<false><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call, step);
+    if (vec) relu_grad_quant_kernel<true><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call, step, push);
+    else relu_grad_quant_kernel<false><<<grid, 256, 0, stream>>>(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call, step, push);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
+}
+
+extern "C" int tango_quantize_relu_grad(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows,
+                                        int64_t cols, const float *row_scale, const float *scale, int8_t *q,
+                                        int64_t ldq, int mode, uint64_t seed, uint64_t call, const uint64_t *step,
+                                        tango_stream_t stream) {
+    return launch_relu_grad_quant(g, ldg, y, ldy, rows, cols, row_scale, scale, q, ldq, mode, seed, call, step,
+                                  PushTargets{nullptr, 0, 0}, (cudaStream_t)stream);
+}
+
+extern "C" int tango_quantize_relu_grad_push(const float *g, int64_t ldg, const float *y, int64_t ldy, int64_t rows,
+                                             int64_t cols, const float *row_scale, const float *scale,
+                                             int8_t *const *tables, int n_tables, int64_t row0, int64_t ldq, int mode,
+                                             uint64_t seed, uint64_t call, const uint64_t *step,
+                                             tango_stream_t stream) {
+    if (n_tables < 1 || n_tables > 64) return TANGO_EINVAL;
+    return launch_relu_grad_quant(g, ldg, y, ldy, rows, cols, row_scale, scale, nullptr, ldq, mode, seed, call, step,
+                                  PushTargets{tables, n_tables, row0}, (cudaStream_t)stream);
 }

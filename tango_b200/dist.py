@@ -45,7 +45,8 @@ def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_row
 class DistGraph:
     """Rank-local view of a graph that every rank holds (or can rebuild from the same seed)."""
 
-    def __init__(self, g: Graph, rank: int, world: int, balance: str = "dealt", scale_mode: str = "global"):
+    def __init__(self, g: Graph, rank: int, world: int, balance: str = "dealt", scale_mode: str = "global",
+                 transport: str = "nccl"):
         """balance='dealt': nodes sorted by in-degree + out-degree are dealt round-robin to the ranks (equal rows,
         nearly equal edges even on power-law graphs, no padding of the gathered buffer);
         balance='cyclic': node v lives on rank v % world;
@@ -53,8 +54,14 @@ class DistGraph:
         work); balance='rows': contiguous blocks of equal row counts.
         scale_mode='global': the ranks agree on one quantisation scale per aggregated tensor (all-reduce max of one
         float), which makes the result bit-identical to the single-GPU run; scale_mode='shard': every shard keeps its
-        own scale and the aggregation kernel applies the scale of the shard a neighbour came from."""
+        own scale and the aggregation kernel applies the scale of the shard a neighbour came from.
+        transport='nccl': all-gather / all-reduce through torch.distributed; transport='peer' (global scale mode, one
+        node, CUDA devices): the quantizers store straight into every GPU's gathered table over NVLink and the ranks
+        meet in a one-CTA rendezvous kernel (tango_b200.peer) -- no library collective on the data path."""
         assert scale_mode in ("global", "shard")
+        assert transport in ("nccl", "peer")
+        assert transport == "nccl" or scale_mode == "global", "the peer transport implements the global scale mode"
+        self.peer = None
         n = g.num_nodes()
         self.rank, self.world, self.n_total, self.scale_mode = rank, world, n, scale_mode
         csc, csr = g.adj_csc, g.adj_csr
@@ -74,6 +81,9 @@ class DistGraph:
         self.r0, self.r1 = self.fwd.r0, self.fwd.r1
         self.in_norm = g.in_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
         self.out_norm = g.out_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
+        if transport == "peer" and world > 1:
+            from .peer import PeerTransport
+            self.peer = PeerTransport(rank, world, self.in_norm.device)
 
 
 def _padded_storage(q: torch.Tensor) -> torch.Tensor:
@@ -109,16 +119,44 @@ def _aggregate(dg: DistGraph, part: RowPartition, x_local: torch.Tensor, scale_l
     if scale_local is None:
         scale_local = K._get_scale(x_local, in_row_scale)
     scale_local = _agree_on_scale(dg, scale_local)
-    q = K.alloc_int8(x_local.shape, x_local.device)
     call = K.next_call() if mode == K.ROUND_STOCHASTIC else 0
+    if dg.peer is not None:
+        f = x_local.shape[1]
+        table, ptrs, ld = _peer_table(dg, part, f)
+        dg.peer.quantize_push(x_local, scale_local, ptrs, dg.rank * dg.shard_rows, ld, mode, seed, call, in_row_scale)
+        dg.peer.barrier()
+        return _spmm_gathered(dg, part, table, scale_local, f, row_scale, bias, relu)
+    q = K.alloc_int8(x_local.shape, x_local.device)
     K._quantize_into(q, x_local, scale_local, mode, seed, call, in_row_scale)
     return _aggregate_quantized(dg, part, q, scale_local, x_local.shape[1], row_scale, bias, relu)
+
+
+def _peer_table(dg: DistGraph, part: RowPartition, f: int):
+    """(this rank's gathered int8 table for aggregations of width f over `part`, every rank's table address, ld)."""
+    ld = (f + 15) // 16 * 16
+    table, ptrs = dg.peer.table(("fwd" if part is dg.fwd else "bwd", ld), dg.world * dg.shard_rows, ld)
+    return table, ptrs, ld
+
+
+def _spmm_gathered(dg: DistGraph, part: RowPartition, q_all: torch.Tensor, scales: torch.Tensor, f: int,
+                   row_scale=None, bias=None, relu=False):
+    """Aggregates this rank's rows from the gathered int8 table (one scale, or one per shard in shard mode)."""
+    from . import kernels as K
+    out = torch.empty((dg.n_local, f), dtype=torch.float32, device=q_all.device)
+    feats = q_all[:, :f] if q_all.shape[1] != f else q_all
+    if dg.scale_mode == "global":
+        K._csr_spmm(out, part.indptr_flat, part.indices, feats, scales, part.schedule_flat, 1, row_scale, bias, relu)
+    else:
+        K._csr_spmm(out, part.indptr, part.indices, feats, scales, part.schedule, dg.world, row_scale, bias, relu)
+    return out
 
 
 def _agree_on_scale(dg: DistGraph, scale_local: torch.Tensor) -> torch.Tensor:
     """global scale mode: the largest local scale becomes everybody's scale (one-float all-reduce)."""
     if dg.scale_mode != "global":
         return scale_local
+    if dg.peer is not None:
+        return dg.peer.max_scalar(scale_local)
     s = scale_local.clone()
     dist.all_reduce(s, op=dist.ReduceOp.MAX)
     return s
@@ -130,14 +168,7 @@ def _aggregate_quantized(dg: DistGraph, part: RowPartition, q: torch.Tensor, sca
     from . import kernels as K
     shared = dg.scale_mode == "global"
     q_all, scales = all_gather_quantized(_padded_storage(q), scale_local, dg.shard_rows, gather_scales=not shared)
-    out = torch.empty((dg.n_local, f), dtype=torch.float32, device=q.device)
-    feats = q_all[:, :f] if q_all.shape[1] != f else q_all
-    if shared:
-        K._csr_spmm(out, part.indptr_flat, part.indices, feats, scale_local, part.schedule_flat, 1, row_scale, bias,
-                    relu)
-    else:
-        K._csr_spmm(out, part.indptr, part.indices, feats, scales, part.schedule, dg.world, row_scale, bias, relu)
-    return out
+    return _spmm_gathered(dg, part, q_all, scale_local if shared else scales, f, row_scale, bias, relu)
 
 
 class _dist_gcn_conv_fused(Function):
@@ -153,9 +184,7 @@ class _dist_gcn_conv_fused(Function):
         if mode_f == K.ROUND_STOCHASTIC:
             K.next_call()
         X = X.contiguous()
-        sX, sW = K._get_scale(X, dg.out_norm), K._get_scale(W)
-        if dg.scale_mode == "global":
-            dist.all_reduce(sX, op=dist.ReduceOp.MAX)
+        sX, sW = _agree_on_scale(dg, K._get_scale(X, dg.out_norm)), K._get_scale(W)
         Xq, Wq = K.alloc_int8(X.shape, X.device), K.alloc_int8(W.shape, X.device)
         H = torch.empty((X.shape[0], W.shape[0]), dtype=torch.float32, device=X.device)
         sH = torch.zeros(1, dtype=torch.float32, device=X.device)
@@ -177,15 +206,21 @@ class _dist_gcn_conv_fused(Function):
             call = K.next_call() if mode_q == K.ROUND_STOCHASTIC else 0
             s_loc, db = K.relu_grad_stats(d_out, out, dg.in_norm, want_db)
             s_loc = _agree_on_scale(dg, s_loc)
-            dZq = K.relu_grad_quant(d_out, out, dg.in_norm, s_loc, mode_q, seed, call)
-            dH = _aggregate_quantized(dg, dg.bwd, dZq, s_loc, d_out.shape[1])
+            if dg.peer is not None:
+                f = d_out.shape[1]
+                table, ptrs, ld = _peer_table(dg, dg.bwd, f)
+                dg.peer.relu_grad_quantize_push(d_out, out, s_loc, ptrs, dg.rank * dg.shard_rows, ld, mode_q, seed,
+                                                call, dg.in_norm)
+                dg.peer.barrier()
+                dH = _spmm_gathered(dg, dg.bwd, table, s_loc, f)
+            else:
+                dZq = K.relu_grad_quant(d_out, out, dg.in_norm, s_loc, mode_q, seed, call)
+                dH = _aggregate_quantized(dg, dg.bwd, dZq, s_loc, d_out.shape[1])
         else:
             g1 = d_out.contiguous()
             db = g1.sum(0) if want_db else None
             dH = _aggregate(dg, dg.bwd, g1, None, None, None, False, in_row_scale=dg.in_norm)
-        sdH = K._get_scale(dH)
-        if dg.scale_mode == "global":
-            dist.all_reduce(sdH, op=dist.ReduceOp.MAX)
+        sdH = _agree_on_scale(dg, K._get_scale(dH))
         dHq, _ = K.quantize(dH, sdH, mode=mode_q, seed=seed)
         dX, dW = K.QGEMM_backward(dHq, Xq, Wq, sdH, sX, sW, ctx.needs_input_grad[1], ctx.needs_input_grad[2],
                                   dx_row_scale=dg.out_norm)

@@ -16,7 +16,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out_dir, balance, scale_mode):
+def _worker(rank, world, port, out_dir, balance, scale_mode, transport="nccl"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     import torch.nn.functional as F
@@ -27,7 +27,7 @@ def _worker(rank, world, port, out_dir, balance, scale_mode):
     from tango_b200.graph import rmat_graph
     n = 5003
     g = rmat_graph(n, 120000, 17, device=dev)
-    dg = DistGraph(g, rank, world, balance=balance, scale_mode=scale_mode)
+    dg = DistGraph(g, rank, world, balance=balance, scale_mode=scale_mode, transport=transport)
     torch.manual_seed(4)
     model = DistGCN(dg, 100, 32, 7, 1).to(dev)
     gen = torch.Generator().manual_seed(9)
@@ -40,14 +40,17 @@ def _worker(rank, world, port, out_dir, balance, scale_mode):
     lt = loss.detach().clone()
     dist.all_reduce(lt)
     torch.save({"logits": logits.detach().cpu(), "ids": dg.local_ids.cpu(), "loss": lt.cpu(),
-                "grads": [p.grad.cpu() for p in model.parameters()]}, os.path.join(out_dir, f"r{rank}.pt"))
+                "grads": [p.grad.cpu() for p in model.parameters()],
+                "peer_status": dg.peer.status() if dg.peer is not None else 0}, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("balance,scale_mode", [("dealt", "global"), ("nnz", "global"), ("rows", "shard"),
-                                                ("dealt", "shard"), ("cyclic", "global")])
-def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode):
+@pytest.mark.parametrize("balance,scale_mode,transport", [("dealt", "global", "nccl"), ("nnz", "global", "nccl"),
+                                                          ("rows", "shard", "nccl"), ("dealt", "shard", "nccl"),
+                                                          ("cyclic", "global", "nccl"), ("dealt", "global", "peer"),
+                                                          ("nnz", "global", "peer")])
+def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.nn.functional as F
@@ -55,7 +58,8 @@ def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode):
     from tango_b200.gnn import GCN
     from tango_b200.graph import rmat_graph
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), balance, scale_mode), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), balance, scale_mode, transport), nprocs=world,
+             join=True)
     n = 5003
     g = rmat_graph(n, 120000, 17, device="cuda")
     T.graph_preprocess(g)
@@ -68,6 +72,7 @@ def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode):
     loss = F.cross_entropy(logits, y)
     loss.backward()
     parts = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
+    assert all(p["peer_status"] == 0 for p in parts)          # no rendezvous wait expired
     ref = logits.detach().cpu()
     got = torch.empty_like(ref)
     for p in parts:
