@@ -284,6 +284,16 @@ int tango_quantize_relu_grad_push(const float *g, int64_t ldg, const float *y, i
                                   int n_tables, int64_t row0, int64_t ldq, int mode, uint64_t seed, uint64_t call,
                                   const uint64_t *step, tango_stream_t stream);
 
+/* Set-up helpers for buffers that the other processes of the node map (host side, once per buffer; the operator
+ * entry points themselves still never allocate).  tango_peer_alloc: cudaMalloc + zero fill on the current device and
+ * the 64-byte CUDA IPC handle of the allocation; tango_peer_open: maps another process's buffer for kernels of the
+ * CURRENT device (peer access is enabled on demand) and returns its address in this process; tango_peer_close /
+ * tango_peer_free undo them. */
+int tango_peer_alloc(int64_t bytes, void **ptr, unsigned char *handle64);
+int tango_peer_open(const unsigned char *handle64, void **ptr);
+int tango_peer_close(void *ptr);
+int tango_peer_free(void *ptr);
+
 /* Lets kernels of the current device store to and load from memory of `peer_device` (cudaDeviceEnablePeerAccess;
  * already enabled counts as success).  TANGO_EINVAL if the two devices cannot reach each other. */
 int tango_enable_peer_access(int peer_device);

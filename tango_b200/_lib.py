@@ -73,6 +73,10 @@ _SIGS = {
                              P, P], c_int),
     "tango_quantize_relu_grad_push": ([P, c_int64, P, c_int64, c_int64, c_int64, P, P, P, c_int, c_int64, c_int64, c_int,
                                        c_uint64, c_uint64, P, P], c_int),
+    "tango_peer_alloc": ([c_int64, P, P], c_int),
+    "tango_peer_open": ([P, P], c_int),
+    "tango_peer_close": ([P], c_int),
+    "tango_peer_free": ([P], c_int),
     "tango_enable_peer_access": ([c_int], c_int),
     "tango_peer_sync": ([P, c_int, c_int, P, P, P, P, P], c_int),
     "tango_probe_row_gather": ([P, c_int64, c_int64, c_int, c_int, c_int, P, P], c_int64),

@@ -11,6 +11,8 @@
 //
 // The wait is bounded (two seconds of %globaltimer): on expiry the kernel stores TANGO_ETIMEOUT in the status word and
 // returns, so a missing peer can never hang the GPU.
+#include <cstring>
+
 #include "common.cuh"
 
 namespace tango {
@@ -68,6 +70,50 @@ __global__ void __launch_bounds__(64) peer_sync_kernel(unsigned long long *const
 }  // namespace tango
 
 using namespace tango;
+
+// ---- set-up helpers (host side, once per buffer): memory that other processes of the node can map.
+// The buffer is a plain cudaMalloc allocation, so its address is the base address cudaIpcGetMemHandle wants, and a
+// peer opens the handle with ITS OWN device current, which maps the memory for kernels of that device (with peer
+// access enabled on demand).
+
+extern "C" int tango_peer_alloc(int64_t bytes, void **ptr, unsigned char *handle64) {
+    if (bytes <= 0 || !ptr || !handle64) return TANGO_EINVAL;
+    void *p = nullptr;
+    TANGO_CUDA_TRY(cudaMalloc(&p, (size_t)bytes));
+    cudaError_t e = cudaMemset(p, 0, (size_t)bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        TANGO_CUDA_TRY(e);
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memcpy(handle64, &h, 64);
+    *ptr = p;
+    return TANGO_OK;
+}
+
+extern "C" int tango_peer_open(const unsigned char *handle64, void **ptr) {
+    if (!handle64 || !ptr) return TANGO_EINVAL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void *p = nullptr;
+    TANGO_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr = p;
+    return TANGO_OK;
+}
+
+extern "C" int tango_peer_close(void *ptr) {
+    if (!ptr) return TANGO_OK;
+    TANGO_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+    return TANGO_OK;
+}
+
+extern "C" int tango_peer_free(void *ptr) {
+    if (!ptr) return TANGO_OK;
+    TANGO_CUDA_TRY(cudaFree(ptr));
+    return TANGO_OK;
+}
 
 extern "C" int tango_enable_peer_access(int peer_device) {
     int cur = -1;

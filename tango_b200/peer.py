@@ -1,7 +1,8 @@
 """Exchange between the GPUs of one node over peer memory instead of NCCL (no counterpart in the reference).
 
-Every rank allocates its buffers with the PyTorch allocator, publishes CUDA IPC handles through the process group
-(host side, once), and maps the buffers of the other ranks.  After that the data path uses no library call:
+Every rank allocates its shared buffers through the library (plain cudaMalloc), publishes their CUDA IPC handles
+through the process group (host side, once), and maps the buffers of the other ranks with its own device current.
+After that the data path uses no library call:
 
   * `max_scalar`    -- barrier + all-reduce(max) of one float in one tiny kernel (`tango_peer_sync`),
   * `quantize_push` -- the quantizer stores its int8 rows straight into the gathered table of every GPU
@@ -12,6 +13,7 @@ Waits on other GPUs are bounded on the device; `status()` reports an expired wai
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -21,15 +23,49 @@ from . import config
 from ._lib import check, lib
 
 
-def _share(t: torch.Tensor):
-    """Picklable CUDA IPC description of the storage behind `t`."""
-    return t.untyped_storage()._share_cuda_()
+class _RawCuda:
+    """Exposes a raw device allocation through __cuda_array_interface__ so that torch can view it without a copy."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|i1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
 
 
-def _open(handle, dtype: torch.dtype) -> torch.Tensor:
-    """Flat tensor over a peer's storage, mapped into this process."""
-    storage = torch.UntypedStorage._new_shared_cuda(*handle)
-    return torch.empty(0, dtype=dtype, device=storage.device).set_(storage)
+class SharedBuffer:
+    """`nbytes` zero-filled bytes on this rank's GPU that every rank of the group maps (a collective, host side):
+    `local` is a torch int8 view of this rank's buffer, `ptrs[r]` the address of rank r's buffer in THIS process."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, device: torch.device, group=None):
+        self.rank, self.device = rank, device
+        ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(device):
+            check(lib.tango_peer_alloc(nbytes, ctypes.byref(ptr), handle), "peer_alloc")
+            torch.cuda.synchronize(device)
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self.ptrs = []
+            for r in range(world):
+                if r == rank:
+                    self.ptrs.append(ptr.value)
+                    continue
+                remote = ctypes.c_void_p()
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
+                check(lib.tango_peer_open(buf, ctypes.byref(remote)), "peer_open")   # maps it for THIS device
+                self.ptrs.append(remote.value)
+        self._own = ptr.value
+        self.local = torch.as_tensor(_RawCuda(ptr.value, nbytes), device=device)
+        self.ptrs_dev = torch.tensor(self.ptrs, dtype=torch.int64, device=device)
+        dist.barrier(group=group)                                 # everybody has mapped everything
+
+    def release(self):
+        """Unmaps the peers' buffers and frees the own one (call on every rank, after a barrier)."""
+        with torch.cuda.device(self.device):
+            for r, p in enumerate(self.ptrs):
+                if r != self.rank and p:
+                    lib.tango_peer_close(p)
+            if self._own:
+                lib.tango_peer_free(self._own)
+        self.ptrs, self._own, self.local = [], 0, None
 
 
 class PeerTransport:
@@ -38,25 +74,12 @@ class PeerTransport:
         self.rank, self.world, self.device, self.group = rank, world, device, group
         self._stream = lambda: torch.cuda.current_stream(device).cuda_stream
         # rendezvous words: 2 banks of `world` 64-bit words on every rank, written by everybody
-        self._slots = torch.zeros(2 * world, dtype=torch.int64, device=device)
+        self._slots = SharedBuffer(2 * world * 8, rank, world, device, group)
+        self._slot_ptrs = self._slots.ptrs_dev
         self._round = torch.zeros(1, dtype=torch.int64, device=device)
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
-        self._peer_slots = self._exchange(self._slots, torch.int64)
-        self._slot_ptrs = torch.tensor([t.data_ptr() for t in self._peer_slots], dtype=torch.int64, device=device)
-        self._tables: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor, list]] = {}
+        self._tables: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor, SharedBuffer]] = {}
         torch.cuda.synchronize(device)
-        dist.barrier(group=group)
-
-    def _exchange(self, local: torch.Tensor, dtype: torch.dtype):
-        """Publishes `local` and returns the list of every rank's tensor (own entry = `local` itself)."""
-        handles = [None] * self.world
-        dist.all_gather_object(handles, _share(local), group=self.group)
-        tensors = [local if r == self.rank else _open(handles[r], dtype) for r in range(self.world)]
-        with torch.cuda.device(self.device):
-            for t in tensors:                      # kernels of this device will address the peers' memory directly
-                if t.device != self.device:
-                    check(lib.tango_enable_peer_access(t.device.index), "enable_peer_access")
-        return tensors
 
     # ------------------------------------------------------------------------------------------------ rendezvous
     def max_scalar(self, value: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -85,12 +108,8 @@ class PeerTransport:
         Returns (local table, device array of every rank's table address)."""
         ent = self._tables.get(key)
         if ent is None:
-            local = torch.zeros((rows, ld), dtype=torch.int8, device=self.device)
-            peers = self._exchange(local, torch.int8)
-            ptrs = torch.tensor([t.data_ptr() for t in peers], dtype=torch.int64, device=self.device)
-            torch.cuda.synchronize(self.device)
-            dist.barrier(group=self.group)
-            ent = (local, ptrs, peers)
+            buf = SharedBuffer(rows * ld, self.rank, self.world, self.device, self.group)
+            ent = (buf.local.view(rows, ld), buf.ptrs_dev, buf)
             self._tables[key] = ent
         assert ent[0].shape == (rows, ld), "a gathered table keeps its shape"
         return ent[0], ent[1]
