@@ -411,7 +411,7 @@ def run_ours(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "s8", "data": "synthetic",
             "config": {"workload": name, "nodes": n, "edges": n_edges, "layers": f"{in_feats}-{hidden}-{classes}",
-                       "rounding": args.rounding, "parallelism": f"row-partition x{world}", "scale_mode": args.scale_mode if world > 1 else "single", "balance": args.balance if world > 1 else "single", "transport": args.transport if world > 1 else "single",
+                       "rounding": args.rounding, "parallelism": f"row-partition x{world}", "scale_mode": args.scale_mode if world > 1 else "single", "balance": args.balance if world > 1 else "single", "transport": dg.transport if world > 1 else "single",
                        "cuda_graph": graph is not None,
                        "timing": "CUDA events, inputs larger than L2 (no flush)"},
             "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": (h_feats.numel() * 4 + h_labels.numel() * 8),
@@ -626,7 +626,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gcn_c5", choices=sorted(WORKLOADS))
     ap.add_argument("--rounding", default="reference", choices=["reference", "nearest", "stochastic"])
-    ap.add_argument("--transport", default="nccl", choices=["nccl", "peer"],
+    ap.add_argument("--transport", default="auto", choices=["auto", "nccl", "peer"],
                     help="multi-GPU exchange: NCCL collectives, or stores into peer memory + rendezvous kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale-mode", default="global", choices=["global", "shard"],

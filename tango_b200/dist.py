@@ -57,9 +57,15 @@ class DistGraph:
         own scale and the aggregation kernel applies the scale of the shard a neighbour came from.
         transport='nccl': all-gather / all-reduce through torch.distributed; transport='peer' (global scale mode, one
         node, CUDA devices): the quantizers store straight into every GPU's gathered table over NVLink and the ranks
-        meet in a one-CTA rendezvous kernel (tango_b200.peer) -- no library collective on the data path."""
+        meet in a one-CTA rendezvous kernel (tango_b200.peer) -- no library collective on the data path;
+        transport='auto': 'peer' when it applies and its set-up succeeds on every rank, else 'nccl'."""
         assert scale_mode in ("global", "shard")
-        assert transport in ("nccl", "peer")
+        assert transport in ("nccl", "peer", "auto")
+        if transport == "auto":      # peer memory where it applies, NCCL otherwise (decided alike on all ranks)
+            transport = "peer" if (scale_mode == "global" and world > 1 and g.device.type == "cuda") else "nccl"
+            self._fallback = True
+        else:
+            self._fallback = False
         assert transport == "nccl" or scale_mode == "global", "the peer transport implements the global scale mode"
         self.peer = None
         n = g.num_nodes()
@@ -83,7 +89,13 @@ class DistGraph:
         self.out_norm = g.out_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
         if transport == "peer" and world > 1:
             from .peer import PeerTransport
-            self.peer = PeerTransport(rank, world, self.in_norm.device)
+            try:
+                self.peer = PeerTransport(rank, world, self.in_norm.device)
+            except RuntimeError:
+                if not self._fallback:
+                    raise
+                self.peer = None     # the set-up fails on all ranks or on none, so all of them fall back to NCCL
+        self.transport = "peer" if self.peer is not None else "nccl"
 
 
 def _padded_storage(q: torch.Tensor) -> torch.Tensor:

@@ -37,35 +37,50 @@ class SharedBuffer:
 
     def __init__(self, nbytes: int, rank: int, world: int, device: torch.device, group=None):
         self.rank, self.device = rank, device
+        self.ptrs, self._own, self.local = [None] * world, 0, None
         ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        err = None
         with torch.cuda.device(device):
-            check(lib.tango_peer_alloc(nbytes, ctypes.byref(ptr), handle), "peer_alloc")
-            torch.cuda.synchronize(device)
+            try:
+                check(lib.tango_peer_alloc(nbytes, ctypes.byref(ptr), handle), "peer_alloc")
+                self._own = ptr.value
+                self.ptrs[rank] = ptr.value
+                torch.cuda.synchronize(device)
+            except Exception as exc:                              # reported below, on every rank alike
+                err = exc
             handles = [None] * world
-            dist.all_gather_object(handles, bytes(handle), group=group)
-            self.ptrs = []
-            for r in range(world):
-                if r == rank:
-                    self.ptrs.append(ptr.value)
-                    continue
-                remote = ctypes.c_void_p()
-                buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
-                check(lib.tango_peer_open(buf, ctypes.byref(remote)), "peer_open")   # maps it for THIS device
-                self.ptrs.append(remote.value)
-        self._own = ptr.value
+            dist.all_gather_object(handles, bytes(handle) if err is None else None, group=group)
+            if err is None and all(h is not None for h in handles):
+                try:
+                    for r in range(world):
+                        if r == rank:
+                            continue
+                        remote = ctypes.c_void_p()
+                        buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
+                        check(lib.tango_peer_open(buf, ctypes.byref(remote)), "peer_open")   # maps it for THIS device
+                        self.ptrs[r] = remote.value
+                except Exception as exc:
+                    err = exc
+            # every rank learns whether every rank succeeded, so that all of them raise (or none does)
+            oks = [None] * world
+            dist.all_gather_object(oks, err is None and all(p is not None for p in self.ptrs), group=group)
+        if not all(oks):
+            self.release()
+            raise RuntimeError(f"peer-memory set-up failed on rank(s) {[r for r, ok in enumerate(oks) if not ok]}"
+                               + (f": {err}" if err is not None else ""))
         self.local = torch.as_tensor(_RawCuda(ptr.value, nbytes), device=device)
         self.ptrs_dev = torch.tensor(self.ptrs, dtype=torch.int64, device=device)
-        dist.barrier(group=group)                                 # everybody has mapped everything
 
     def release(self):
         """Unmaps the peers' buffers and frees the own one (call on every rank, after a barrier)."""
         with torch.cuda.device(self.device):
+            self.local = None
             for r, p in enumerate(self.ptrs):
                 if r != self.rank and p:
                     lib.tango_peer_close(p)
             if self._own:
                 lib.tango_peer_free(self._own)
-        self.ptrs, self._own, self.local = [], 0, None
+        self.ptrs, self._own = [], 0
 
 
 class PeerTransport:
