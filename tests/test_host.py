@@ -143,6 +143,10 @@ def _worker(rank, world, port, out_dir):
                         q_all[:, :f].numpy(), scales.numpy(), shard_rows=part.shard_rows)
     np.save(os.path.join(out_dir, f"out{rank}.npy"), out)
     np.save(os.path.join(out_dir, f"scales{rank}.npy"), scales.numpy())
+    # transport selection is a host-side decision taken alike on all ranks: no CUDA device -> library collectives
+    from tango_b200.dist import DistGraph
+    dg = DistGraph(g, rank, world, transport="auto")
+    assert dg.transport == "nccl" and dg.peer is None and dg.n_local == dg.fwd.n_local
     dist.destroy_process_group()
 
 
