@@ -5,6 +5,10 @@ the adjacency (forward aggregation) and the CSR rows (backward aggregation), bot
 data-path exchange is one all-gather per aggregation of the int8-quantized feature shard plus its fp32 scale; the
 aggregation kernel then applies the scale of the shard each neighbour came from.  Weight gradients are summed with
 an all-reduce after the backward pass.
+
+Two transports carry that exchange: torch.distributed collectives (NCCL on GPUs, gloo on CPU), or -- on the GPUs of
+one node, `transport="peer"` -- quantizer kernels that store into every GPU's gathered table over NVLink plus a
+one-CTA rendezvous kernel for the barrier and the scale agreement (tango_b200.peer).
 """
 from __future__ import annotations
 
