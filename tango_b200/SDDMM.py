@@ -2,10 +2,10 @@
 which the reference's HGT and link-prediction scripts call (evaluation/test_HGT.py:58) but never define."""
 from __future__ import annotations
 
-import torch
 from torch.autograd.function import Function, once_differentiable
 
 from . import config
+from .kernels import *  # noqa: F401,F403  (the reference's module re-exports its kernels the same way)
 from .kernels import incidence_SPMM, mySDDMM_int8, quantize, spmm_u_mul_e_int8
 
 

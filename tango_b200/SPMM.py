@@ -1,12 +1,11 @@
 """Quantized aggregation operators: the autograd surface of the reference's cuda/SPMM.py."""
 from __future__ import annotations
 
-import torch
 from torch.autograd.function import Function, once_differentiable
 
 from . import config
-from .kernels import (ROUND_NEAREST, cuda_kernels, csr_SPMM, multi_cusparse_SPMM, mySDDMM_int8, quantize,
-                      spmm_u_mul_e_int8)
+from .kernels import *  # noqa: F401,F403  (the reference's module re-exports its kernels the same way)
+from .kernels import cuda_kernels, csr_SPMM, mySDDMM_int8, quantize, spmm_u_mul_e_int8
 
 
 def _q(t, scale=None, align=16):
