@@ -15,20 +15,35 @@ __global__ void __launch_bounds__(256) absmax_kernel(const float *__restrict__ x
                                                      float *__restrict__ scale) {
     float m = 0.f;
     const int64_t cv = cols / LW, total = rows * cv;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / cv, c = (i - r * cv) * LW;
-        float t;
-        if (LW == 4) {
-            const float4 v = __ldcs(reinterpret_cast<const float4 *>(x + r * ld + c));
-            t = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-        } else if (LW == 2) {
-            const float2 v = __ldcs(reinterpret_cast<const float2 *>(x + r * ld + c));
-            t = fmaxf(fabsf(v.x), fabsf(v.y));
-        } else {
-            t = fabsf(x[r * ld + c]);
+    // four independent loads in flight per thread (an 8-byte load per trip alone leaves HBM half idle)
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+        float t[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t i = i0 + u * stride;
+            t[u] = 0.f;
+            if (i < total) {
+                int64_t r, c;
+                if (total <= 0x7fffffff) {      // 32-bit division where it suffices
+                    const uint32_t r32 = (uint32_t)i / (uint32_t)cv;
+                    r = r32; c = (int64_t)((uint32_t)i - r32 * (uint32_t)cv) * LW;
+                } else {
+                    r = i / cv; c = (i - r * cv) * LW;
+                }
+                if (LW == 4) {
+                    const float4 v = __ldcs(reinterpret_cast<const float4 *>(x + r * ld + c));
+                    t[u] = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+                } else if (LW == 2) {
+                    const float2 v = __ldcs(reinterpret_cast<const float2 *>(x + r * ld + c));
+                    t[u] = fmaxf(fabsf(v.x), fabsf(v.y));
+                } else {
+                    t[u] = fabsf(x[r * ld + c]);
+                }
+                if (row_scale) t[u] = __fmul_rn(t[u], fabsf(__ldg(row_scale + r)));
+            }
         }
-        if (row_scale) t = __fmul_rn(t, fabsf(__ldg(row_scale + r)));
-        m = fmaxf(m, t);
+        m = fmaxf(fmaxf(m, fmaxf(t[0], t[1])), fmaxf(t[2], t[3]));
     }
     const int64_t rem = cols - cv * LW;  // < LW columns per row left over
     if (rem > 0) {
@@ -40,6 +55,52 @@ __global__ void __launch_bounds__(256) absmax_kernel(const float *__restrict__ x
             m = fmaxf(m, t);
         }
     }
+    block_absmax_to_scale(m, scale);
+}
+
+// Contiguous matrix whose rows do not start on 16-byte boundaries (e.g. 602 columns), with a per-row factor: the data
+// is read as one flat stream of aligned 128-bit loads; a vector that straddles a row boundary (cols >= 4: at most one)
+// takes the factor of the next row for its trailing elements.
+__global__ void __launch_bounds__(256) absmax_flat_rows_kernel(const float *__restrict__ x, int64_t numel, int64_t cols,
+                                                               const float *__restrict__ row_scale,
+                                                               float *__restrict__ scale) {
+    float m = 0.f;
+    const int64_t n4 = numel >> 2;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const bool small = numel <= 0x7fffffff;
+    for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i0 < n4; i0 += 4 * stride) {
+        float t[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t i = i0 + u * stride;
+            t[u] = 0.f;
+            if (i < n4) {
+                const float4 v = __ldcs(reinterpret_cast<const float4 *>(x) + i);
+                const int64_t e = i << 2;
+                int64_t r, off;
+                if (small) {
+                    const uint32_t r32 = (uint32_t)e / (uint32_t)cols;
+                    r = r32; off = (uint32_t)e - r32 * (uint32_t)cols;
+                } else {
+                    r = e / cols; off = e - r * cols;
+                }
+                const float s0 = fabsf(__ldg(row_scale + r));
+                if (off + 3 < cols) {
+                    t[u] = __fmul_rn(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))), s0);
+                } else {
+                    const float s1 = fabsf(__ldg(row_scale + r + 1));   // r + 1 exists: the vector ends inside it
+                    const float a0 = __fmul_rn(fabsf(v.x), s0);
+                    const float a1 = __fmul_rn(fabsf(v.y), off + 1 < cols ? s0 : s1);
+                    const float a2 = __fmul_rn(fabsf(v.z), off + 2 < cols ? s0 : s1);
+                    const float a3 = __fmul_rn(fabsf(v.w), s1);
+                    t[u] = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+                }
+            }
+        }
+        m = fmaxf(fmaxf(m, fmaxf(t[0], t[1])), fmaxf(t[2], t[3]));
+    }
+    const int64_t tail = (n4 << 2) + blockIdx.x * (int64_t)blockDim.x + threadIdx.x;   // numel % 4 last elements
+    if (tail < numel) m = fmaxf(m, __fmul_rn(fabsf(x[tail]), fabsf(__ldg(row_scale + tail / cols))));
     block_absmax_to_scale(m, scale);
 }
 
@@ -219,6 +280,12 @@ extern "C" int tango_absmax_scale(const float *x, int64_t rows, int64_t cols, in
     if (!x) return TANGO_EINVAL;
     if (ld == cols && !row_scale) {  // contiguous: treat as one long row so the vector path applies to any shape
         cols = rows * cols; rows = 1; ld = cols;
+    }
+    if (row_scale && ld == cols && cols >= 4 && cols % 4 != 0 && aligned(x, 16)) {
+        const int grid = stream_grid(rows * cols / 4, 256, 16);
+        absmax_flat_rows_kernel<<<grid, 256, 0, stream>>>(x, rows * cols, cols, row_scale, scale);
+        TANGO_LAUNCH_CHECK();
+        return TANGO_OK;
     }
     const int lw = (aligned(x, 16) && (rows == 1 || ld % 4 == 0)) ? 4 : (aligned(x, 8) && (rows == 1 || ld % 2 == 0)) ? 2 : 1;
     const int grid = stream_grid(rows * ceil_div(cols, lw), 256, 16);

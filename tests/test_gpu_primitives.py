@@ -93,6 +93,19 @@ def test_quantize_row_scale(cuda):
     np.testing.assert_array_equal(out.cpu().numpy(), O.quantize(xs, O.absmax_scale(xs)))
 
 
+@pytest.mark.parametrize("shape", [(64, 602), (257, 41), (5, 7), (3, 5), (1000, 6), (33, 4099)])
+def test_absmax_with_row_factors_on_unaligned_rows(cuda, shape):
+    """Contiguous rows that do not start on 16-byte boundaries are read as one flat vector stream; vectors that
+    straddle a row boundary must take each element's own row factor."""
+    from tango_b200 import kernels as K
+    rng = np.random.default_rng(shape[1])
+    x = rng.standard_normal(shape).astype(np.float32)
+    rs = (rng.random(shape[0]) * 10).astype(np.float32)
+    rs[rng.integers(0, shape[0])] = 1000.0               # one row dominates: a wrong row factor shows immediately
+    xs = (x * rs[:, None]).astype(np.float32)
+    assert K._get_scale(_dev(x), _dev(rs)).item() == O.absmax_scale(xs)
+
+
 def test_stochastic_rounding_is_unbiased_and_seeded(cuda):
     from tango_b200 import kernels as K
     x = torch.full((1 << 16,), 0.3, device="cuda")
