@@ -457,7 +457,7 @@ __global__ void __launch_bounds__(128) incidence_contig_kernel(const SpmmArgs a)
 #pragma unroll
         for (int c = 0; c < F; ++c)
             if (lane == c && acc[c] != 0) atomicAdd(a.ws + (int64_t)u.w * a.ws_ld + c, acc[c]);
-    } else if (w - a.n_units < a.n_rows) {
+    } else if (w - a.n_units < a.n_long) {
         int64_t row = w - a.n_units;
         if (a.row_order) row = __ldg(a.row_order + row);
         const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
@@ -584,6 +584,14 @@ static bool try_incidence_contig(SpmmArgs &a, const tango_spmm_plan *plan, cudaS
     rc = TANGO_OK;
     a.n_long = a.n_rows;
     if (plan) a.row_order = plan->row_order;
+    // rows with a handful of edges (the tail of the degree-sorted order) are cheaper with one lane group per row than
+    // with a whole warp and its cross-lane reduction: they go to spmm_short_kernel, which needs 4- or 16-byte pieces
+    const int short_vec = (f == 16) ? 16 : (f == 4 || f == 8) ? 4 : 0;
+    if (short_vec && plan && plan->row_order && plan->n_long_rows >= 0 && plan->n_long_rows <= a.n_rows) {
+        a.n_long = plan->n_long_rows;
+        a.f_pad = f;
+        a.G = f / short_vec;          // 1 or 2 lanes per row
+    }
     if (plan && plan->n_units > 0) {
         if (!plan->units || !plan->heavy_rows || !plan->ws || plan->ws_ld < f || plan->n_heavy <= 0 ||
             !aligned(plan->units, 16)) { rc = TANGO_EINVAL; return true; }
@@ -593,16 +601,25 @@ static bool try_incidence_contig(SpmmArgs &a, const tango_spmm_plan *plan, cudaS
             rc = TANGO_ECUDA; return true;
         }
     }
-    const int64_t blocks = ceil_div(a.n_units + a.n_rows, 4);
+    const int64_t blocks = ceil_div(a.n_units + a.n_long, 4);
     if (blocks > 0x7fffffff) { rc = TANGO_ESIZE; return true; }
-    switch (f) {
-        case 1: incidence_contig_kernel<1><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
-        case 2: incidence_contig_kernel<2><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
-        case 4: incidence_contig_kernel<4><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
-        case 8: incidence_contig_kernel<8><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
-        default: incidence_contig_kernel<16><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+    if (blocks > 0) {
+        switch (f) {
+            case 1: incidence_contig_kernel<1><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+            case 2: incidence_contig_kernel<2><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+            case 4: incidence_contig_kernel<4><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+            case 8: incidence_contig_kernel<8><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+            default: incidence_contig_kernel<16><<<(unsigned)blocks, 128, 0, stream>>>(a); break;
+        }
+        if (cudaPeekAtLastError() != cudaSuccess) { rc = TANGO_ECUDA; return true; }
     }
-    if (cudaPeekAtLastError() != cudaSuccess) { rc = TANGO_ECUDA; return true; }
+    if (a.n_long < a.n_rows) {
+        const int64_t sb = ceil_div((a.n_rows - a.n_long) * a.G, 128);
+        if (sb > 0x7fffffff) { rc = TANGO_ESIZE; return true; }
+        if (short_vec == 16) spmm_short_kernel<16, MODE_COPY><<<(unsigned)sb, 128, 0, stream>>>(a);
+        else spmm_short_kernel<4, MODE_COPY><<<(unsigned)sb, 128, 0, stream>>>(a);
+        if (cudaPeekAtLastError() != cudaSuccess) { rc = TANGO_ECUDA; return true; }
+    }
     if (a.n_units > 0) {
         const int64_t fb = ceil_div(a.n_heavy * a.f, 256);
         spmm_finalize_kernel<<<(unsigned)fb, 256, 0, stream>>>(a);

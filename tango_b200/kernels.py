@@ -282,8 +282,8 @@ def _incidence_spmm(out, indptr, edge_ids, E, scale, sched=None):
         check(lib.tango_spmm_incidence(_p(indptr), _p(edge_ids), n_rows, _p(E), ldz, f, _p(scale), _p(out), ldo, plan,
                                        _stream()), "incidence_SPMM")
     contiguous = edge_ids is None and ldz == f and f in (1, 2, 4, 8, 16)    # streamed by the contiguous-row kernel
-    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0) + (
-        not contiguous and sched is not None and sched.n_long < sched.row_order.numel())
+    has_short = sched is not None and sched.n_long < sched.row_order.numel() and (not contiguous or f in (4, 8, 16))
+    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0) + has_short
     del keep
 
 
