@@ -287,6 +287,9 @@ def _incidence_spmm(out, indptr, edge_ids, E, scale, sched=None):
     del keep
 
 
+ROWWISE_SDDMM_MIN_DEGREE = 32     # average edges per row from which mySDDMM_int8("dot") walks rows
+
+
 def _sddmm_dot_rows(out, scaleOut, indptr, indices, edge_ids, U, V, scaleU, scaleV, sched=None) -> bool:
     """Row-wise dot SDDMM over a CSR/CSC bundle; False when the operand layout needs the endpoint-list kernel."""
     h, d = U.shape[-2], U.shape[-1]
@@ -433,9 +436,11 @@ def mySDDMM_int8(g, op, U, V, scaleU, scaleV, isReduce, reverse=False):
     out = torch.empty(out_shape, dtype=torch.float32, device=src.device)
     scale = torch.zeros((1,), dtype=torch.float32, device=src.device) if isReduce else torch.Tensor()
     done = False
-    if (op == "dot" and src.numel() > 0 and U.shape[1:] == V.shape[1:] and U.dim() == 3
-            and U.shape[0] == g.num_nodes() == V.shape[0]):
-        # walk the rows of the fixed endpoint: V's row stays in registers, only U is gathered
+    if (op == "dot" and src.numel() >= ROWWISE_SDDMM_MIN_DEGREE * g.num_nodes() and U.shape[1:] == V.shape[1:]
+            and U.dim() == 3 and U.shape[0] == g.num_nodes() == V.shape[0]):
+        # walk the rows of the fixed endpoint: V's row stays in registers, only U is gathered.  Worth it when rows
+        # are long enough to fill a warp's batches; on a graph with a handful of edges per row the endpoint-list
+        # kernel (32 edges per warp, whatever their rows) is the faster one.
         indptr, indices, edge_ids = _bundle(g, reverse)
         done = _sddmm_dot_rows(out, scale, indptr, indices, edge_ids, U, V, scaleU, scaleV, _schedule(g, reverse))
     if not done:

@@ -384,8 +384,10 @@ def test_sddmm_dot_rows_matches_endpoint_kernel(cuda, h, d, order):
             torch.as_strided(t, (n, t.stride(0) - h * d), (t.stride(0), 1), h * d).zero_()
     su, sv = _scale_t(np.float32(0.02)), _scale_t(np.float32(0.005))
     for reverse in (False, True):
-        K.launch_counter[0] = 0
-        out, sc = K.mySDDMM_int8(g, "dot", u_t, v_t, su, sv, True, reverse=reverse)
+        out = torch.empty((g.num_edges(), h, 1), device="cuda")
+        sc = torch.zeros(1, device="cuda")
+        indptr, indices, edge_ids = K._bundle(g, reverse)
+        assert K._sddmm_dot_rows(out, sc, indptr, indices, edge_ids, u_t, v_t, su, sv, K._schedule(g, reverse))
         s_np, d_np = (dst_np, src_np) if reverse else (src_np, dst_np)
         ref = O.sddmm_dot(s_np, d_np, uq, vq, np.float32(0.02), np.float32(0.005))
         np.testing.assert_array_equal(out.cpu().numpy()[..., 0], ref)
@@ -395,6 +397,9 @@ def test_sddmm_dot_rows_matches_endpoint_kernel(cuda, h, d, order):
         s_t, d_t = g.coo[::-1] if reverse else g.coo
         K.cuda_kernels.mySDDMM_int8("dot", out2, torch.Tensor(), s_t, d_t, u_t, v_t, su, sv)
         assert torch.equal(out, out2)
+        # and the public wrapper, whichever of the two kernels it picks for this graph
+        out3, sc3 = K.mySDDMM_int8(g, "dot", u_t, v_t, su, sv, True, reverse=reverse)
+        assert torch.equal(out, out3) and sc3.item() == sc.item()
 
 
 def test_sddmm_recipe_fixture(cuda):
