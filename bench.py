@@ -141,7 +141,7 @@ def run_reference(args):
         loss = F.cross_entropy(model(feats), labels)
         loss.backward()
         opt.step()
-        return float(loss)
+        return float(loss.detach())
 
     for _ in range(args.warmup):
         step()
