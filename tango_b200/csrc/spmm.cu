@@ -2,10 +2,13 @@
 //
 // One warp owns one output row (or one "unit" = slice of a long row).  Within the warp, G lanes cover one
 // neighbour's feature row with VEC-byte loads (G * VEC >= padded feature width) and 32/G neighbours are gathered per
-// step.  Neighbour ids are fetched 32 at a time with one coalesced load and handed out by shuffle.  Bytes are
-// sign-extended and added with dp4a against a one-hot (copy-u) or weight-carrying (u_mul_e) selector, so every
-// accumulator is an exact int32.  Rows longer than the plan's threshold are cut into units that add into an int32
-// scratch row with integer atomics (order independent => deterministic) and a second kernel finishes them.
+// step.  Neighbour ids are fetched 32 at a time with one coalesced load (the next batch is prefetched) and handed out
+// by shuffle; four gathers are in flight per lane (eight for narrow rows).  The same word of four neighbours is
+// byte-transposed with PRMT and added with a 4-way dp4a against (1,1,1,1) (copy-u) or the four neighbours' int8
+// weights (u_mul_e), so every accumulator is an exact int32.  Rows longer than the plan's threshold are cut into
+// units that add into an int32 scratch row with integer atomics (order independent => deterministic) and a second
+// kernel finishes them; rows of at most 48 neighbours are handled by lane groups (spmm_short_kernel); in-edge sums
+// over contiguous edge rows have their own streaming kernel (incidence_contig_kernel).
 #include "common.cuh"
 
 namespace tango {
