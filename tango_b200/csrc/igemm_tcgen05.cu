@@ -9,10 +9,13 @@
 //                                              int32 atomics into scratch, then a small dequantising kernel.
 // so no transposed copies of the quantized tensors are ever written.
 //
-// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns tensor memory and issues the MMAs (one lane), warps 2-5 run the
-// epilogue (each reads the 32 TMEM lanes it may access).  Every mbarrier wait is bounded: after ~2 s without
-// progress the kernel records TANGO_ETIMEOUT in the status word, lets outstanding copies land, frees its tensor
-// memory and returns.
+// Two kernels.  igemm_kernel (split-K dW, and the fallback): CTA = 6 warps, one output tile per CTA -- warp 0 issues
+// TMA loads, warp 1 owns tensor memory and issues the MMAs (one lane), warps 2-5 run the epilogue (each reads the 32
+// TMEM lanes it may access).  igemm_persistent_kernel (forward and dX): one CTA of 10 warps per SM keeps its tile of
+// the B operand resident in shared memory, streams 128-row A tiles through a 3-stage TMA ring, alternates between
+// two TMEM accumulators so the epilogue of one tile overlaps the MMAs of the next, and runs 8 epilogue warps.
+// Every mbarrier wait is bounded: after ~2 s without progress the kernel records TANGO_ETIMEOUT in the status word,
+// lets outstanding copies land, frees its tensor memory and returns.
 #include <cuda.h>
 
 #include <mutex>
