@@ -52,3 +52,46 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src, f"{f} mentions the oracle"
+
+
+def _prototypes():
+    """name -> (return type text, [parameter type texts]) for every function declared in the header."""
+    text = open(os.path.join(ROOT, "include", "tango_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"^\s*#.*$", "", text, flags=re.M)
+    protos = {}
+    for m in re.finditer(r"([A-Za-z_][\w\s\*]*?)\b(tango_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S):
+        ret, name, params = m.group(1).strip(), m.group(2), m.group(3).strip()
+        plist = [] if params in ("", "void") else [" ".join(p.split()) for p in params.split(",")]
+        protos[name] = (ret, plist)
+    return protos
+
+
+def _ctype_of(decl: str):
+    """ctypes class the binding must use for a C parameter (or return) declaration."""
+    if "*" in decl or decl.startswith("tango_stream_t"):
+        return ctypes.c_void_p
+    base = decl.replace("const ", "").split()[0]
+    return {"int": ctypes.c_int, "int64_t": ctypes.c_int64, "uint64_t": ctypes.c_uint64,
+            "float": ctypes.c_float}[base]
+
+
+def test_ctypes_signatures_match_the_header():
+    """Every entry of the ctypes table has the arity and the scalar / pointer classes of its C prototype, so a
+    signature change in the header cannot silently shift arguments in the binding."""
+    from tango_b200 import _lib
+    protos = _prototypes()
+    assert set(protos) == set(_lib._SIGS)
+    for name, (ret, params) in protos.items():
+        argtypes, restype = _lib._SIGS[name]
+        assert len(argtypes) == len(params), f"{name}: {len(argtypes)} ctypes arguments, {len(params)} in the header"
+        for k, (a, decl) in enumerate(zip(argtypes, params)):
+            want = _ctype_of(decl)
+            if want is ctypes.c_void_p:          # any pointer class will do (typed struct pointers included)
+                assert a is ctypes.c_void_p or issubclass(a, ctypes._Pointer), f"{name}: argument {k} ({decl})"
+            else:
+                assert a is want, f"{name}: argument {k} ({decl}) bound as {a.__name__}"
+        if "char" in ret:
+            assert restype is ctypes.c_char_p
+        else:
+            assert restype is _ctype_of(ret), f"{name}: returns {ret}, bound as {restype.__name__}"
