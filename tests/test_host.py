@@ -219,3 +219,53 @@ def test_graph_from_edge_list(tmp_path):
     assert pairs == {(0, 1), (1, 0), (1, 2), (2, 1), (3, 0), (0, 3), (0, 0), (1, 1), (2, 2), (3, 3)}
     assert g.num_nodes() == 4 and g.adj_csc[0].tolist() == [0, 3, 6, 8, 10]
     assert g._identity["csc"]
+
+
+def test_rendezvous_protocol_model():
+    """Host-side model of the one-CTA rendezvous kernel (csrc/peer.cu): rank r writes (round, value) into word
+    bank(round) * world + r of every rank's slot array, then waits for the `world` words of that bank in its own
+    array.  Ranks run as threads with random delays; every round must return the maximum of that round's values on
+    every rank although fast ranks are already writing the next round while slow ones still read (two banks)."""
+    import random
+    import threading
+    import time
+    world, rounds = 4, 200
+    slots = [[(0, 0.0)] * (2 * world) for _ in range(world)]      # slots[k][bank * world + r] = (round, value)
+    results = [[None] * rounds for _ in range(world)]
+    rng = random.Random(5)
+    values = [[rng.random() for _ in range(rounds)] for _ in range(world)]
+    errors = []
+
+    def rank_main(r):
+        local = random.Random(100 + r)
+        for e in range(1, rounds + 1):
+            bank = (e & 1) * world
+            if local.random() < 0.3:
+                time.sleep(local.random() * 1e-4)
+            for k in range(world):                                 # "release" stores into every rank's array
+                slots[k][bank + r] = (e, values[r][e - 1])
+            got = []
+            for t in range(world):                                 # bounded wait on the own array
+                t0 = time.time()
+                while slots[r][bank + t][0] < e:
+                    if time.time() - t0 > 5.0:
+                        errors.append((r, e, t))
+                        return
+                    time.sleep(0)
+                got.append(slots[r][bank + t])
+            # a word may already carry a LATER round of the same bank only if that rank passed round e + 1, which
+            # needs this rank's round e + 1 store -- impossible while this rank is still in round e
+            if any(rd != e for rd, _ in got):
+                errors.append((r, e, "overwritten"))
+                return
+            results[r][e - 1] = max(v for _, v in got)
+
+    threads = [threading.Thread(target=rank_main, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors[:3]
+    for e in range(rounds):
+        want = max(values[r][e] for r in range(world))
+        assert all(results[r][e] == want for r in range(world))
