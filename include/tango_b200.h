@@ -10,6 +10,9 @@
  * "host".  The device that owns the pointers must be current in the calling
  * thread.  No global mutable state is kept, so the library may be entered from
  * several host threads (PyTorch's autograd thread runs the backward calls).
+ * The exceptions are named where they are declared: tango_qgemm_dw_noalloc
+ * (scratch inside the library) and the tango_peer_* set-up helpers of the
+ * multi-GPU section (they create and map shared buffers, once, on the host).
  *
  * Each declaration cites the reference interface it replaces as file:line
  * inside the Tango repository (cuda/src/cuda.cpp holds its pybind table).
