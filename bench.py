@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized GCN training epoch (the workload BASELINE.json's metric is quoted on).
+"""Benchmark of the quantized GCN training epoch on the 232,965-node / 114.6 M-edge graph.
 
     python bench.py --gpus N --steps K --warmup W            # this library, N GPUs (torchrun for N > 1)
     python bench.py --impl reference --gpus N --steps K ...  # the reference's fp32 formulation on the host cores
@@ -30,7 +30,7 @@ WORKLOADS = {
     # name: (nodes, directed non-loop edges, in_feats, hidden, classes, graph seed)
     "gcn_c5": (232_965, 114_615_892 - 232_965, 602, 256, 41, 20245),
     "gcn_c1": (19_717, 88_648, 500, 16, 3, 20241),
-    # 2-layer GAT, 4 heads x 64 hidden, 1 output head x 41 classes (BASELINE config 4), same graph as gcn_c5
+    # 2-layer GAT, 4 heads x 64 hidden, 1 output head x 41 classes, same graph as gcn_c5
     "gat_c4": (232_965, 114_615_892 - 232_965, 602, 64, 41, 20245),
 }
 
@@ -87,10 +87,23 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_graph(name: str, device):
-    from tango_b200.graph import rmat_graph
+def _graph_module(load_package: bool):
+    """tango_b200.graph; for the reference arm it is loaded by path, so that the product's CUDA library is never
+    loaded into that process (the module itself needs only torch)."""
+    if load_package:
+        from tango_b200 import graph
+        return graph
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_tango_graph_only", os.path.join(ROOT, "tango_b200", "graph.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def build_graph(name: str, device, load_package: bool = True):
     n, e, *_rest, seed = WORKLOADS[name]
-    return rmat_graph(n, e, seed, device=device)
+    return _graph_module(load_package).rmat_graph(n, e, seed, device=device)
 
 
 def make_inputs(name: str, rows, pin: bool):
@@ -108,6 +121,42 @@ def make_inputs(name: str, rows, pin: bool):
 
 
 # ----------------------------------------------------------------------------------------------- reference arm
+def _host_adjacency(name: str):
+    """CSC and CSR (indptr, indices) of the workload's graph, in-degrees, out-degrees and the edge count, built on the
+    host cores only (this arm never touches the GPU nor loads the product's library).  Generating 114.6 M R-MAT edges
+    takes a couple of minutes on the host, so the arrays are kept in a scratch file for the next run on this machine."""
+    import numpy as np
+    import torch
+    n, e, *_rest, seed = WORKLOADS[name]
+    cache = os.path.join(os.environ.get("TMPDIR", "/tmp"), f"tango_b200_bench_{name}_{n}_{e}_{seed}.npz")
+    if os.path.exists(cache):
+        try:
+            z = np.load(cache)
+            csc = [torch.from_numpy(z["csc_indptr"]), torch.from_numpy(z["csc_indices"])]
+            csr = [torch.from_numpy(z["csr_indptr"]), torch.from_numpy(z["csr_indices"])]
+            return csc, csr, csc[0][1:] - csc[0][:-1], csr[0][1:] - csr[0][:-1], int(csc[1].numel())
+        except Exception:
+            pass
+    G = _graph_module(False)
+    src, dst = G.rmat_edges(n, e, seed, "cpu")
+    src, dst = G.add_self_loop(src, dst, n)
+    src, dst = src.long(), dst.long()
+
+    def compress(rows, cols):
+        key, _ = torch.sort(rows * n + cols)
+        indptr = torch.zeros(n + 1, dtype=torch.int64)
+        torch.cumsum(torch.bincount(rows, minlength=n), 0, out=indptr[1:])
+        return [indptr.to(torch.int32), (key % n).to(torch.int32)]
+
+    csr, csc = compress(src, dst), compress(dst, src)
+    try:
+        np.savez(cache, csc_indptr=csc[0].numpy(), csc_indices=csc[1].numpy(), csr_indptr=csr[0].numpy(),
+                 csr_indices=csr[1].numpy())
+    except OSError:
+        pass
+    return csc, csr, csc[0][1:] - csc[0][:-1], csr[0][1:] - csr[0][:-1], int(src.numel())
+
+
 def run_reference(args):
     """The reference's fp32 DGL/PyTorch formulation of the epoch on the host cores (restated without DGL in
     oracle/fp32_baseline.py), full workload, all host threads."""
@@ -121,13 +170,7 @@ def run_reference(args):
     torch.set_num_threads(cores)
     name = args.workload
     n, _, in_feats, hidden, classes, _ = WORKLOADS[name]
-    dev = "cuda" if torch.cuda.is_available() else "cpu"   # the synthetic graph is only *generated* on the GPU
-    g = build_graph(name, dev)
-    csc = [t.cpu() for t in g.adj_csc]
-    csr = [t.cpu() for t in g.adj_csr]
-    ind, outd = g.in_degrees().cpu(), g.out_degrees().cpu()
-    n_edges = g.num_edges()
-    del g
+    csc, csr, ind, outd, n_edges = _host_adjacency(name)
     a, a_t = B.csr_matrix(csc[0], csc[1], n), B.csr_matrix(csr[0], csr[1], n)
     torch.manual_seed(6)
     w1 = torch.nn.init.xavier_uniform_(torch.empty(hidden, in_feats))
@@ -180,9 +223,6 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # NCCL collectives are captured into the step's CUDA graph: the process group's watchdog must not poll
-        # events of a capturing stream
-        os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")
         dist.init_process_group("nccl", device_id=dev)
 
     name = args.workload
@@ -225,9 +265,26 @@ def run_ours(args):
         loss = F.cross_entropy(logits, labels, reduction="none").sum() / n
         loss.backward()
         if world > 1:
-            allreduce_grads(model)
+            allreduce_grads(model, peer=dg.peer)
         opt.step()
         return loss
+
+    # Before any update: loss and an order-independent 64-bit checksum of the logits of the initial model.  With one
+    # quantisation scale agreed by all ranks ("global" scale mode) every logit is bit-identical to the single-GPU
+    # run, so both values must come out the same at 1, 2, 4 and 8 GPUs.
+    with torch.no_grad():
+        logits0 = model(d_feats)
+        ce0 = F.cross_entropy(logits0, d_labels, reduction="none")
+        sums = torch.stack([logits0.contiguous().view(torch.int32).to(torch.int64).sum(),
+                            ce0.contiguous().view(torch.int32).to(torch.int64).sum()])
+        loss0 = ce0.double().sum().reshape(1)
+        if world > 1:
+            dist.all_reduce(sums)
+            dist.all_reduce(loss0)
+        step0 = {"loss_step0": float(loss0) / n,
+                 "logits_step0_checksum": f"{int(sums[0]) & 0xFFFFFFFFFFFFFFFF:016x}",
+                 "loss_rows_step0_checksum": f"{int(sums[1]) & 0xFFFFFFFFFFFFFFFF:016x}"}
+        del logits0, ce0
 
     # The whole step (forward, loss, backward, gradient all-reduce, Adam) is captured once in a CUDA graph and
     # replayed: ~80 launches per step otherwise leave the GPUs waiting for the Python host at 2+ GPUs.
@@ -333,6 +390,7 @@ def run_ours(args):
         loss = float(lt)
     status = K.device_status()
     if world > 1 and dg.peer is not None:
+        dg.peer.raise_if_expired()       # any rank's expired rendezvous, spread by the gradient all-reduce
         status = status or dg.peer.status()
 
     # dominant kernel on its own: the layer-1 aggregation (int8 features of width `hidden`) on this rank's rows
@@ -357,9 +415,11 @@ def run_ours(args):
         ach = alg / (k_ms * 1e-3) / 1e9
         roof = {"kernel": "spmm_kernel<16,copy_u> F=256 (layer-1 aggregation)", "bound": "hbm", "achieved": ach,
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                # dram__bytes_read+write of one ncu capture on a 20.2 M-edge copy of the graph (397 MB), plus 4 B for
-                # every further edge of the index stream
                 "traffic": 397_105_920 + 4 * max(0, n_edges - 20_232_965),
+                "traffic_source": "derived, not measured in this run: dram__bytes_read+write of the ncu capture in "
+                                  "profiles/spmm_copy_u_f256_ncu.md (397.1 MB on a 20.2 M-edge graph with the same nodes) "
+                                  "+ 4 B of index stream for every further edge",
+                "binding_ceiling": "l2_row_gather (see frac_of_l2_row_gather_peak); the HBM fraction is secondary",
                 "peak_source": peak_kind, "kernel_ms": k_ms, "algorithmic_bytes": alg,
                 "gathered_bytes_per_s_GB": touched / (k_ms * 1e-3) / 1e9,
                 "note": "the E*F gathered bytes are served by L2; HBM sees each feature row about once"}
@@ -403,6 +463,16 @@ def run_ours(args):
     cpu_base = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline and not name.startswith("gat"):
         cpu_base = _cpu_baseline(name, g, model)
+    secondary = None
+    if world == 1 and not args.no_secondary and name == "gcn_c5":
+        # outside the timed region: the GAT epoch on the same graph and the per-primitive numbers
+        graph = static_loss = None
+        del model, opt, d_feats, stage
+        torch.cuda.empty_cache()
+        secondary = {"gat_c4": _gat_epoch(g, dev)}
+        del g
+        torch.cuda.empty_cache()
+        secondary["primitives"] = run_primitives(args, quiet=True)
 
     if rank == 0:
         line = {
@@ -420,17 +490,71 @@ def run_ours(args):
             "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
             "clocks": clocks, "loss": loss, "status_word": status,
         }
+        line.update(step0)
+        if secondary:
+            line["secondary"] = secondary
         if roof:
             line["roofline"] = roof
         if cpu_base:
             line["cpu_baseline"] = cpu_base
         print(json.dumps(line), flush=True)
     if world > 1:
-        # the captured graph holds NCCL work; leave without tearing the communicator down under it
-        dist.barrier()
-        torch.cuda.synchronize()
+        # orderly teardown: the captured graph (it holds NCCL work) goes first, then the peer buffers, then the
+        # process group.  A watchdog ends the process if a library call of the teardown never returns.
         sys.stdout.flush()
-        os._exit(0)
+        done = threading.Event()
+
+        def _watchdog():
+            if not done.wait(60.0):
+                sys.stderr.write("bench: teardown did not finish within 60 s, leaving\n")
+                sys.stderr.flush()
+                os._exit(0)
+
+        threading.Thread(target=_watchdog, daemon=True).start()
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = static_loss = None
+        del opt
+        torch.cuda.synchronize()
+        dg.close()
+        dist.destroy_process_group()
+        done.set()
+
+
+def _gat_epoch(g, dev):
+    """Epoch (forward + loss + backward + Adam) of the 2-layer GAT (4 heads x 64, then 1 head x 41 classes) on the
+    same 114.6 M-edge graph, launched kernel by kernel; CUDA events around 5 steps after 3 warm-up steps."""
+    import torch
+    import torch.nn.functional as F
+    from tango_b200 import kernels as K
+    from tango_b200.gnn import GAT
+    n, _, in_feats, hidden, classes, _ = WORKLOADS["gat_c4"]
+    torch.manual_seed(6)
+    model = GAT(g, 2, in_feats, hidden, classes, [4, 1]).to(dev)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2, weight_decay=5e-4)
+    h_feats, h_labels = make_inputs("gat_c4", slice(0, n), False)
+    feats, labels = h_feats.to(dev), h_labels.to(dev)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        loss = F.cross_entropy(model(feats), labels)
+        loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    K.launch_counter[0] = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    return {"metric": "gat_epoch_ms", "value": e0.elapsed_time(e1) / 5, "unit": "ms", "steps": 5, "warmup": 3,
+            "layers": f"{in_feats}-4x{hidden}-{classes}", "edges": g.num_edges(), "loss": float(loss.detach()),
+            "gpu_launches_per_step": K.launch_counter[0] // 5, "cuda_graph": False, "status_word": K.device_status()}
 
 
 def _cpu_baseline(name, g, model):
@@ -507,10 +631,11 @@ def run_case(args):
         raise SystemExit(f"unknown case {args.case}")
 
 
-def run_primitives(args):
-    """Per-primitive numbers on the shapes of BASELINE configs 2 (QLinear) and 3 (SpMM / SDDMM): one JSON line per
-    primitive with ms, algorithmic GB/s (and TOPS for the GEMMs) and the fraction of the measured HBM peak.  L2 is
-    flushed (256 MB write) before every timed launch."""
+def run_primitives(args, quiet: bool = False):
+    """Per-primitive numbers on the QLinear shape (232,965 x 602 -> 256) and on the SpMM / SDDMM graph (169,343
+    nodes, 1,166,243 edges + self loops): one JSON line per primitive with ms, algorithmic GB/s (and TOPS for the
+    GEMMs) and the fraction of the measured HBM peak.  L2 is flushed (256 MB write) before every timed launch.
+    With quiet the lines are returned instead of printed."""
     import torch
     import tango_b200 as T
     from tango_b200 import kernels as K
@@ -541,7 +666,8 @@ def run_primitives(args):
             line["TOPS"] = round(ops / (ms * 1e-3) / 1e12, 1)
         line.update(extra)
         out_lines.append(line)
-        print(json.dumps(line), flush=True)
+        if not quiet:
+            print(json.dumps(line), flush=True)
 
     # ---- config 2: QLinear 232,965 x 602 -> 256
     m, k, n = 232_965, 602, 256
@@ -591,13 +717,22 @@ def run_primitives(args):
     q16, s16 = K.quantize(torch.randn((nn_, 1, 16), device=dev))
     report("sddmm add H=1 D=16", timeit(lambda: K.mySDDMM_int8(g, "add", q16, q16, s16, s16, False)),
            2 * nn_ * 16 + 8 * e + 4 * e * 16)
-    print(json.dumps({"suite": "primitives", "status_word": K.device_status(), "n": len(out_lines)}), flush=True)
+    if not quiet:
+        print(json.dumps({"suite": "primitives", "status_word": K.device_status(), "n": len(out_lines)}), flush=True)
+    return out_lines
 
 
 def _row_gather_peak(q, width):
     """GB/s at which tango_probe_row_gather reads random rows of the int8 table `q` (rows of `width` bytes)."""
+    import ctypes
     import torch
-    from tango_b200._lib import lib
+    path = os.path.join(ROOT, "tango_b200", "lib", "libtango_bench_probe.so")
+    if not os.path.exists(path):
+        return None
+    probe = ctypes.CDLL(path).bench_probe_row_gather
+    probe.restype = ctypes.c_int64
+    probe.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                      ctypes.c_void_p, ctypes.c_void_p]
     row_bytes = q.stride(0)
     if row_bytes != width or row_bytes & (row_bytes - 1) or not 16 <= row_bytes <= 512:
         return None
@@ -605,11 +740,11 @@ def _row_gather_peak(q, width):
     st = torch.cuda.current_stream().cuda_stream
     best = None
     for ctas, threads in ((8, 256), (16, 128), (8, 128), (4, 256)):      # best of a few launch shapes
-        lib.tango_probe_row_gather(q.data_ptr(), q.shape[0], row_bytes, 50, ctas, threads, sink.data_ptr(), st)
+        probe(q.data_ptr(), q.shape[0], row_bytes, 50, ctas, threads, sink.data_ptr(), st)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        nbytes = lib.tango_probe_row_gather(q.data_ptr(), q.shape[0], row_bytes, 1000, ctas, threads, sink.data_ptr(), st)
+        nbytes = probe(q.data_ptr(), q.shape[0], row_bytes, 1000, ctas, threads, sink.data_ptr(), st)
         e1.record()
         torch.cuda.synchronize()
         if nbytes > 0:
@@ -629,6 +764,8 @@ def main():
     ap.add_argument("--transport", default="auto", choices=["auto", "nccl", "peer"],
                     help="multi-GPU exchange: NCCL collectives, or stores into peer memory + rendezvous kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the untimed extras of the 1-GPU line (GAT epoch, per-primitive numbers)")
     ap.add_argument("--scale-mode", default="global", choices=["global", "shard"],
                     help="multi-GPU: one quantisation scale agreed by all ranks, or one per shard")
     ap.add_argument("--balance", default="dealt", choices=["dealt", "cyclic", "nnz", "rows"], help="multi-GPU node placement")

@@ -306,20 +306,13 @@ int tango_enable_peer_access(int peer_device);
  * mapped by every rank); round_word: this rank's device word counting the rounds (zero-initialised; all ranks must
  * call the same number of times); val_in / val_out may be NULL (pure barrier).  On return from the kernel everything
  * that the other ranks wrote to this GPU's memory before their call is visible to later kernels of this stream.
- * The wait is bounded (2 s); on expiry *status = TANGO_ETIMEOUT and the kernel returns. */
+ * The wait is bounded: limit_ns nanoseconds (<= 0 selects the default of 2 s).  On expiry *status = TANGO_ETIMEOUT,
+ * val_out receives the maximum over the ranks that did arrive, and the kernel returns; the round still counts, so a
+ * rank that was merely late meets the others again at the next call.  The limit is also the largest skew between
+ * ranks that a training loop may have at a rendezvous (a rank that spends longer than this between two steps, e.g.
+ * in an evaluation pass that only it runs, makes the others time out). */
 int tango_peer_sync(uint64_t *const *slots /* device */, int rank, int world, uint64_t *round_word, const float *val_in,
-                    float *val_out, int *status, tango_stream_t stream);
-
-/* ---------------------------------------------------------------- measurement aid */
-
-/* No counterpart in the reference.  Gathers pseudo-random rows (row_bytes a power of two in [16, 512]) of `table`
- * [rows, row_bytes] into registers with 128-bit loads, eight in flight per lane, 148 x ctas_per_sm CTAs of `threads`
- * threads (a multiple of 32, at most 256), and returns the number of bytes the launch gathers (or a negative
- * TANGO_E* code).  Timing the launch with a table
- * that fits in L2 gives the random-row gather ceiling that the aggregation kernels are compared with; `sink` is a
- * 4-byte device word that is never actually written. */
-int64_t tango_probe_row_gather(const void *table, int64_t rows, int64_t row_bytes, int iters, int ctas_per_sm,
-                               int threads, uint32_t *sink, tango_stream_t stream);
+                    float *val_out, int *status, int64_t limit_ns, tango_stream_t stream);
 
 #ifdef __cplusplus
 }

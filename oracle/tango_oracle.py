@@ -352,3 +352,64 @@ def recipe_sddmm_inputs(dim: int, out_len: int = 1):
     src = np.array([0, 0, 0, 1], dtype=np.int32)
     dst = np.array([0, 1, 2, 2], dtype=np.int32)
     return src, dst, u, v, F32(1.0), F32(1.0)
+
+
+# ----------------------------------------------------------------------------
+# The quantized GCN layer, forward and backward, as a chain of the primitives
+# above ("multiply first" branch, norm='both': in_feats > out_feats).
+# ----------------------------------------------------------------------------
+def gcn_layer_forward(csc, out_norm, in_norm, x, w, b, relu: bool):
+    """evaluation/test_gcn.py:86-137: X * d_out^-1/2 -> Qlinear_func_reduce
+    (cuda/QLinear.py:50-60: truncating fused forward, output scale) ->
+    spmm_copy_u with that scale (cuda/SPMM.py:8-16: nearest quantizer, CSC
+    aggregation) -> * d_in^-1/2 -> + bias -> activation.
+    csc = (indptr, indices) with rows = destinations.  Returns (out, cache)."""
+    xs = (np.asarray(x, F32) * np.asarray(out_norm, F32)[:, None]).astype(F32)
+    h, xq, wq, sx, sw, sh = qgemm_forward(xs, w, reduce_out=True)
+    hq = quantize(h, sh)
+    agg = spmm_copy_u(csc[0], csc[1], hq, sh)
+    out = (agg * np.asarray(in_norm, F32)[:, None]).astype(F32)
+    if b is not None:
+        out = (out + np.asarray(b, F32)[None, :]).astype(F32)
+    if relu:
+        out = np.maximum(out, F32(0))
+    return out, dict(xq=xq, wq=wq, sx=sx, sw=sw, out=out, relu=relu, has_bias=b is not None)
+
+
+def gcn_layer_backward(csr, out_norm, in_norm, cache, d_out, need_dx: bool = True):
+    """Backward of gcn_layer_forward, operator by operator as autograd runs the
+    reference's layer: ReLU mask; bias gradient = column sums in fp32; right
+    norm; spmm_copy_u.backward (cuda/SPMM.py:18-24: nearest quantizer with the
+    gradient's own scale, aggregation over the CSR = reversed graph);
+    Qlinear_func_reduce.backward (cuda/QLinear.py:62-72: dY_q nearest, dX and dW
+    from the cached int8 operands); left norm.  csr = (indptr, indices) with
+    rows = sources.  Returns (dX or None, dW, db or None)."""
+    g = np.asarray(d_out, F32)
+    if cache["relu"]:
+        g = np.where(cache["out"] > 0, g, F32(0)).astype(F32)
+    db = g.astype(np.float64).sum(0).astype(F32) if cache["has_bias"] else None
+    gz = (g * np.asarray(in_norm, F32)[:, None]).astype(F32)
+    sdz = absmax_scale(gz)
+    dh = spmm_copy_u(csr[0], csr[1], quantize(gz, sdz), sdz)
+    sdh = absmax_scale(dh)
+    dhq = quantize(dh, sdh)
+    dw = qgemm_backward_dw(dhq, cache["xq"], sdh, cache["sx"])
+    dx = None
+    if need_dx:
+        dx = (qgemm_backward_dx(dhq, cache["wq"], sdh, cache["sw"]) * np.asarray(out_norm, F32)[:, None]).astype(F32)
+    return dx, dw, db
+
+
+def cross_entropy_mean(logits, labels):
+    """Mean cross-entropy over all rows and its gradient with respect to the
+    logits (float64 internally; torch.nn.functional.cross_entropy as used at
+    evaluation/test_gcn.py:257, without the train mask synthetic data lacks)."""
+    z = np.asarray(logits, np.float64)
+    z = z - z.max(axis=1, keepdims=True)
+    lse = np.log(np.exp(z).sum(axis=1, keepdims=True))
+    logp = z - lse
+    n = z.shape[0]
+    loss = -logp[np.arange(n), labels].mean()
+    grad = np.exp(logp)
+    grad[np.arange(n), labels] -= 1.0
+    return F32(loss), (grad / n).astype(F32)

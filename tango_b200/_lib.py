@@ -78,8 +78,7 @@ _SIGS = {
     "tango_peer_close": ([P], c_int),
     "tango_peer_free": ([P], c_int),
     "tango_enable_peer_access": ([c_int], c_int),
-    "tango_peer_sync": ([P, c_int, c_int, P, P, P, P, P], c_int),
-    "tango_probe_row_gather": ([P, c_int64, c_int64, c_int, c_int, c_int, P, P], c_int64),
+    "tango_peer_sync": ([P, c_int, c_int, P, P, P, P, c_int64, P], c_int),
     "tango_edge_softmax": ([P, P, P, c_int64, c_int64, P, c_int, c_float, P, P, P], c_int),
     "tango_edge_softmax_bwd": ([P, P, P, c_int64, c_int64, c_int, c_float, P, P, P, P, P], c_int),
 }

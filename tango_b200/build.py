@@ -15,7 +15,10 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libtango_b200.so")
-SOURCES = ["quantize.cu", "spmm.cu", "sddmm.cu", "gat_softmax.cu", "igemm_tcgen05.cu", "probe.cu", "peer.cu"]
+SOURCES = ["quantize.cu", "spmm.cu", "sddmm.cu", "gat_softmax.cu", "igemm_tcgen05.cu", "peer.cu"]
+# measurement aid of the benchmark, a library of its own (not part of the product ABI)
+PROBE_SRC = os.path.join(CSRC, "bench", "row_gather_probe.cu")
+PROBE_LIB_PATH = os.path.join(LIB_DIR, "libtango_bench_probe.so")
 
 
 def _nvcc() -> str:
@@ -24,10 +27,11 @@ def _nvcc() -> str:
 
 
 def needs_build() -> bool:
-    if not os.path.exists(LIB_PATH):
+    if not os.path.exists(LIB_PATH) or not os.path.exists(PROBE_LIB_PATH):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", "tango_b200.h")]
+    t = min(os.path.getmtime(LIB_PATH), os.path.getmtime(PROBE_LIB_PATH))
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh"))]
+    deps += [PROBE_SRC, os.path.join(ROOT, "include", "tango_b200.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
@@ -47,6 +51,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed building libtango_b200.so")
     if verbose:
         sys.stderr.write(res.stderr)
+    res = subprocess.run([_nvcc(), "-shared", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a",
+                          "-lineinfo", "-O3", "-std=c++17", "-o", PROBE_LIB_PATH, PROBE_SRC],
+                         capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed building libtango_bench_probe.so")
     return LIB_PATH
 
 

@@ -729,7 +729,12 @@ using namespace tango;
 
 extern "C" int64_t tango_qgemm_dw_workspace_bytes(int64_t n, int64_t k) {
     if (n < 0 || k < 0) return 0;
-    return n * round_up(k, 4) * (int64_t)sizeof(int32_t);
+    if (n == 0 || k == 0) return 0;
+    // n * round_up(k, 4) * 4 must fit in int64: saturate instead of wrapping around
+    if (k > INT64_MAX - 3) return INT64_MAX;
+    const int64_t ldws = round_up(k, 4);
+    if (n > INT64_MAX / 4 / ldws) return INT64_MAX;
+    return n * ldws * (int64_t)sizeof(int32_t);
 }
 
 extern "C" int tango_qgemm_nt(const int8_t *xq, int64_t ldx, const int8_t *wq, int64_t ldw, int64_t m, int64_t n,
@@ -827,8 +832,9 @@ extern "C" int tango_qgemm_dw_noalloc(const int8_t *dyq, int64_t lddy, const int
                                       int64_t n, int64_t k, const float *sdy, const float *sx, float *dw,
                                       int64_t lddw, int *status, tango_stream_t stream) {
     if (n < 0 || k < 0) return TANGO_EINVAL;
-    const int64_t need = tango_qgemm_dw_workspace_bytes(n, k);
-    if (need > tango::kStaticDwScratchElems * (int64_t)sizeof(int32_t)) return TANGO_ESIZE;
+    // compared in elements and by division, so that no product of caller-given sizes can wrap around
+    if (k > tango::kStaticDwScratchElems) return TANGO_ESIZE;
+    if (n > 0 && k > 0 && n > tango::kStaticDwScratchElems / round_up(k, 4)) return TANGO_ESIZE;
     void *scratch = nullptr;
     const int rc = tango::dw_scratch_address(&scratch);
     if (rc) return rc;

@@ -9,8 +9,9 @@
 // word that a slow rank has not read yet: a rank can only reach round e + 2 after every rank has written round
 // e + 1, i.e. after every rank has finished reading round e.
 //
-// The wait is bounded (two seconds of %globaltimer): on expiry the kernel stores TANGO_ETIMEOUT in the status word and
-// returns, so a missing peer can never hang the GPU.
+// The wait is bounded (limit_ns of %globaltimer, two seconds by default): on expiry the kernel stores TANGO_ETIMEOUT
+// in the status word and returns the maximum of the values it did see, so a missing peer can never hang the GPU.  The
+// round counter still advances, and a late peer's word stays in its bank, so the ranks meet again in the next round.
 #include <cstring>
 
 #include "common.cuh"
@@ -33,7 +34,8 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 __global__ void __launch_bounds__(64) peer_sync_kernel(unsigned long long *const *slots, int rank, int world,
                                                        unsigned long long *round_word, const float *val_in,
-                                                       float *val_out, int *status) {
+                                                       float *val_out, int *status,
+                                                       unsigned long long limit_ns) {
     __shared__ float vals[64];
     const int t = threadIdx.x;
     const unsigned long long e = *round_word + 1ull;          // every thread reads before thread 0 advances it
@@ -49,14 +51,15 @@ __global__ void __launch_bounds__(64) peer_sync_kernel(unsigned long long *const
         const unsigned long long t0 = global_timer_ns();
         unsigned long long v = ld_acquire_sys(my_word);
         while ((v >> 32) < e) {
-            if (global_timer_ns() - t0 > 2000000000ull) {
+            if (global_timer_ns() - t0 > limit_ns) {
                 if (status) atomicExch(status, TANGO_ETIMEOUT);
                 break;
             }
             __nanosleep(100);
             v = ld_acquire_sys(my_word);
         }
-        got = __uint_as_float((unsigned int)(v & 0xffffffffull));
+        // a word that still carries an older round holds an older value: it does not take part
+        got = ((v >> 32) >= e) ? __uint_as_float((unsigned int)(v & 0xffffffffull)) : 0.f;
     }
     vals[t] = (t < world && (got == got)) ? got : 0.f;
     __syncthreads();
@@ -132,11 +135,12 @@ extern "C" int tango_enable_peer_access(int peer_device) {
 }
 
 extern "C" int tango_peer_sync(uint64_t *const *slots, int rank, int world, uint64_t *round_word, const float *val_in,
-                               float *val_out, int *status, tango_stream_t stream) {
+                               float *val_out, int *status, int64_t limit_ns, tango_stream_t stream) {
     if (!slots || !round_word || world < 1 || world > 64 || rank < 0 || rank >= world) return TANGO_EINVAL;
+    const unsigned long long limit = limit_ns > 0 ? (unsigned long long)limit_ns : 2000000000ull;
     peer_sync_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(reinterpret_cast<unsigned long long *const *>(slots), rank, world,
                                                          reinterpret_cast<unsigned long long *>(round_word), val_in,
-                                                         val_out, status);
+                                                         val_out, status, limit);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
 }

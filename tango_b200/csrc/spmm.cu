@@ -246,17 +246,10 @@ __device__ __forceinline__ float finish_value(float v, int64_t row, int col, con
     return v;
 }
 
+constexpr int kSpmmThreads = 128;   // four warps (four rows or slices) per CTA
+
 template <int VEC, int MODE, bool DEEP = false>
-#ifndef SPMM_THREADS
-#define SPMM_THREADS 128
-#endif
-#ifndef SPMM_MINB
-#define SPMM_MINB 8
-#endif
-#ifndef SPMM_MINB_DEEP
-#define SPMM_MINB_DEEP 6
-#endif
-__global__ void __launch_bounds__(SPMM_THREADS, DEEP ? SPMM_MINB_DEEP : SPMM_MINB) spmm_kernel(const SpmmArgs a) {
+__global__ void __launch_bounds__(kSpmmThreads, DEEP ? 6 : 8) spmm_kernel(const SpmmArgs a) {
     const int lane = threadIdx.x & 31;
     const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int sub = lane % a.G;
@@ -503,12 +496,6 @@ static int pow2_ceil(int x) {
     return p;
 }
 
-#ifdef SPMM_NO_DEEP
-constexpr bool kDeepNarrow = false;
-#else
-constexpr bool kDeepNarrow = true;
-#endif
-
 template <int MODE>
 static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t stream) {
     if (a.n_rows == 0 || a.f == 0) return TANGO_OK;
@@ -545,19 +532,19 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
         a.f_pad <= 32 * vec)
         a.n_long = plan->n_long_rows;
     const int64_t warps = a.n_units + a.n_long;
-    const int64_t blocks = ceil_div(warps, SPMM_THREADS / 32);
+    const int64_t blocks = ceil_div(warps, kSpmmThreads / 32);
     if (blocks > 0x7fffffff) return TANGO_ESIZE;
 #define TANGO_SPMM_LAUNCH(V, M)                                                                  \
     do {                                                                                         \
-        if (blocks > 0) spmm_kernel<V, M><<<(unsigned)blocks, SPMM_THREADS, 0, stream>>>(a);     \
+        if (blocks > 0) spmm_kernel<V, M><<<(unsigned)blocks, kSpmmThreads, 0, stream>>>(a);     \
     } while (0)
     if (MODE == MODE_WEIGHT_LANE && (a.D % vec) != 0) {
         if (vec == 16) TANGO_SPMM_LAUNCH(16, MODE_WEIGHT_ELEM);
         else if (vec == 4) TANGO_SPMM_LAUNCH(4, MODE_WEIGHT_ELEM);
         else TANGO_SPMM_LAUNCH(1, MODE_WEIGHT_LANE);  // VEC == 1: a lane holds one byte, always inside one head
     } else {
-        if (vec == 16 && a.G == 4 && kDeepNarrow) {
-            if (blocks > 0) spmm_kernel<16, MODE, true><<<(unsigned)blocks, SPMM_THREADS, 0, stream>>>(a);
+        if (vec == 16 && a.G == 4) {
+            if (blocks > 0) spmm_kernel<16, MODE, true><<<(unsigned)blocks, kSpmmThreads, 0, stream>>>(a);
         } else if (vec == 16) TANGO_SPMM_LAUNCH(16, MODE);
         else if (vec == 4) TANGO_SPMM_LAUNCH(4, MODE);
         else TANGO_SPMM_LAUNCH(1, MODE);

@@ -101,6 +101,12 @@ class DistGraph:
                 self.peer = None     # the set-up fails on all ranks or on none, so all of them fall back to NCCL
         self.transport = "peer" if self.peer is not None else "nccl"
 
+    def close(self) -> None:
+        """Releases the peer-memory buffers of this partition (a collective; no kernel may be in flight)."""
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
+
 
 def _padded_storage(q: torch.Tensor) -> torch.Tensor:
     """The [rows, ld] storage behind an int8 tensor returned by kernels.quantize."""
@@ -280,14 +286,21 @@ class DistGCN(nn.Module):
         return h
 
 
-def allreduce_grads(module: nn.Module, group=None) -> None:
-    """Sums the parameter gradients over the ranks (each rank holds the contribution of its rows)."""
+def allreduce_grads(module: nn.Module, group=None, peer=None) -> None:
+    """Sums the parameter gradients over the ranks (each rank holds the contribution of its rows).  With `peer` (a
+    PeerTransport) the rank's rendezvous status word rides along in the same all-reduce, so that after the step every
+    rank knows whether ANY rank gave up a wait (`peer.raise_if_expired()`); no extra collective, no synchronisation."""
     grads = [p.grad for p in module.parameters() if p.grad is not None]
     if not grads:
         return
-    flat = torch.cat([g.reshape(-1) for g in grads])
+    parts = [g.reshape(-1) for g in grads]
+    if peer is not None:
+        parts.append(peer.status_word().float().abs())
+    flat = torch.cat(parts)
     dist.all_reduce(flat, group=group)
     off = 0
     for g in grads:
         g.copy_(flat[off:off + g.numel()].view_as(g))
         off += g.numel()
+    if peer is not None:
+        peer.group_status.add_(flat[off:off + 1])

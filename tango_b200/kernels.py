@@ -37,11 +37,16 @@ def _p(t: Optional[torch.Tensor]):
     return None if t is None or t.numel() == 0 else t.data_ptr()
 
 
+_dummy_index = {}      # device -> one int32 zero, the address handed over for empty index arrays
+
+
 def _pi(t: torch.Tensor):
     """Pointer of a mandatory index array; an empty one (graph without edges) still needs a valid address."""
     if t.numel() == 0:
-        t = torch.zeros(1, dtype=torch.int32, device=t.device)
-        _pi.keep = t
+        d = _dummy_index.get(t.device)
+        if d is None:
+            d = _dummy_index[t.device] = torch.zeros(1, dtype=torch.int32, device=t.device)
+        return d.data_ptr()
     return t.data_ptr()
 
 

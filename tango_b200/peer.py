@@ -20,7 +20,7 @@ import torch
 import torch.distributed as dist
 
 from . import config
-from ._lib import check, lib
+from ._lib import TangoError, check, lib
 
 
 class _RawCuda:
@@ -84,9 +84,17 @@ class SharedBuffer:
 
 
 class PeerTransport:
-    def __init__(self, rank: int, world: int, device: torch.device, group=None):
+    """limit_ns bounds every wait for another GPU (default 2 s).  It is also the largest skew the ranks may have at a
+    rendezvous: a rank that arrives later than this (first-step lazy loading on a busy host, a rank-0-only evaluation
+    between two steps) makes the others give up, record TANGO_ETIMEOUT and carry on with what they have, which is then
+    wrong.  `allreduce_grads(..., peer=...)` spreads the status word to all ranks once per step and
+    `raise_if_expired()` turns it into an exception on every rank alike."""
+
+    def __init__(self, rank: int, world: int, device: torch.device, group=None, limit_ns: int = 0):
         assert 1 <= world <= 64
         self.rank, self.world, self.device, self.group = rank, world, device, group
+        self.limit_ns = int(limit_ns)
+        self.group_status = torch.zeros(1, dtype=torch.float32, device=device)   # sum over ranks of expired waits
         self._stream = lambda: torch.cuda.current_stream(device).cuda_stream
         # rendezvous words: 2 banks of `world` 64-bit words on every rank, written by everybody
         self._slots = SharedBuffer(2 * world * 8, rank, world, device, group)
@@ -104,7 +112,7 @@ class PeerTransport:
             check(lib.tango_peer_sync(self._slot_ptrs.data_ptr(), self.rank, self.world, self._round.data_ptr(),
                                       value.data_ptr() if value is not None else None,
                                       out.data_ptr() if out is not None else None, self._status.data_ptr(),
-                                      self._stream()), "peer_sync")
+                                      self.limit_ns, self._stream()), "peer_sync")
         from . import kernels
         kernels.launch_counter[0] += 1
         return out
@@ -113,8 +121,37 @@ class PeerTransport:
         self.max_scalar(None)
 
     def status(self) -> int:
-        """0, or TANGO_ETIMEOUT if a wait for another GPU expired."""
+        """0, or TANGO_ETIMEOUT if a wait of THIS rank for another GPU expired since the last reset.  Synchronises."""
         return int(self._status.item())
+
+    def status_word(self) -> torch.Tensor:
+        """The sticky per-rank status word on the device (int32, 0 or TANGO_ETIMEOUT)."""
+        return self._status
+
+    def reset_status(self) -> None:
+        self._status.zero_()
+        self.group_status.zero_()
+
+    def raise_if_expired(self) -> None:
+        """Raises on every rank if any rank's rendezvous expired in a step whose gradients went through
+        `allreduce_grads(..., peer=self)` (which spreads the status), or if this rank's own did.  Synchronises: call it
+        where the loop reads the loss anyway."""
+        if float(self.group_status.item()) != 0.0 or int(self._status.item()) != 0:
+            raise TangoError("a bounded wait for another GPU expired: the gathered int8 tables or the agreed scales of "
+                             "that step may be incomplete (raise PeerTransport.limit_ns if ranks legitimately skew)")
+
+    def close(self) -> None:
+        """Unmaps and frees every shared buffer (a collective: all ranks call it, with no kernel of theirs in flight).
+        Tensors returned by `table()` must not be used afterwards."""
+        torch.cuda.synchronize(self.device)
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+        for _tab, _ptrs, buf in self._tables.values():
+            buf.release()
+        self._tables.clear()
+        if self._slots is not None:
+            self._slots.release()
+            self._slots = None
 
     # ------------------------------------------------------------------------------------------------ gathered tables
     def table(self, key, rows: int, ld: int):

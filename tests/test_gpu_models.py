@@ -1,6 +1,7 @@
-"""Model-level parity on the GPU: the quantized GCN layer chain against the CPU oracle chain (bit-exact forward,
-1e-3 gradients), fused vs unfused layer (bit-identical), GAT layer against its fp32 formulation, autograd
-operators against fp32 autograd within quantisation error."""
+"""Model-level parity on the GPU: the quantized GCN layer chain against the CPU oracle chain (bit-exact forward;
+loss and every gradient of a full training step within 1e-3 of the oracle's backward chain), fused vs unfused layer
+(bit-identical), GAT layer against its fp32 formulation, autograd operators against fp32 autograd within
+quantisation error (information about the int8 noise, not the parity bar)."""
 import numpy as np
 import pytest
 import torch
@@ -210,7 +211,7 @@ def test_gat_edge_softmax_bwd_kernel(cuda):
 
 
 def test_config1_gcn_forward_bit_exact_vs_oracle(cuda):
-    """BASELINE config 1 at full size (19,717 nodes, 88,648 edges + self loops, 500 -> 16 -> 3): the logits of the
+    """The 19,717-node configuration at full size (88,648 edges + self loops, 500 -> 16 -> 3): the logits of the
     2-layer quantized GCN equal the oracle's layer chain bit for bit."""
     import tango_b200 as T
     from tango_b200.gnn import GCN
@@ -229,6 +230,59 @@ def test_config1_gcn_forward_bit_exact_vs_oracle(cuda):
     ref = _oracle_gcn_layer(g, h, m.layers[1].weight.detach().cpu().numpy(), m.layers[1].bias.detach().cpu().numpy(),
                             False)
     np.testing.assert_array_equal(logits, ref)
+
+
+def _rel(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)
+
+
+@pytest.mark.parametrize("shape", [(19_717, 88_648, 20241, 500, 16, 3), (6000, 150_000, 33, 602, 256, 41)])
+@pytest.mark.parametrize("fused", [True, False])
+def test_gcn_training_step_loss_and_gradients_vs_oracle_chain(cuda, shape, fused):
+    """One full step (forward, mean cross-entropy, backward) of the 2-layer quantized GCN -- at the full size of the
+    19,717-node configuration and on a smaller graph with the 602 -> 256 -> 41 widths -- against the oracle's chain:
+    quantize dY (nearest) -> reversed aggregation -> dX / dW from the cached int8 operands, ReLU mask, norms, fp32 bias
+    gradient (cuda/QLinear.py:37-47,62-72, cuda/SPMM.py:18-24, evaluation/test_gcn.py:104-137).  Bar: loss, dW1, dW2,
+    db1, db2 within 1e-3 of the oracle (relative to each tensor's largest magnitude).  The forward pass is bit-exact;
+    the gradients differ only through the fp32-vs-fp64 softmax of the loss and the summation order of the bias
+    gradient."""
+    import tango_b200 as T
+    from tango_b200.gnn import GCN
+    from tango_b200.graph import rmat_graph
+    n, e, seed, f_in, hid, cls = shape
+    g = rmat_graph(n, e, seed, device="cuda")
+    T.graph_preprocess(g)
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((n, f_in)).astype(np.float32)
+    labels = rng.integers(0, cls, n)
+    torch.manual_seed(6)
+    m = GCN(g, f_in, hid, cls, 1, fused=fused).cuda()
+    with torch.no_grad():
+        m.layers[0].bias.copy_(torch.from_numpy((rng.standard_normal(hid) * 0.1).astype(np.float32)))
+        m.layers[1].bias.copy_(torch.from_numpy((rng.standard_normal(cls) * 0.1).astype(np.float32)))
+    logits = m(torch.from_numpy(x).cuda())
+    loss = F.cross_entropy(logits, torch.from_numpy(labels).cuda())
+    loss.backward()
+    # ---- oracle chain
+    csc = [t.cpu().numpy().astype(np.int64) for t in g.adj_csc]
+    csr = [t.cpu().numpy().astype(np.int64) for t in g.adj_csr]
+    on = g.out_degrees().float().clamp(min=1).pow(-0.5).cpu().numpy()
+    inn = g.in_degrees().float().clamp(min=1).pow(-0.5).cpu().numpy()
+    w1, b1 = m.layers[0].weight.detach().cpu().numpy(), m.layers[0].bias.detach().cpu().numpy()
+    w2, b2 = m.layers[1].weight.detach().cpu().numpy(), m.layers[1].bias.detach().cpu().numpy()
+    h1, c1 = O.gcn_layer_forward(csc, on, inn, x, w1, b1, True)
+    z, c2 = O.gcn_layer_forward(csc, on, inn, h1, w2, b2, False)
+    np.testing.assert_array_equal(logits.detach().cpu().numpy(), z)
+    rloss, dz = O.cross_entropy_mean(z, labels)
+    dh1, dw2, db2 = O.gcn_layer_backward(csr, on, inn, c2, dz, True)
+    _, dw1, db1 = O.gcn_layer_backward(csr, on, inn, c1, dh1, False)
+    assert abs(loss.item() - float(rloss)) / float(rloss) < 1e-3
+    got = {"dW1": m.layers[0].weight.grad, "dW2": m.layers[1].weight.grad, "db1": m.layers[0].bias.grad,
+           "db2": m.layers[1].bias.grad}
+    want = {"dW1": dw1, "dW2": dw2, "db1": db1, "db2": db2}
+    for name in got:
+        assert _rel(got[name].cpu().numpy(), want[name]) < 1e-3, name
 
 
 def test_relu_grad_fusion_kernels(cuda):

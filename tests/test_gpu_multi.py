@@ -36,13 +36,16 @@ def _worker(rank, world, port, out_dir, balance, scale_mode, transport="nccl"):
     logits = model(x)
     loss = F.cross_entropy(logits, y, reduction="sum") / n
     loss.backward()
-    allreduce_grads(model)
+    allreduce_grads(model, peer=dg.peer)
+    if dg.peer is not None:
+        dg.peer.raise_if_expired()
     lt = loss.detach().clone()
     dist.all_reduce(lt)
     torch.save({"logits": logits.detach().cpu(), "ids": dg.local_ids.cpu(), "loss": lt.cpu(),
                 "grads": [p.grad.cpu() for p in model.parameters()],
                 "peer_status": dg.peer.status() if dg.peer is not None else 0}, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
+    dg.close()
     dist.destroy_process_group()
 
 

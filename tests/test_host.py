@@ -269,3 +269,51 @@ def test_rendezvous_protocol_model():
     for e in range(rounds):
         want = max(values[r][e] for r in range(world))
         assert all(results[r][e] == want for r in range(world))
+
+
+def test_reference_import_names_resolve_to_one_copy_of_each_module():
+    """The reference's scripts do `from cuda.kernels import *` and call `cuda_kernels.get_scale`
+    (evaluation/test_fuse.py:48-49, evaluation/SPMM_broadcast.py:15); after install_as_cuda() those names are the same
+    objects as tango_b200's, and a setting made through one name is seen through the other."""
+    import importlib
+    import sys
+    import tango_b200
+    tango_b200.install_as_cuda()
+    try:
+        ns = {}
+        exec("from cuda.kernels import *\nfrom cuda.QLinear import QLinear, Qlinear_func, Qlinear_func_reduce\n"
+             "from cuda.SPMM import spmm_copy_u, spmm_u_mul_e\nfrom cuda.SDDMM import sddmm_u_add_v\n"
+             "from cuda.util import graph_preprocess\nimport cuda, cuda.config", ns)
+        assert ns["cuda"] is tango_b200
+        assert ns["cuda_kernels"] is tango_b200.kernels.cuda_kernels
+        assert ns["cuda_kernels"].get_scale is tango_b200.kernels._get_scale
+        for name in ("quantize", "mySDDMM_int8", "QGEMM_forward", "QGEMM_backward", "transpose_quant",
+                     "multi_cusparse_SPMM", "incidence_SPMM", "csr_SPMM", "multi_cusparse_SPMV"):
+            assert ns[name] is getattr(tango_b200.kernels, name), name
+        assert ns["QLinear"] is tango_b200.QLinear and ns["spmm_copy_u"] is tango_b200.spmm_copy_u
+        assert ns["sddmm_u_add_v"] is tango_b200.sddmm_u_add_v and ns["graph_preprocess"] is tango_b200.graph_preprocess
+        assert importlib.import_module("cuda.kernels") is tango_b200.kernels
+        assert importlib.import_module("cuda.QLinear") is sys.modules["tango_b200.QLinear"]
+        old = config.get_rounding()
+        try:
+            ns["cuda"].config.set_rounding("stochastic", seed=5)
+            assert tango_b200.config.get_rounding() == "stochastic" and tango_b200.config.seed() == 5
+            assert sys.modules["cuda.config"].mode_for("quantize") == tango_b200.kernels.ROUND_STOCHASTIC
+        finally:
+            config.set_rounding(old)
+    finally:
+        for k in [k for k in sys.modules if k == "cuda" or k.startswith("cuda.")]:
+            if sys.modules[k] is tango_b200 or getattr(sys.modules[k], "__name__", "").startswith("tango_b200"):
+                del sys.modules[k]
+
+
+def test_dw_workspace_query_saturates_instead_of_wrapping():
+    from tango_b200 import _lib
+    L = _lib.lib
+    assert L.tango_qgemm_dw_workspace_bytes(256, 602) == 256 * 604 * 4
+    big = 2 ** 62
+    assert L.tango_qgemm_dw_workspace_bytes(big, big) == 2 ** 63 - 1
+    assert L.tango_qgemm_dw_workspace_bytes(3, 2 ** 63 - 2) == 2 ** 63 - 1
+    # the entry point with built-in scratch refuses such sizes before any CUDA call
+    assert L.tango_qgemm_dw_noalloc(None, 16, None, 16, 8, 2 ** 31, 2 ** 31, None, None, None, 2 ** 31, None, None) == -5
+    assert L.tango_qgemm_dw_noalloc(None, 16, None, 16, 8, 2 ** 40, 4, None, None, None, 4, None, None) == -5

@@ -151,3 +151,85 @@ def test_edge_softmax_rows_sum_to_one():
     sums = np.zeros((30, 3))
     np.add.at(sums, dst, a)
     np.testing.assert_allclose(sums[np.diff(indptr) > 0], 1.0, rtol=1e-5)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# The oracle against outputs of the REFERENCE's own CUDA kernels (tests/golden/ref_fixtures*.npz, produced on a B200
+# by tests/golden/make_ref_fixtures.py from the module oracle/build_ref.py compiles out of the reference's sources
+# with the reference's flags).  The reference is built with --use_fast_math: its divisions are approximate and its
+# a*s + b*t contracts into a fused multiply-add, so where such an operation is involved the comparison allows what
+# that can change (stated per case); everything else must match bit for bit.
+# ----------------------------------------------------------------------------------------------------------------
+_REF_PATH = os.path.join(os.path.dirname(__file__), "golden", "ref_fixtures.npz")
+_REF_SP_PATH = os.path.join(os.path.dirname(__file__), "golden", "ref_fixtures_cusparse.npz")
+needs_ref = pytest.mark.skipif(not os.path.exists(_REF_PATH), reason="reference fixtures not generated")
+needs_ref_sp = pytest.mark.skipif(not os.path.exists(_REF_SP_PATH), reason="reference cuSPARSE fixtures not generated")
+
+
+def _ulps(a, b):
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    return np.abs(a.view(np.int32).astype(np.int64) - b.view(np.int32).astype(np.int64))
+
+
+@needs_ref
+def test_reference_get_scale_and_quantize():
+    r = np.load(_REF_PATH)
+    x, s_ref = r["q_x"], r["q_scale"][0]
+    # max|x| / 127 with an approximate division: within 2 ulp of the IEEE quotient
+    assert _ulps(s_ref, O.absmax_scale(x)).max() <= 2
+    # power-of-two scale: the reciprocal is exact in either arithmetic -> every code, ties included, must match
+    np.testing.assert_array_equal(O.quantize(x, np.float32(0.0625)), r["q_out_pow2"])
+    np.testing.assert_array_equal(O.quantize(r["q_ties_x"], np.float32(0.0625)), r["q_ties_out"])   # half to even
+    np.testing.assert_array_equal(C.quantize(r["q_ties_x"], 0.0625, 1), r["q_ties_out"])
+    # natural scale: x * (1/s) with an approximate reciprocal may land on the other side of a .5 boundary
+    q = O.quantize(x, s_ref).astype(np.int32)
+    diff = np.abs(q - r["q_out"].astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 2e-3
+
+
+@needs_ref
+def test_reference_transpose_quant():
+    r = np.load(_REF_PATH)
+    for tag in ("a", "b"):
+        x, s, out = r[f"tq_{tag}_x"], r[f"tq_{tag}_scale"][0], r[f"tq_{tag}_out"]
+        mine = O.transpose_quant(x, s).reshape(out.shape).astype(np.int32)
+        diff = np.abs(mine - out.astype(np.int32))
+        assert diff.max() <= 1 and (diff != 0).mean() < 2e-3
+
+
+@needs_ref
+def test_reference_sddmm():
+    r = np.load(_REF_PATH)
+    src, dst = r["sd_src"], r["sd_dst"]
+    for tag in ("h4d16", "h1d70", "h2d33"):
+        u, v, su, sv = r[f"sd_{tag}_u"], r[f"sd_{tag}_v"], r[f"sd_{tag}_su"][0], r[f"sd_{tag}_sv"][0]
+        mine = O.sddmm_dot(src, dst, u, v, su, sv)
+        np.testing.assert_array_equal(mine, r[f"sd_{tag}_out"][..., 0])           # int32 dot, one fp32 multiply
+        np.testing.assert_array_equal(C.sddmm_dot(src, dst, u, v, su, sv), r[f"sd_{tag}_out"][..., 0])
+        assert _ulps(r[f"sd_{tag}_scale_out"][0], O.absmax_scale(mine)).max() <= 2
+    u, v, su, sv = r["se_u"], r["se_v"], r["se_su"][0], r["se_sv"][0]
+    np.testing.assert_array_equal(O.sddmm_elementwise("mul", src, dst, u, v, su, sv), r["se_mul_out"][..., 0])
+    for op in ("add", "sub"):       # a*su + b*sv contracts into one FMA under fast-math: last-bit differences
+        np.testing.assert_allclose(O.sddmm_elementwise(op, src, dst, u, v, su, sv), r[f"se_{op}_out"][..., 0],
+                                   rtol=0, atol=2e-7 * 127 * 0.03)
+    assert _ulps(O.sddmm_elementwise("div", src, dst, u, v, su, sv), r["se_div_out"][..., 0]).max() <= 4
+
+
+@needs_ref
+def test_reference_backward_gemms():
+    r = np.load(_REF_PATH)
+    for tag in ("a", "b"):
+        dy, w, x = r[f"bg_{tag}_dy"], r[f"bg_{tag}_w"], r[f"bg_{tag}_x"]
+        sdy, sw, sx = r[f"bg_{tag}_sdy"][0], r[f"bg_{tag}_sw"][0], r[f"bg_{tag}_sx"][0]
+        np.testing.assert_array_equal(O.qgemm_backward_dx(dy, w, sdy, sw), r[f"bg_{tag}_dx"])
+        np.testing.assert_array_equal(O.qgemm_backward_dw(dy, x, sdy, sx), r[f"bg_{tag}_dw"])
+
+
+@needs_ref_sp
+def test_reference_cusparse_spmm():
+    r = np.load(_REF_SP_PATH)
+    indptr, indices, sc = r["sp_indptr"], r["sp_indices"], r["sp_scale"][0]
+    # the library accumulates in fp32 (sums stay below 2^24 here, so exactly) and applies alpha once
+    np.testing.assert_array_equal(O.spmm_copy_u(indptr, indices, r["sp_nq"], sc), r["sp_copy_u_out"])
+    eq = np.ascontiguousarray(r["sp_e_t"][:, 0, :].T)          # [nnz, H], already in slot order
+    np.testing.assert_array_equal(O.spmm_u_mul_e(indptr, indices, None, r["sp_n3"], eq, sc), r["sp_u_mul_e_out"])
