@@ -228,6 +228,7 @@ def run_ours(args):
     name = args.workload
     n, _, in_feats, hidden, classes, _ = WORKLOADS[name]
     T.config.set_rounding(args.rounding, seed=1234)
+    T.config.set_hub_block(args.hub_block)
     step_counter = None
     if args.rounding == "stochastic":
         # read by the quantizers on the device, bumped inside the step: every replay of the captured graph rounds anew
@@ -411,9 +412,13 @@ def run_ours(args):
         torch.cuda.synchronize()
         k_ms = e0.elapsed_time(e1) / reps
         alg = n * hidden + 4 * n_edges + 4 * (n + 1) + 4 * n * hidden      # features + CSR + fp32 output, once each
-        touched = n_edges * hidden + 4 * n_edges + 4 * (n + 1) + 4 * n * hidden
+        hb = getattr(g, "_hubs", {}).get("csc")
+        e_gath = n_edges - (hb.n_block_edges if hb is not None else 0)     # edges that are still gathered one by one
+        touched = e_gath * hidden + 4 * e_gath + 4 * (n + 1) + 4 * n * hidden
         ach = alg / (k_ms * 1e-3) / 1e9
-        roof = {"kernel": "spmm_kernel<16,copy_u> F=256 (layer-1 aggregation)", "bound": "hbm", "achieved": ach,
+        roof = {"kernel": "layer-1 aggregation F=256: spmm_kernel<16,copy_u> on the gathered edges"
+                          + (" + int8 tensor-core product of the dense hub block" if getattr(g, "_hubs", None) else ""),
+                "bound": "hbm", "achieved": ach,
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                 "traffic": 397_105_920 + 4 * max(0, n_edges - 20_232_965),
                 "traffic_source": "derived, not measured in this run: dram__bytes_read+write of the ncu capture in "
@@ -463,13 +468,36 @@ def run_ours(args):
     cpu_base = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline and not name.startswith("gat"):
         cpu_base = _cpu_baseline(name, g, model)
+    used_graph = graph is not None
+    hub_info = None
+    if world == 1 and getattr(g, "_hubs", None):
+        hb = g._hubs.get("csc")
+        hub_info = {"side": int(hb.dense.shape[0]), "edges_in_block": hb.n_block_edges,
+                    "share_of_edges": hb.n_block_edges / n_edges, "density": hb.density}
     secondary = None
     if world == 1 and not args.no_secondary and name == "gcn_c5":
-        # outside the timed region: the GAT epoch on the same graph and the per-primitive numbers
+        # outside the timed region: the same epoch with every edge gathered (no dense hub block), the GAT epoch on
+        # the same graph and the per-primitive numbers
         graph = static_loss = None
+        secondary = {}
+        if getattr(g, "_hubs", None):
+            hubs, g._hubs = g._hubs, {}
+            for _ in range(3):
+                step(d_feats, d_labels)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                step(d_feats, d_labels)
+            e1.record()
+            torch.cuda.synchronize()
+            g._hubs = hubs
+            secondary["gcn_c5_every_edge_gathered"] = {"value": e0.elapsed_time(e1) / 5, "unit": "ms", "steps": 5,
+                                                       "cuda_graph": False,
+                                                       "note": "hub block off: identical results, gather kernels only"}
         del model, opt, d_feats, stage
         torch.cuda.empty_cache()
-        secondary = {"gat_c4": _gat_epoch(g, dev)}
+        secondary["gat_c4"] = _gat_epoch(g, dev)
         del g
         torch.cuda.empty_cache()
         secondary["primitives"] = run_primitives(args, quiet=True)
@@ -482,7 +510,7 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "s8", "data": "synthetic",
             "config": {"workload": name, "nodes": n, "edges": n_edges, "layers": f"{in_feats}-{hidden}-{classes}",
                        "rounding": args.rounding, "parallelism": f"row-partition x{world}", "scale_mode": args.scale_mode if world > 1 else "single", "balance": args.balance if world > 1 else "single", "transport": dg.transport if world > 1 else "single",
-                       "cuda_graph": graph is not None,
+                       "cuda_graph": used_graph, "hub_block": hub_info,
                        "timing": "CUDA events, inputs larger than L2 (no flush)"},
             "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": (h_feats.numel() * 4 + h_labels.numel() * 8),
                     "d2h_bytes_per_step": 4,
@@ -615,6 +643,35 @@ def run_case(args):
         torch.cuda.synchronize()
         print(json.dumps({"case": args.case, "nodes": n, "edges": g.num_edges(), "h": h, "d": d,
                           "checksum": float(out.double().sum())}))
+    elif args.case.startswith("c3_"):
+        # one primitive on the SpMM / SDDMM graph (169,343 nodes, 1,166,243 edges + self loops): c3_spmm_f128,
+        # c3_umule_f128, c3_sddmm_h4_f128, c3_incidence_w16, ...
+        parts = args.case.split("_")
+        g = rmat_graph(169_343, 1_166_243, 20243, device=dev)
+        T.graph_preprocess(g)
+        n, e = g.num_nodes(), g.num_edges()
+        kind = parts[1]
+        if kind == "incidence":
+            w = int(parts[2][1:])
+            zq, sz = K.quantize(torch.randn((e, w), device=dev), align=4)
+            fn = lambda: K.incidence_SPMM(g, zq, sz)
+        else:
+            f = int(parts[-1][1:])
+            q, s = K.quantize(torch.randn((n, f), device=dev))
+            if kind == "spmm":
+                fn = lambda: K.csr_SPMM(g, q, s)
+            elif kind == "umule":
+                eq, se = K.quantize(torch.rand((e, 4), device=dev), align=1)
+                fn = lambda: K.spmm_u_mul_e_int8(g, q.view(n, 4, f // 4), eq, s * se)
+            elif kind == "sddmm":
+                h = int(parts[2][1:])
+                fn = lambda: K.mySDDMM_int8(g, "dot", q.view(n, h, f // h), q.view(n, h, f // h), s, s, False)[0]
+            else:
+                raise SystemExit(f"unknown case {args.case}")
+        for _ in range(3):
+            out = fn()
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "nodes": n, "edges": e, "checksum": float(out.double().sum())}))
     elif args.case == "gemm":
         m, k, n = 65_536, 602, 256
         x, w, dy = torch.randn((m, k), device=dev), torch.randn((n, k), device=dev) * 0.04, torch.randn((m, n), device=dev)
@@ -722,6 +779,137 @@ def run_primitives(args, quiet: bool = False):
     return out_lines
 
 
+def run_dist_phases(args):
+    """Per-phase CUDA-event times of one row-partitioned training step (launch under torch.distributed.run like the
+    epoch benchmark): every phase of the step is run on its own, back to back `reps` times between two barriers, and
+    the maximum over the ranks is reported.  No profiler is involved.  Prints one JSON line on rank 0."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    import tango_b200 as T
+    from tango_b200 import config, kernels as K
+    from tango_b200.dist import (DistGCN, DistGraph, _aggregate, _agree_on_scale, _peer_table, _spmm_gathered,
+                                 allreduce_grads)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world > 1, "launch with torch.distributed.run"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    name = args.workload
+    n, _, in_feats, hidden, classes, _ = WORKLOADS[name]
+    g = build_graph(name, dev)
+    dg = DistGraph(g, rank, world, balance=args.balance, scale_mode="global", transport=args.transport)
+    del g
+    torch.cuda.empty_cache()
+    torch.manual_seed(6)
+    model = DistGCN(dg, in_feats, hidden, classes, 1).to(dev)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2, weight_decay=5e-4, capturable=True)
+    h_feats, h_labels = make_inputs(name, dg.local_ids.cpu(), False)
+    X, y = h_feats.to(dev), h_labels.to(dev)
+    nl = dg.n_local
+    mode, seed = config.mode_for("quantize"), config.seed()
+    H1 = torch.randn((nl, hidden), device=dev)
+    H2 = torch.randn((nl, classes), device=dev)
+    W1, W2 = model.layers[0].weight.detach(), model.layers[1].weight.detach()
+    sc = K._get_scale(H1)
+    s2 = K._get_scale(H2)
+    reps = 20
+    res = {}
+
+    def timed(label, fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res[label] = round(float(t) * 1e3, 1)      # microseconds
+
+    def graphed(fn):
+        """Replays `fn` from a CUDA graph so that the host's launch overhead is not what is measured."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        gph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gph, capture_error_mode="thread_local"):
+            fn()
+        return gph.replay
+
+    peer = dg.peer
+    if peer is not None:
+        timed("rendezvous (scale agreement or barrier), one", graphed(lambda: peer.max_scalar(sc)))
+        for f, h, s_ in ((hidden, H1, sc), (classes, H2, s2)):
+            table, ptrs, ld = _peer_table(dg, dg.fwd, f)
+            timed(f"quantize + push to all GPUs, width {f}",
+                  graphed(lambda: peer.quantize_push(h, s_, ptrs, dg.rank * dg.shard_rows, ld, mode, seed, 0, dg.in_norm)))
+            timed(f"quantize + push + barrier, width {f}",
+                  graphed(lambda: (peer.quantize_push(h, s_, ptrs, dg.rank * dg.shard_rows, ld, mode, seed, 0, dg.in_norm),
+                                   peer.barrier())))
+            timed(f"aggregation forward, width {f}", graphed(lambda: _spmm_gathered(dg, dg.fwd, table, s_, f, dg.in_norm)))
+            tb, _, _ = _peer_table(dg, dg.bwd, f)
+            timed(f"aggregation backward, width {f}", graphed(lambda: _spmm_gathered(dg, dg.bwd, tb, s_, f)))
+    sX = K._get_scale(X, dg.out_norm)
+    timed("absmax of the features (602 wide, with the left norm)", graphed(lambda: K._get_scale(X, dg.out_norm)))
+    Xq, W1q = K.alloc_int8(X.shape, dev), K.alloc_int8(W1.shape, dev)
+    Hh = torch.empty((nl, hidden), device=dev)
+    sH = torch.zeros(1, device=dev)
+    sW1 = K._get_scale(W1)
+    timed("layer-1 forward GEMM (quantize X, W + GEMM + output scale)",
+          graphed(lambda: K._qgemm_forward(Hh, X, Xq, W1, W1q, None, sH, sX, sW1, 0, 0, 0, dg.out_norm)))
+    dHq, sdH = K.quantize(H1)
+    timed("absmax + quantize of a 256-wide gradient", graphed(lambda: K.quantize(H1)))
+    timed("layer-1 dW GEMM", graphed(lambda: K.QGEMM_backward(dHq, Xq, W1q, sdH, sX, sW1, False, True)))
+    X2q, W2q = K.alloc_int8((nl, hidden), dev), K.alloc_int8(W2.shape, dev)
+    sX2, sW2 = K._get_scale(H1), K._get_scale(W2)
+    H2o = torch.empty((nl, classes), device=dev)
+    timed("layer-2 forward GEMM", graphed(lambda: K._qgemm_forward(H2o, H1, X2q, W2, W2q, None, sH, sX2, sW2, 0, 0, 0, dg.out_norm)))
+    d2q, sd2 = K.quantize(H2)
+    timed("layer-2 dX + dW GEMMs", graphed(lambda: K.QGEMM_backward(d2q, X2q, W2q, sd2, sX2, sW2, True, True, dg.out_norm)))
+    timed("ReLU-gradient statistics + quantize (256 wide)",
+          graphed(lambda: K.relu_grad_quantize(H1, Hh, dg.in_norm, True, mode, seed, 0)))
+    logits = torch.randn((nl, classes), device=dev, requires_grad=True)
+
+    def loss_fb():
+        logits.grad = None
+        (F.cross_entropy(logits, y, reduction="none").sum() / n).backward()
+    timed("loss forward + backward", graphed(loss_fb))
+    for p_ in model.parameters():
+        p_.grad = torch.zeros_like(p_)
+    timed("gradient all-reduce (NCCL, one flat buffer)", graphed(lambda: allreduce_grads(model, peer=peer)))
+    timed("Adam update", graphed(opt.step))
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        loss = F.cross_entropy(model(X), y, reduction="none").sum() / n
+        loss.backward()
+        allreduce_grads(model, peer=peer)
+        opt.step()
+    K.launch_counter[0] = 0
+    replay = graphed(step)
+    launches = K.launch_counter[0] // 2
+    timed("whole step (CUDA graph)", replay)
+    if rank == 0:
+        print(json.dumps({"suite": "dist_phases", "n_gpus": world, "workload": name, "transport": dg.transport,
+                          "unit": "us, max over ranks, mean of %d back-to-back runs" % reps,
+                          "library_launches_per_step": launches, "phases": res}), flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dg.close()
+    dist.destroy_process_group()
+
+
 def _row_gather_peak(q, width):
     """GB/s at which tango_probe_row_gather reads random rows of the int8 table `q` (rows of `width` bytes)."""
     import ctypes
@@ -764,18 +952,22 @@ def main():
     ap.add_argument("--transport", default="auto", choices=["auto", "nccl", "peer"],
                     help="multi-GPU exchange: NCCL collectives, or stores into peer memory + rendezvous kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--hub-block", type=int, default=16384,
+                    help="side of the dense hub block of the unweighted aggregation (tensor cores); 0 = gather every edge")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the untimed extras of the 1-GPU line (GAT epoch, per-primitive numbers)")
     ap.add_argument("--scale-mode", default="global", choices=["global", "shard"],
                     help="multi-GPU: one quantisation scale agreed by all ranks, or one per shard")
     ap.add_argument("--balance", default="dealt", choices=["dealt", "cyclic", "nnz", "rows"], help="multi-GPU node placement")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of a CUDA graph")
-    ap.add_argument("--suite", default=None, choices=["primitives"],
+    ap.add_argument("--suite", default=None, choices=["primitives", "dist_phases"],
                     help="per-primitive numbers on the QLinear and SpMM/SDDMM configurations instead of the epoch")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, sddmm_rows, gemm) and exit")
     args = ap.parse_args()
     if args.suite == "primitives":
         run_primitives(args)
+    elif args.suite == "dist_phases":
+        run_dist_phases(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":

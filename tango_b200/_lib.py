@@ -30,6 +30,14 @@ class SpmmPlan(Structure):
         ("split_threshold", c_int32),
         ("row_order", c_void_p),
         ("n_long_rows", c_int64),
+        ("dense_a", c_void_p),
+        ("dense_lda", c_int64),
+        ("dense_rows", c_int64),
+        ("dense_cols", c_void_p),
+        ("dense_n_cols", c_int64),
+        ("dense_b", c_void_p),
+        ("dense_status", c_void_p),
+        ("n_skip_rows", c_int64),
     ]
 
 

@@ -8,7 +8,8 @@ from __future__ import annotations
 
 from ._lib import ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_TRUNC
 
-_state = {"rounding": "reference", "seed": 0, "share_quantized_inputs": False, "step_counter": None}
+_state = {"rounding": "reference", "seed": 0, "share_quantized_inputs": False, "step_counter": None,
+          "hub_block": 16384}
 
 
 def set_rounding(mode: str = "reference", seed: int = 0) -> None:
@@ -63,3 +64,17 @@ def set_step_counter(counter) -> None:
 
 def step_counter():
     return _state["step_counter"]
+
+
+def set_hub_block(side: int) -> None:
+    """Side length (rows = columns) of the dense hub block that graph_preprocess builds for the unweighted
+    aggregation on large power-law graphs; 0 switches it off (every edge is gathered, as the reference's CSR SpMM
+    does).  Results are bit-identical either way: the block's product is an exact int32 sum like the gathered one.
+    Applies to graphs preprocessed after the call."""
+    if side < 0:
+        raise ValueError(side)
+    _state["hub_block"] = int(side)
+
+
+def hub_block() -> int:
+    return _state["hub_block"]

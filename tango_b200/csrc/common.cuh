@@ -61,6 +61,12 @@ __device__ __forceinline__ float inv_scale(float s) {
     return isinf(inv) ? 0.f : inv;
 }
 
+// Internal (not exported): ws[r, c] += sum_k a[r, k] * b[k, c] as exact int32 with the tcgen05 int8 GEMM, integer
+// atomics into ws.  a is [m, lda] (reduction contiguous), b is [k, ldb] (reduction index = row), both 16-byte aligned
+// with leading dimensions that are multiples of 16.  Defined in igemm_tcgen05.cu, used by the SpMM's dense hub block.
+int igemm_accumulate_i32(const int8_t *a, int64_t lda, const int8_t *b, int64_t ldb, int64_t m, int64_t n, int64_t k,
+                         int32_t *ws, int64_t ldws, int *status, cudaStream_t stream);
+
 // ---------------------------------------------------------------------------------------------- Philox4x32-10
 struct Philox {
     uint32_t k0, k1;

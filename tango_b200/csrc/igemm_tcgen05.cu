@@ -49,6 +49,7 @@ struct GemmParams {
     float *absmax;
     int *status;
     uint32_t tmem_cols;
+    int tma_store;   // persistent kernel: the epilogue hands 32 x 16 fp32 boxes to the TMA engine (needs ldo % 4 == 0)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -101,6 +102,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+
+// Bulk tensor store shared -> global (this GPU's memory only) of one box, tracked by the issuing thread's bulk
+// async-group; wait_read returns once the engine has read the shared-memory source of every committed store,
+// wait_all once the stores have been performed.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
 // Bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
@@ -364,7 +379,7 @@ constexpr int kStageLd = 16;  // words per staged epilogue row (16 columns, no p
 
 __global__ void __launch_bounds__(320, 1)
 igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                        const GemmParams p) {
+                        const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_a_full[kMaxStages];
     __shared__ __align__(8) uint64_t bar_a_empty[kMaxStages];
@@ -517,6 +532,26 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
                     if (want_max && row < p.M && (full_cols || col0 + i < p.N)) amax = fmaxf(amax, fabsf(v));
                     r[i] = __float_as_uint(v);
                 }
+                if (p.tma_store) {
+                    // The 32 x 16 fp32 box goes out as ONE bulk tensor store: lane = row writes its 64 bytes into the
+                    // warp's tile in the 64-byte swizzle the tensor map expects (16-byte chunk c of row r sits at chunk
+                    // c ^ ((r >> 1) & 3): conflict-free for a quarter warp), the writes are made visible to the async
+                    // proxy, and lane 0 issues the store.  Rows >= M and columns >= N are clipped by the tensor map.
+                    // The tile is rewritten only after the engine has read the previous box.
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+                    const uint32_t row_addr = smem_u32(tile) + (uint32_t)lane * 64u;
+                    const uint32_t sw = ((uint32_t)lane >> 1) & 3u;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)i ^ sw) << 4)),
+                                     "r"(r[4 * i]), "r"(r[4 * i + 1]), "r"(r[4 * i + 2]), "r"(r[4 * i + 3])
+                                     : "memory");
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) tma_store_2d(&tm_out, smem_u32(tile), col0, m0 + q * 32);
+                    continue;
+                }
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
                     *reinterpret_cast<uint4 *>(tile + lane * kStageLd + 4 * i) =
@@ -566,6 +601,7 @@ igemm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             if (lane == 0)
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_acc_empty[buf])) : "memory");
         }
+        if (p.tma_store && lane == 0) tma_store_wait_all();   // this lane's bulk stores, before shared memory goes away
         if (p.absmax) {
             amax = warp_max(amax);
             if (lane == 0 && amax > 0.f) {
@@ -638,6 +674,25 @@ static int make_map(CUtensorMap *map, const void *base, int64_t inner, int64_t o
     return TANGO_OK;
 }
 
+// 2-D fp32 tensor map over the row-major output [rows, cols] (leading dimension ld floats) for the epilogue's bulk
+// stores: boxes of 32 rows x 16 columns, 64-byte swizzle.
+static int make_out_map(CUtensorMap *map, const float *base, int64_t cols, int64_t rows, int64_t ld) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return TANGO_ECUDA;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+    cuuint32_t box[2] = {16, 32};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = (int)r;
+        return TANGO_ECUDA;
+    }
+    return TANGO_OK;
+}
+
 struct GemmCall {
     const int8_t *a; int64_t lda; int a_mn;
     const int8_t *b; int64_t ldb; int b_mn;
@@ -646,6 +701,7 @@ struct GemmCall {
     float *out; int64_t ldo; int32_t *ws; int64_t ldws;
     const float *sa, *sb, *bias; float *absmax; int *status;
     const float *out_row_scale = nullptr;
+    int pipeline_bytes = 98304;   // shared memory for the TMA ring of igemm_kernel (98304 lets two CTAs share an SM)
 };
 
 static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
@@ -665,7 +721,7 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
     p.b_boxes = c.b_mn ? (int)ceil_div(p.n_tile, 128) : 1;
     p.b_bytes = c.b_mn ? p.b_boxes * kABytes : (int)round_up((int64_t)p.n_tile * kBlockK, 1024);
     const int stage_bytes = kABytes + p.b_bytes;
-    p.stages = 98304 / stage_bytes;
+    p.stages = c.pipeline_bytes / stage_bytes;
     if (p.stages < 2) p.stages = 2;
     if (p.stages > 6) p.stages = 6;
     p.mode = c.mode; p.out = c.out; p.ldo = c.ldo; p.ws = c.ws; p.ldws = c.ldws;
@@ -699,6 +755,12 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
             uint32_t cols = 32;
             while ((int)cols < p.n_tile) cols <<= 1;
             pp.tmem_cols = cols * 2;
+            CUtensorMap tm_out = tm_a;   // placeholder when the bulk-store path is off (never dereferenced then)
+            pp.tma_store = (c.ldo % 4 == 0 && aligned(c.out, 16)) ? 1 : 0;
+            if (pp.tma_store) {
+                rc = make_out_map(&tm_out, c.out, c.N, c.M, c.ldo);
+                if (rc) return rc;
+            }
             const size_t smem_p = (size_t)(1024 + b_res + st * kABytes + staging);
             TANGO_CUDA_TRY(cudaFuncSetAttribute(igemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 (int)(227 * 1024 - 1024)));
@@ -708,7 +770,7 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
             if (gx > m_tiles) gx = m_tiles;
             const dim3 pgrid((unsigned)gx, (unsigned)n_tiles, 1);
             if (pgrid.y > 65535) return TANGO_ESIZE;
-            igemm_persistent_kernel<<<pgrid, 320, smem_p, stream>>>(tm_a, tm_b, pp);
+            igemm_persistent_kernel<<<pgrid, 320, smem_p, stream>>>(tm_a, tm_b, tm_out, pp);
             TANGO_LAUNCH_CHECK();
             return TANGO_OK;
         }
@@ -721,6 +783,20 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
     igemm_kernel<<<grid, 192, smem, stream>>>(tm_a, tm_b, p);
     TANGO_LAUNCH_CHECK();
     return TANGO_OK;
+}
+
+int igemm_accumulate_i32(const int8_t *a, int64_t lda, const int8_t *b, int64_t ldb, int64_t m, int64_t n, int64_t k,
+                         int32_t *ws, int64_t ldws, int *status, cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || k <= 0) return TANGO_OK;
+    // D[m, n] += A[m, k] . B[k, n]: A K-major, B stored with the reduction index as its row; two splits of the
+    // reduction when one wave of tiles would leave SMs idle
+    const int64_t tiles = ceil_div(m, kTileM) * ceil_div(n, 256);
+    int splits = (int)(kNumSMs / (tiles > 0 ? tiles : 1));
+    if (splits < 1) splits = 1;
+    if (splits > 4) splits = 4;
+    GemmCall c{a, lda, 0, b, ldb, 1, m, n, k, 1, splits, nullptr, 0, ws, ldws, nullptr, nullptr, nullptr, nullptr, status};
+    c.pipeline_bytes = 196608;    // one CTA per SM: a deeper ring instead of a second resident CTA
+    return launch_gemm(c, stream);
 }
 
 }  // namespace tango

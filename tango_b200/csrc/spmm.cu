@@ -490,6 +490,19 @@ __global__ void __launch_bounds__(256) spmm_finalize_kernel(const SpmmArgs a) {
     }
 }
 
+// Packs the feature rows ids[0..n) of `src` ([*, ld] int8, ld a multiple of 16) into dst [n, ld]: the B operand of
+// the dense hub block.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const int8_t *__restrict__ src, int64_t ld,
+                                                          const int32_t *__restrict__ ids, int64_t n,
+                                                          int8_t *__restrict__ dst) {
+    const int64_t pieces = ld >> 4, total = n * pieces;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / pieces, c = i - r * pieces;
+        reinterpret_cast<uint4 *>(dst + r * ld)[c] =
+            __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)__ldg(ids + r) * ld) + c);
+    }
+}
+
 static int pow2_ceil(int x) {
     int p = 1;
     while (p < x) p <<= 1;
@@ -510,6 +523,46 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
         a.n_heavy = plan->n_heavy; a.ws = plan->ws; a.ws_ld = plan->ws_ld; a.split_threshold = plan->split_threshold;
         TANGO_CUDA_TRY(cudaMemsetAsync(a.ws, 0, sizeof(int32_t) * (size_t)(a.n_heavy * a.nseg * a.ws_ld), stream));
     }
+    const bool dense = plan && plan->dense_a && plan->dense_rows > 0 && plan->dense_n_cols > 0;
+    if (dense) {
+        // dense hub block: pack the block's feature rows, multiply on the tensor cores, add into the heavy rows'
+        // int32 scratch (cleared above); the gather kernels below then cover only the edges outside the block
+        if (MODE != MODE_COPY || a.nseg != 1 || plan->n_units < 0 || !plan->heavy_rows || !plan->ws ||
+            plan->dense_rows > plan->n_heavy || !plan->dense_cols || !plan->dense_b || plan->dense_lda < plan->dense_n_cols ||
+            plan->n_skip_rows != plan->n_heavy || !plan->row_order || plan->ws_ld < a.f)
+            return TANGO_EINVAL;
+        if (a.ld % 16 || !aligned(a.feat, 16) || plan->dense_lda % 16 || plan->dense_n_cols % 16 ||
+            !aligned(plan->dense_a, 16) || !aligned(plan->dense_b, 16))
+            return TANGO_EALIGN;
+        if (plan->n_units == 0) {      // no unit set the scratch fields above
+            a.heavy_rows = plan->heavy_rows; a.n_heavy = plan->n_heavy; a.ws = plan->ws; a.ws_ld = plan->ws_ld;
+            a.split_threshold = plan->split_threshold;
+            TANGO_CUDA_TRY(cudaMemsetAsync(a.ws, 0, sizeof(int32_t) * (size_t)(a.n_heavy * a.ws_ld), stream));
+        }
+        const int64_t ldb = round_up(a.f, 16);
+        if (ldb > a.ld) return TANGO_EINVAL;
+        {
+            const int64_t pieces = plan->dense_n_cols * (ldb >> 4);
+            int64_t gb = ceil_div(pieces, 256);
+            if (gb > kNumSMs * 8) gb = kNumSMs * 8;
+            if (ldb == a.ld) {
+                gather_rows_kernel<<<(unsigned)gb, 256, 0, stream>>>(a.feat, a.ld, plan->dense_cols, plan->dense_n_cols,
+                                                                    plan->dense_b);
+            } else {
+                return TANGO_EINVAL;   // feature rows wider than their padded width: not a layout the quantizers make
+            }
+            TANGO_LAUNCH_CHECK();
+        }
+        const int rc = igemm_accumulate_i32(plan->dense_a, plan->dense_lda, plan->dense_b, ldb, plan->dense_rows, a.f,
+                                            plan->dense_n_cols, a.ws, a.ws_ld, plan->dense_status, stream);
+        if (rc) return rc;
+    }
+    if (plan && plan->n_skip_rows > 0) {
+        // the leading rows of row_order belong to units + finalize: the row kernels start after them
+        if (!plan->row_order || plan->n_skip_rows > a.n_rows || plan->n_long_rows < plan->n_skip_rows) return TANGO_EINVAL;
+        a.row_order = plan->row_order + plan->n_skip_rows;
+        a.n_rows -= plan->n_skip_rows;
+    }
     if (MODE == MODE_WEIGHT_LANE && a.H == 1) a.D = 1 << 20;  // one head: every byte shares the weight
     int vec = 1;
     if (a.ld % 16 == 0 && aligned(a.feat, 16)) vec = 16;
@@ -528,9 +581,11 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
     }
     // short rows (the tail of the degree-sorted order) go to the lane-group kernel when one pass of G lanes covers a row
     const bool four = vec >= 4 && !(MODE == MODE_WEIGHT_LANE && (a.D % vec) != 0);
-    if (plan && plan->row_order && plan->n_long_rows >= 0 && plan->n_long_rows <= a.n_rows && four &&
+    const int64_t n_skip = plan ? plan->n_skip_rows : 0;
+    if (plan && plan->row_order && plan->n_long_rows >= n_skip && plan->n_long_rows - n_skip <= a.n_rows && four &&
         a.f_pad <= 32 * vec)
-        a.n_long = plan->n_long_rows;
+        a.n_long = plan->n_long_rows - n_skip;
+    else if (n_skip > 0) a.n_long = a.n_rows;
     const int64_t warps = a.n_units + a.n_long;
     const int64_t blocks = ceil_div(warps, kSpmmThreads / 32);
     if (blocks > 0x7fffffff) return TANGO_ESIZE;
@@ -559,7 +614,7 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
         else spmm_short_kernel<4, MODE><<<(unsigned)sb, 128, 0, stream>>>(a);
         TANGO_LAUNCH_CHECK();
     }
-    if (a.n_units > 0) {
+    if (a.n_units > 0 || dense) {
         const int64_t fb = ceil_div(a.n_heavy * a.f, 256);
         spmm_finalize_kernel<<<(unsigned)fb, 256, 0, stream>>>(a);
         TANGO_LAUNCH_CHECK();

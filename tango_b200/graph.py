@@ -243,10 +243,14 @@ UNIT_NNZ = 2048
 
 class SpmmSchedule:
     """Device arrays consumed by the SpMM kernels: `units` [n_units, 4] = (segment row, begin, end, scratch slot)
-    for every slice of a row longer than the threshold, and `heavy_rows` = those rows."""
+    for every slice of a row longer than the threshold, and `heavy_rows` = those rows.
+
+    force_heavy (optional, nseg == 1): row ids that are finished through the int32 scratch whatever their length (the
+    rows of a dense hub block, in the block's row order); they come first in `heavy_rows`, every heavy row comes
+    first in `row_order`, and `n_skip` = n_heavy tells the row kernels to start after them."""
 
     def __init__(self, indptr: torch.Tensor, nseg: int = 1, threshold: Optional[int] = None,
-                 unit: Optional[int] = None):
+                 unit: Optional[int] = None, force_heavy: Optional[torch.Tensor] = None):
         if threshold is None:
             # A row is worked on by one warp, neighbour batch after neighbour batch, so the longest unsplit row sets
             # the critical path of the kernel.  Keep it short relative to the total work: about nnz / 16384 (one
@@ -262,12 +266,27 @@ class SpmmSchedule:
         n_rows = (indptr.numel() - 1) // nseg
         ip = indptr.long()
         row_deg = ip[nseg::nseg] - ip[:-1:nseg][:n_rows] if nseg > 1 else ip[1:] - ip[:-1]
-        # rows in order of decreasing length: the warps of a CTA then work on rows of similar length and the
-        # longest rows start first
-        self.row_order = torch.argsort(row_deg, descending=True, stable=True).to(torch.int32)
-        self.n_long = int((row_deg > SHORT_ROW_NNZ).sum())
+        self.n_skip = 0
+        if force_heavy is None:
+            # rows in order of decreasing length: the warps of a CTA then work on rows of similar length and the
+            # longest rows start first
+            self.row_order = torch.argsort(row_deg, descending=True, stable=True).to(torch.int32)
+            self.n_long = int((row_deg > SHORT_ROW_NNZ).sum())
+            heavy = torch.nonzero(row_deg > threshold).flatten()
+        else:
+            assert nseg == 1
+            forced = force_heavy.long()
+            is_forced = torch.zeros(n_rows, dtype=torch.bool, device=indptr.device)
+            is_forced[forced] = True
+            heavy = torch.cat([forced, torch.nonzero((row_deg > threshold) & ~is_forced).flatten()])
+            is_heavy = is_forced.clone()
+            is_heavy[heavy] = True
+            rest = torch.nonzero(~is_heavy).flatten()
+            rest = rest[torch.argsort(row_deg[rest], descending=True, stable=True)]
+            self.row_order = torch.cat([heavy, rest]).to(torch.int32)
+            self.n_skip = int(heavy.numel())
+            self.n_long = self.n_skip + int((row_deg[rest] > SHORT_ROW_NNZ).sum())
         self.n_block_rows = int((row_deg > BLOCK_ROW_NNZ).sum())   # rows that deserve a whole CTA in row-team kernels
-        heavy = torch.nonzero(row_deg > threshold).flatten()
         self.n_heavy = int(heavy.numel())
         self.heavy_rows = heavy.to(torch.int32)
         if self.n_heavy == 0:
@@ -288,6 +307,62 @@ class SpmmSchedule:
         # longest slices first
         self.units = units.to(torch.int32).contiguous()
         self.n_units = int(self.units.shape[0])
+
+
+HUB_BLOCK_MIN_DENSITY = 0.04   # below this a dense int8 product costs more than gathering the block's edges
+
+
+class HubBlock:
+    """The dense hub block of an aggregation matrix (CSR-like `indptr`, `indices` over `n_cols` feature rows): its
+    `rows` (the block_rows longest rows) x `cols` (the block_cols most referenced columns) sub-matrix as a dense int8
+    0/1 array `dense` [rows, cols], the remaining edges as a CSR of their own (`indptr`, `indices`: every edge of the
+    matrix is in exactly one of the two), and the row schedule of that remainder with the block's rows forced through
+    the int32 scratch, where the tensor-core product of the block and the gathered remainder meet.
+
+    On the power-law graphs this library trains on, 7 % of the rows x 7 % of the columns hold 44 % of the edges at a
+    density of 19 %: multiplying that block as a dense matrix replaces 50 M 256-byte gathers through L2 with a
+    16384 x 16384 x 256 int8 product.  Exact int32 either way, so results do not change by a bit."""
+
+    def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, n_cols: int, block_rows: int = 16384,
+                 block_cols: int = 16384, min_density: float = HUB_BLOCK_MIN_DENSITY):
+        dev = indptr.device
+        ip = indptr.long()
+        n_rows = ip.numel() - 1
+        row_deg = ip[1:] - ip[:-1]
+        kr = min(block_rows, n_rows) // 128 * 128
+        ks = min(block_cols, n_cols) // 128 * 128
+        self.ok = False
+        if kr <= 0 or ks <= 0:
+            return
+        col_deg = torch.bincount(indices.long(), minlength=n_cols)
+        rows = torch.argsort(row_deg, descending=True, stable=True)[:kr]
+        cols = torch.argsort(col_deg, descending=True, stable=True)[:ks]
+        row_slot = torch.full((n_rows,), -1, dtype=torch.int64, device=dev)
+        row_slot[rows] = torch.arange(kr, device=dev)
+        col_pos = torch.full((n_cols,), -1, dtype=torch.int64, device=dev)
+        col_pos[cols] = torch.arange(ks, device=dev)
+        edge_row = torch.repeat_interleave(torch.arange(n_rows, device=dev), row_deg)
+        rs, cp = row_slot[edge_row], col_pos[indices.long()]
+        in_blk = (rs >= 0) & (cp >= 0)
+        self.n_block_edges = int(in_blk.sum())
+        self.density = self.n_block_edges / float(kr * ks)
+        if self.density < min_density:
+            return
+        dense = torch.zeros(kr * ks, dtype=torch.int8, device=dev)
+        dense.index_put_((rs[in_blk] * ks + cp[in_blk],), torch.ones(1, dtype=torch.int8, device=dev).expand(
+            self.n_block_edges), accumulate=True)            # multiplicity (1 on a simple graph)
+        self.dense = dense.view(kr, ks)
+        keep = ~in_blk
+        self.indices = indices[keep].contiguous()
+        tail_deg = row_deg - torch.bincount(edge_row[in_blk], minlength=n_rows)
+        tip = torch.zeros(n_rows + 1, dtype=torch.int64, device=dev)
+        torch.cumsum(tail_deg, 0, out=tip[1:])
+        self.indptr = tip.to(torch.int32)
+        self.rows = rows.to(torch.int32)
+        self.cols = cols.to(torch.int32).contiguous()
+        self.schedule = SpmmSchedule(self.indptr, force_heavy=rows)
+        self.schedule.hub = self
+        self.ok = True
 
 
 def balanced_bounds(weights: torch.Tensor, world: int):

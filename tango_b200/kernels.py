@@ -238,14 +238,23 @@ def _make_plan(sched: Optional[SpmmSchedule], f: int, device):
     order = getattr(sched, "row_order", None)
     order_ptr = order.data_ptr() if order is not None and order.numel() else None
     n_long = getattr(sched, "n_long", -1) if order_ptr else -1
-    if sched.n_units == 0:
+    hub = getattr(sched, "hub", None)
+    if sched.n_heavy == 0:
         plan = SpmmPlan(None, 0, None, 0, None, 0, sched.threshold, order_ptr, n_long)
         return ctypes.byref(plan), (plan,)
     ws_ld = _round_up(f, 16)
     ws = torch.empty((sched.n_heavy * sched.nseg, ws_ld), dtype=torch.int32, device=device)
-    plan = SpmmPlan(sched.units.data_ptr(), sched.n_units, sched.heavy_rows.data_ptr(), sched.n_heavy, ws.data_ptr(),
-                    ws_ld, sched.threshold, order_ptr, n_long)
-    return ctypes.byref(plan), (plan, ws)
+    plan = SpmmPlan(sched.units.data_ptr() if sched.n_units else None, sched.n_units, sched.heavy_rows.data_ptr(),
+                    sched.n_heavy, ws.data_ptr(), ws_ld, sched.threshold, order_ptr, n_long)
+    keep = [plan, ws]
+    if hub is not None:
+        packed = torch.empty((hub.cols.numel(), ws_ld), dtype=torch.int8, device=device)
+        plan.dense_a, plan.dense_lda, plan.dense_rows = hub.dense.data_ptr(), hub.dense.stride(0), hub.dense.shape[0]
+        plan.dense_cols, plan.dense_n_cols = hub.cols.data_ptr(), hub.cols.numel()
+        plan.dense_b, plan.dense_status = packed.data_ptr(), _status_word(device).data_ptr()
+        plan.n_skip_rows = sched.n_skip
+        keep.append(packed)
+    return ctypes.byref(plan), tuple(keep)
 
 
 def _csr_spmm(out, indptr, indices, U, scaleU, sched=None, nseg=1, row_scale=None, bias=None, relu=False,
@@ -257,7 +266,9 @@ def _csr_spmm(out, indptr, indices, U, scaleU, sched=None, nseg=1, row_scale=Non
     with torch.cuda.device(U.device):
         check(lib.tango_spmm_copy_u(_p(indptr), _pi(indices), n_rows, nseg, _p(U), ldn, f, _p(scaleU), _p(row_scale),
                                     _p(bias), int(relu), _p(out), ldo, _p(out_absmax), plan, _stream()), "csr_SPMM")
-    launch_counter[0] += 1 + (sched is not None and sched.n_units > 0) + (sched is not None and sched.n_long < sched.row_order.numel())
+    launch_counter[0] += (1 + (sched is not None and sched.n_heavy > 0)
+                          + (sched is not None and sched.n_long < sched.row_order.numel())
+                          + (2 if getattr(sched, "hub", None) is not None else 0))
     del keep
 
 
@@ -524,10 +535,15 @@ def incidence_SPMM(g, E, scaleE, reverse=False):
 def csr_SPMM(g, N, scaleN, reverse=False, row_scale=None, bias=None, relu=False, out_absmax=None):
     """cuda/kernels.py:154-165; the keyword arguments fuse out = act(out * row_scale[:,None] + bias)."""
     indptr, indices, _ = g.adj_csr if reverse else g.adj_csc
+    sched = _schedule(g, reverse)
     out_shape = (g.num_nodes(),) + N.shape[1:]
     dim = N.numel() // N.size(0)
     out = torch.empty((g.num_nodes(), dim), dtype=torch.float32, device=N.device)
-    _csr_spmm(out, indptr, indices, N, scaleN, _schedule(g, reverse), 1, row_scale, bias, relu, out_absmax)
+    hub = getattr(g, "_hubs", {}).get("csr" if reverse else "csc")
+    if hub is not None and N.dim() >= 2 and N.stride(0) % 16 == 0 and N.stride(0) == _round_up(dim, 16):
+        # dense hub block on the tensor cores + the edges outside it through the gather kernels
+        indptr, indices, sched = hub.indptr, hub.indices, hub.schedule
+    _csr_spmm(out, indptr, indices, N, scaleN, sched, 1, row_scale, bias, relu, out_absmax)
     return out.view(out_shape)
 
 

@@ -1,14 +1,28 @@
 """graph_preprocess of the reference's cuda/util.py:5-11, for the DGL-free `Graph`."""
 from __future__ import annotations
 
-from .graph import Graph, SpmmSchedule
+from . import config
+from .graph import HUB_BLOCK_MIN_DENSITY, Graph, HubBlock, SpmmSchedule
+
+HUB_BLOCK_MIN_EDGES = 4_000_000     # smaller graphs are launch-bound: the extra launches would cost more than they save
 
 
-def graph_preprocess(graph: Graph) -> Graph:
+def graph_preprocess(graph: Graph, hub_block=None) -> Graph:
     """Materialises the CSR / CSC index bundles (and the long-row schedules of the SpMM kernels) once, so that no
-    operator call pays for a sort.  `graph.coo`, `graph.inc_in` and `graph.inc_out` are derived on access."""
+    operator call pays for a sort.  `graph.coo`, `graph.inc_in` and `graph.inc_out` are derived on access.
+
+    hub_block: side length of the dense hub block that the unweighted aggregation (csr_SPMM / spmm_copy_u) multiplies
+    on the tensor cores instead of gathering (see graph.HubBlock); None takes config.hub_block() (0 = off), and the
+    block is then only built for graphs large and skewed enough to profit; an explicit side is always honoured."""
     assert graph.device.type == "cuda", "graph must be on GPU"
+    side = config.hub_block() if hub_block is None else int(hub_block)
+    forced = hub_block is not None
+    graph._hubs = {}
     for fmt in ("csr", "csc"):
-        indptr, _, _ = graph.adj_sparse(fmt)
+        indptr, indices, _ = graph.adj_sparse(fmt)
         graph._plans[fmt] = SpmmSchedule(indptr)
+        if side > 0 and (forced or graph.num_edges() >= HUB_BLOCK_MIN_EDGES):
+            hub = HubBlock(indptr, indices, graph.num_nodes(), side, side, 0.0 if forced else HUB_BLOCK_MIN_DENSITY)
+            if hub.ok:
+                graph._hubs[fmt] = hub
     return graph

@@ -112,7 +112,8 @@ def reddit_like():
     import tango_b200 as T
     from tango_b200.graph import rmat_graph
     g = rmat_graph(232_965, 114_615_892 - 232_965, 20245, device="cuda")
-    T.graph_preprocess(g)
+    T.graph_preprocess(g)              # default settings: the dense hub block is built for a graph of this size
+    assert "csc" in g._hubs and g._hubs["csc"].density > 0.1
     indptr = g.adj_csc[0].cpu().numpy().astype(np.int64)
     deg = np.diff(indptr)
     rng = np.random.default_rng(5)
@@ -129,12 +130,25 @@ def _row_slices(g, indptr, rows, reverse=False):
     return out
 
 
+@pytest.mark.parametrize("hub", [True, False])
 @pytest.mark.parametrize("f", [256, 41])
-def test_aggregation_hub_rows_vs_oracle(cuda, reddit_like, f):
+def test_aggregation_hub_rows_vs_oracle(cuda, reddit_like, f, hub):
     """F = 256 (layer 1) and F = 41 (layer 2, rows padded to 48 bytes): sampled rows -- the ten longest among them,
-    up to 108 K in-edges -- equal the oracle's integer row sums times the scale, bit for bit."""
+    up to 108 K in-edges -- equal the oracle's integer row sums times the scale, bit for bit; with the dense hub
+    block on the tensor cores (the default for this graph) and with every edge gathered (sliced rows, int32 atomics)."""
     from tango_b200 import kernels as K
     g, indptr, rows = reddit_like
+    hubs = g._hubs
+    try:
+        if not hub:
+            g._hubs = {}
+        _check_aggregation(g, indptr, rows, f)
+    finally:
+        g._hubs = hubs
+
+
+def _check_aggregation(g, indptr, rows, f):
+    from tango_b200 import kernels as K
     n = g.num_nodes()
     assert np.diff(indptr).max() > 100_000
     rng = np.random.default_rng(f)
@@ -160,6 +174,7 @@ def test_weighted_aggregation_and_dot_sddmm_hub_rows_vs_oracle(cuda, reddit_like
     """4 heads x 64: int8-weighted aggregation and the row-wise dot SDDMM on the sampled rows (hub rows included)."""
     from tango_b200 import kernels as K
     g, indptr, rows = reddit_like
+    assert g._identity.get("csc")        # slot j of the CSC holds edge j: per-edge tensors are in slot order
     n, e, h, d = g.num_nodes(), g.num_edges(), 4, 64
     rng = np.random.default_rng(17)
     nq = rng.integers(-127, 128, (n, h, d), dtype=np.int8)

@@ -518,12 +518,57 @@ def test_csc_numbered_graph_skips_edge_id_indirection(cuda):
 
 
 def test_row_gather_probe_runs_and_validates(cuda):
-    from tango_b200._lib import lib
+    """The benchmark's L2 row-gather probe lives in a library of its own (it is not part of the product ABI)."""
+    import ctypes
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    probe = ctypes.CDLL(os.path.join(root, "tango_b200", "lib", "libtango_bench_probe.so")).bench_probe_row_gather
+    probe.restype = ctypes.c_int64
+    probe.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                      ctypes.c_void_p, ctypes.c_void_p]
     table = torch.ones((1000, 256), dtype=torch.int8, device="cuda")
     sink = torch.zeros(1, dtype=torch.int32, device="cuda")
     st = torch.cuda.current_stream().cuda_stream
-    nbytes = lib.tango_probe_row_gather(table.data_ptr(), 1000, 256, 3, 8, 256, sink.data_ptr(), st)
+    nbytes = probe(table.data_ptr(), 1000, 256, 3, 8, 256, sink.data_ptr(), st)
     torch.cuda.synchronize()
     assert nbytes == 148 * 8 * 256 * 3 * 8 * 16 and int(sink) == 0
-    assert lib.tango_probe_row_gather(table.data_ptr(), 1000, 48, 3, 8, 256, sink.data_ptr(), st) == -2     # not a power of two
-    assert lib.tango_probe_row_gather(None, 1000, 256, 3, 8, 256, sink.data_ptr(), st) == -1
+    assert probe(table.data_ptr(), 1000, 48, 3, 8, 256, sink.data_ptr(), st) == -1     # not a power of two
+    assert probe(None, 1000, 256, 3, 8, 256, sink.data_ptr(), st) == -1
+
+
+
+@pytest.mark.parametrize("f", [256, 41, 64])
+@pytest.mark.parametrize("reverse", [False, True])
+def test_copy_u_with_dense_hub_block_is_bit_identical(cuda, f, reverse):
+    """Aggregation with the hub block multiplied on the tensor cores (forced here on a small graph: 256 x 256 block,
+    i.e. two 128-row GEMM tiles, next to rows that are sliced by length) against the oracle and against the
+    all-gather path: same bits."""
+    import tango_b200 as T
+    from tango_b200 import kernels as K
+    from tango_b200.graph import rmat_graph
+    g = rmat_graph(6000, 400_000, 41, device="cuda")
+    T.graph_preprocess(g, hub_block=256)
+    key = "csr" if reverse else "csc"
+    assert key in g._hubs and g._hubs[key].n_block_edges > 0
+    n = g.num_nodes()
+    rng = np.random.default_rng(f)
+    nq = rng.integers(-127, 128, (n, f), dtype=np.int8)
+    nt = K.alloc_int8((n, f), "cuda")
+    torch.as_strided(nt, (n, nt.stride(0)), (nt.stride(0), 1)).zero_()
+    nt.copy_(torch.from_numpy(nq).cuda())
+    sc = np.float32(0.0137)
+    bias = torch.from_numpy(rng.standard_normal(f).astype(np.float32)).cuda()
+    rs = torch.from_numpy(rng.random(n).astype(np.float32)).cuda()
+    amax = torch.zeros(1, device="cuda")
+    got = K.csr_SPMM(g, nt, _scale_t(sc), reverse, rs, bias, True, amax)
+    assert K.device_status() == 0
+    bundle = g.adj_csr if reverse else g.adj_csc
+    ip, idx = [t.cpu().numpy().astype(np.int64) for t in bundle[:2]]
+    ref = O.spmm_copy_u(ip, idx, nq, sc)
+    ref = np.maximum((ref * rs.cpu().numpy()[:, None]).astype(np.float32) + bias.cpu().numpy()[None, :], 0).astype(np.float32)
+    np.testing.assert_array_equal(got.cpu().numpy(), ref)
+    assert amax.item() == O.absmax_scale(ref)
+    T.graph_preprocess(g, hub_block=0)
+    assert not g._hubs
+    plain = K.csr_SPMM(g, nt, _scale_t(sc), reverse, rs, bias, True)
+    assert torch.equal(plain, got)

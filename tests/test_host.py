@@ -11,7 +11,7 @@ import torch.multiprocessing as mp
 
 from oracle import tango_oracle as O
 from tango_b200 import config
-from tango_b200.graph import Graph, RowPartition, SpmmSchedule, add_self_loop, rmat_edges, rmat_graph
+from tango_b200.graph import Graph, HubBlock, RowPartition, SpmmSchedule, add_self_loop, rmat_edges, rmat_graph
 from tango_b200.kernels import alloc_int8, infer_broadcast_shape
 
 
@@ -317,3 +317,32 @@ def test_dw_workspace_query_saturates_instead_of_wrapping():
     # the entry point with built-in scratch refuses such sizes before any CUDA call
     assert L.tango_qgemm_dw_noalloc(None, 16, None, 16, 8, 2 ** 31, 2 ** 31, None, None, None, 2 ** 31, None, None) == -5
     assert L.tango_qgemm_dw_noalloc(None, 16, None, 16, 8, 2 ** 40, 4, None, None, None, 4, None, None) == -5
+
+
+def test_hub_block_partitions_the_edges_exactly():
+    """Dense hub block + remaining CSR = the original adjacency, edge for edge; the block's rows lead heavy_rows and
+    row_order, and the row kernels are told to skip them."""
+    g = rmat_graph(3000, 60000, 5, device="cpu")
+    ip, idx, _ = g.adj_csc
+    n = g.num_nodes()
+    hub = HubBlock(ip, idx, n, 256, 384, 0.0)
+    assert hub.ok and hub.dense.shape == (256, 384) and 0 < hub.density < 1
+    full = torch.zeros((n, n), dtype=torch.int32)
+    rows = torch.repeat_interleave(torch.arange(n), (ip[1:] - ip[:-1]).long())
+    full.index_put_((rows, idx.long()), torch.ones(1, dtype=torch.int32).expand(idx.numel()), accumulate=True)
+    rest = torch.zeros_like(full)
+    trows = torch.repeat_interleave(torch.arange(n), (hub.indptr[1:] - hub.indptr[:-1]).long())
+    rest.index_put_((trows, hub.indices.long()), torch.ones(1, dtype=torch.int32).expand(hub.indices.numel()),
+                    accumulate=True)
+    assert int(rest[hub.rows.long()[:, None], hub.cols.long()[None, :]].sum()) == 0      # nothing of the block remains
+    rest[hub.rows.long()[:, None], hub.cols.long()[None, :]] += hub.dense.int()
+    assert torch.equal(full, rest)
+    s = hub.schedule
+    assert s.n_skip == s.n_heavy >= 256 and torch.equal(s.heavy_rows[:256], hub.rows)
+    assert torch.equal(s.row_order[:s.n_skip], s.heavy_rows)
+    assert sorted(s.row_order.tolist()) == list(range(n))
+    tail_deg = (hub.indptr[1:] - hub.indptr[:-1]).long()
+    listed = s.row_order[s.n_skip:].long()
+    assert bool((tail_deg[listed] <= s.threshold).all())
+    # a sparse block is refused
+    assert not HubBlock(ip, idx, n, 256, 384, 0.9).ok
