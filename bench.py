@@ -751,6 +751,16 @@ def run_primitives(args, quiet: bool = False):
     report("qgemm dW", timeit(lambda: K.cuda_kernels.QGEMM_backward_gradW(dW, dyq, xq, sdy, sx)),
            m * n + m * ldk + 4 * n * k, ops)
     del X, dY, Y, dX, xq, dyq
+    # ---- a compute-bound shape, as tensor-pipe evidence only (the layer's own shapes above are all HBM-bound)
+    mp, kp, np_ = 232_965, 4096, 4096
+    xp = torch.randint(-127, 128, (mp, kp), dtype=torch.int8, device=dev)
+    wp = torch.randint(-127, 128, (np_, kp), dtype=torch.int8, device=dev)
+    yp = torch.empty((mp, np_), device=dev)
+    one = torch.ones(1, device=dev)
+    report("PROBE (compute-bound, not a layer shape): qgemm int8 operands M=232965 K=N=4096",
+           timeit(lambda: K._qgemm_nt(yp, xp, wp, one, one), reps=3), mp * kp + np_ * kp + 4 * mp * np_,
+           2.0 * mp * kp * np_, dense_int8_peak_TOPS_nominal=4500)
+    del xp, wp, yp
     # ---- config 3: SpMM / SDDMM on 169,343 nodes, 1,166,243 edges (+ self loops)
     nn_, ne_ = 169_343, 1_166_243
     g = rmat_graph(nn_, ne_, 20243, device=dev)

@@ -793,7 +793,7 @@ int igemm_accumulate_i32(const int8_t *a, int64_t lda, const int8_t *b, int64_t 
     const int64_t tiles = ceil_div(m, kTileM) * ceil_div(n, 256);
     int splits = (int)(kNumSMs / (tiles > 0 ? tiles : 1));
     if (splits < 1) splits = 1;
-    if (splits > 4) splits = 4;
+    if (splits > 8) splits = 8;
     GemmCall c{a, lda, 0, b, ldb, 1, m, n, k, 1, splits, nullptr, 0, ws, ldws, nullptr, nullptr, nullptr, nullptr, status};
     c.pipeline_bytes = 196608;    // one CTA per SM: a deeper ring instead of a second resident CTA
     return launch_gemm(c, stream);

@@ -133,6 +133,7 @@ struct DotRowArgs {
     const float *su, *sv;
     float *out;
     float *out_absmax;
+    int64_t n_long;         // rows row_order[0, n_long) get a warp each; the shorter rows after them a lane group
 };
 
 template <int VEC, bool QUAD>
@@ -245,6 +246,88 @@ __global__ void __launch_bounds__(128, 8) sddmm_dot_rows_kernel(const DotRowArgs
         if (a.row_order) row = __ldg(a.row_order + row);
         const int beg = __ldg(a.indptr + row), end = __ldg(a.indptr + row + 1);
         if (!(a.n_units > 0 && end - beg > a.split_threshold)) dot_row_segment<VEC, QUAD>(a, row, beg, end, sc, amax);
+    }
+    if (a.out_absmax) {
+        amax = warp_max(amax);
+        if (lane == 0 && amax > 0.f) {
+            const float s = __fdiv_rn(amax, 127.0f);
+            if (s > __ldcg(a.out_absmax)) atomic_max_nonneg(a.out_absmax, s);
+        }
+    }
+}
+
+// Short rows (a handful of edges): a group of G lanes owns one row, keeps its piece of V[row] in registers, fetches
+// G neighbour ids with one coalesced load, gathers four neighbours' pieces of U at a time, and the LH lanes of a head
+// reduce with shuffles restricted to the group.  Several rows per warp, no lane idles on a 7-edge row.
+template <int VEC>
+__global__ void __launch_bounds__(128, 12) sddmm_dot_short_kernel(const DotRowArgs a) {
+    typedef typename DotVec<VEC>::T V;
+    const int lane = threadIdx.x & 31;
+    const int G = a.G, sub = lane % G;
+    const int64_t gid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const int64_t n_short = a.n_rows - a.n_long;
+    const bool in_range = gid < n_short;
+    const bool active = in_range && sub * VEC < a.f_pad;
+    const int off = active ? sub * VEC : 0;
+    const unsigned gmask = (G >= 32) ? 0xffffffffu : (((1u << G) - 1u) << (lane - sub));
+    const int base_lane = lane - sub;
+    const float sc = __fmul_rn(__ldg(a.su), __ldg(a.sv));
+    const int head = (sub * VEC) / (a.LH * VEC);
+    const bool writer = active && (sub % a.LH) == 0 && head < a.H;
+    float amax = 0.f;
+    int beg = 0, end = 0;
+    V vr = V();
+    if (in_range) {
+        const int64_t row = a.row_order ? (int64_t)__ldg(a.row_order + a.n_long + gid) : a.n_long + gid;
+        beg = __ldg(a.indptr + row); end = __ldg(a.indptr + row + 1);
+        if (active) vr = __ldg(reinterpret_cast<const V *>(a.v + row * a.ldv + off));
+    }
+    const int8_t *ubase = a.u + off;
+    const uint32_t ld = (uint32_t)a.ldu;
+    const int CH = G < 4 ? 4 : G;           // ids fetched per step (narrow groups: lane `sub` fetches several)
+    for (int j0 = beg; j0 < end; j0 += CH) {
+        int my_idx = 0, my_eid = 0;
+        int idx4[4] = {0, 0, 0, 0}, eid4[4] = {0, 0, 0, 0};
+        if (G >= 4) {
+            const int j = j0 + sub;
+            if (j < end) {
+                my_idx = __ldg(a.indices + j);
+                my_eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (j0 + k < end) {
+                    idx4[k] = __ldg(a.indices + j0 + k);
+                    eid4[k] = a.edge_ids ? __ldg(a.edge_ids + j0 + k) : j0 + k;
+                }
+        }
+        const int cnt = min(CH, end - j0);
+        for (int s0 = 0; s0 < cnt; s0 += 4) {
+            V ur[4];
+            int e[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                int idx;
+                if (G >= 4) {
+                    idx = __shfl_sync(gmask, my_idx, base_lane + ((s0 + k) & (G - 1)));
+                    e[k] = __shfl_sync(gmask, my_eid, base_lane + ((s0 + k) & (G - 1)));
+                } else {
+                    idx = idx4[k]; e[k] = eid4[k];
+                }
+                ur[k] = (s0 + k < cnt && active) ? __ldg(reinterpret_cast<const V *>(ubase + (uint64_t)(uint32_t)idx * ld)) : V();
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                int acc = dot_regs<VEC>(ur[k], vr);
+                for (int o = a.LH >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(gmask, acc, o);
+                if (writer && s0 + k < cnt) {
+                    const float r = __fmul_rn((float)acc, sc);
+                    __stcs(a.out + (int64_t)e[k] * a.H + head, r);
+                    amax = fmaxf(amax, fabsf(r));
+                }
+            }
+        }
     }
     if (a.out_absmax) {
         amax = warp_max(amax);
@@ -389,21 +472,36 @@ extern "C" int tango_sddmm_dot_rows(const int32_t *indptr, const int32_t *indice
     a.G = pow2_ceil(a.f_pad / vec);
     a.LH = (h == 1) ? a.G : d / vec;
     a.su = su; a.sv = sv; a.out = out; a.out_absmax = out_absmax;
+    a.n_long = n_rows;
     if (plan) {
         a.row_order = plan->row_order;
         if (plan->n_units > 0) {
             if (!plan->units || !aligned(plan->units, 16)) return TANGO_EINVAL;
             a.units = plan->units; a.n_units = plan->n_units; a.split_threshold = plan->split_threshold;
         }
+        // rows of a few edges (the tail of the degree-sorted order) go to the lane-group kernel
+        if (plan->row_order && plan->n_long_rows >= 0 && plan->n_long_rows <= n_rows) a.n_long = plan->n_long_rows;
     }
-    const int64_t blocks = ceil_div(a.n_units + a.n_rows, 4);
+    const int64_t n_short = n_rows - a.n_long;
+    DotRowArgs al = a;
+    al.n_rows = a.n_long;        // the warp-per-row kernel walks row_order[0, n_long)
+    const int64_t blocks = ceil_div(al.n_units + al.n_rows, 4);
     if (blocks > 0x7fffffff) return TANGO_ESIZE;
     const bool quad = a.LH >= 4;
-    if (vec == 16 && quad) sddmm_dot_rows_kernel<16, true><<<(unsigned)blocks, 128, 0, stream>>>(a);
-    else if (vec == 16) sddmm_dot_rows_kernel<16, false><<<(unsigned)blocks, 128, 0, stream>>>(a);
-    else if (quad) sddmm_dot_rows_kernel<4, true><<<(unsigned)blocks, 128, 0, stream>>>(a);
-    else sddmm_dot_rows_kernel<4, false><<<(unsigned)blocks, 128, 0, stream>>>(a);
-    TANGO_LAUNCH_CHECK();
+    if (blocks > 0) {
+        if (vec == 16 && quad) sddmm_dot_rows_kernel<16, true><<<(unsigned)blocks, 128, 0, stream>>>(al);
+        else if (vec == 16) sddmm_dot_rows_kernel<16, false><<<(unsigned)blocks, 128, 0, stream>>>(al);
+        else if (quad) sddmm_dot_rows_kernel<4, true><<<(unsigned)blocks, 128, 0, stream>>>(al);
+        else sddmm_dot_rows_kernel<4, false><<<(unsigned)blocks, 128, 0, stream>>>(al);
+        TANGO_LAUNCH_CHECK();
+    }
+    if (n_short > 0) {
+        const int64_t sb = ceil_div(n_short * a.G, 128);
+        if (sb > 0x7fffffff) return TANGO_ESIZE;
+        if (vec == 16) sddmm_dot_short_kernel<16><<<(unsigned)sb, 128, 0, stream>>>(a);
+        else sddmm_dot_short_kernel<4><<<(unsigned)sb, 128, 0, stream>>>(a);
+        TANGO_LAUNCH_CHECK();
+    }
     return TANGO_OK;
 }
 

@@ -317,31 +317,77 @@ __global__ void __launch_bounds__(kSpmmThreads, DEEP ? 6 : 8) spmm_kernel(const 
     }
 }
 
-// Short rows: a group of G lanes owns one row (32 / G rows per warp), walks its neighbours four at a time and needs
-// neither shuffles nor a cross-lane reduction -- the warp-per-row kernel would spend most of its time in the ragged
-// tail on rows with a handful of neighbours.
-template <int VEC, int MODE>
-__global__ void __launch_bounds__(128) spmm_short_kernel(const SpmmArgs a) {
+// Short rows: a group of G lanes owns one row (32 / G rows per warp) and needs no cross-lane reduction -- the
+// warp-per-row kernel would spend most of its time in the ragged tail on rows with a handful of neighbours.  Such a
+// row is a short dependent chain (row bounds -> neighbour ids -> gathers -> store), so what matters is how few round
+// trips it takes and how many rows are in flight: with four or more lanes per row the group fetches G neighbour ids
+// (and edge ids) with ONE coalesced load and hands them out by shuffles restricted to the group, so an 8-neighbour
+// row costs one index round trip and two gather round trips; narrower groups read the ids one by one.
+// MULTI: rows cut into per-shard segments with a scale each (row-partitioned multi-GPU aggregation).
+template <int VEC, int MODE, bool MULTI>
+__global__ void __launch_bounds__(128, MULTI ? 8 : 10) spmm_short_kernel(const SpmmArgs a) {
     const int lane = threadIdx.x & 31;
     const int G = a.G, sub = lane % G;
     const int64_t gid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
     const int64_t n_short = a.n_rows - a.n_long;
     const int off = sub * VEC;
-    const bool active = gid < n_short && off < a.f_pad;
+    const bool in_range = gid < n_short;
+    const bool active = in_range && off < a.f_pad;
+    const unsigned gmask = (G >= 32) ? 0xffffffffu : (((1u << G) - 1u) << (lane - sub));
+    const int base_lane = lane - sub;
     float amax = 0.f;
-    if (active) {
-        const int64_t row = a.row_order ? (int64_t)__ldg(a.row_order + a.n_long + gid) : a.n_long + gid;
-        const int32_t *ip = a.indptr + row * a.nseg;
-        const int8_t *base = a.feat + off;
-        const int head = (MODE == MODE_WEIGHT_LANE) ? off / a.D : 0;
-        float facc[VEC];
+    int64_t row = 0;
+    const int32_t *ip = a.indptr;
+    if (in_range) {
+        row = a.row_order ? (int64_t)__ldg(a.row_order + a.n_long + gid) : a.n_long + gid;
+        ip = a.indptr + row * a.nseg;
+    }
+    const int8_t *base = a.feat + (active ? off : 0);
+    const int head = (MODE == MODE_WEIGHT_LANE) ? (active ? off : 0) / a.D : 0;
+    float facc[VEC];
+    if (MULTI) {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) facc[i] = 0.f;
-        for (int k = 0; k < a.nseg; ++k) {
-            const int beg = __ldg(ip + k), end = __ldg(ip + k + 1);
-            int acc[VEC];
+    }
+    const int nseg = in_range ? (MULTI ? a.nseg : 1) : 0;
+    int acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0;
+    for (int k = 0; k < nseg; ++k) {
+        const int beg = __ldg(ip + k), end = __ldg(ip + k + 1);
+        if (MULTI) {
 #pragma unroll
             for (int i = 0; i < VEC; ++i) acc[i] = 0;
+        }
+        if (G >= 4) {
+            for (int j0 = beg; j0 < end; j0 += G) {
+                const int j = j0 + sub;
+                int my_idx = 0, my_eid = 0;
+                if (j < end) {
+                    my_idx = a.indices ? __ldg(a.indices + j) : j;
+                    if (MODE == MODE_WEIGHT_LANE) my_eid = a.edge_ids ? __ldg(a.edge_ids + j) : j;
+                }
+                const int cnt = min(G, end - j0);
+                for (int s0 = 0; s0 < cnt; s0 += 4) {
+                    VecLoad<VEC> v[4];
+                    uint32_t wvec = (MODE == MODE_WEIGHT_LANE) ? 0u : 0x01010101u;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int idx = __shfl_sync(gmask, my_idx, base_lane + ((s0 + u) & (G - 1)));
+                        int eid = 0;
+                        if (MODE == MODE_WEIGHT_LANE) eid = __shfl_sync(gmask, my_eid, base_lane + ((s0 + u) & (G - 1)));
+                        if (s0 + u < cnt) {
+                            v[u].load(base + (uint64_t)(uint32_t)idx * (uint32_t)a.ld);
+                            if (MODE == MODE_WEIGHT_LANE)
+                                wvec |= (uint32_t)(uint8_t)__ldg(a.ew + (uint64_t)(uint32_t)eid * (uint32_t)a.H + head) << (8 * u);
+                        } else {
+                            v[u].zero();
+                        }
+                    }
+                    accumulate_four<VEC>(acc, v, wvec);
+                }
+            }
+        } else {
             for (int j = beg; j < end; j += 4) {
                 VecLoad<VEC> v[4];
                 uint32_t wvec = (MODE == MODE_WEIGHT_LANE) ? 0u : 0x01010101u;
@@ -360,11 +406,21 @@ __global__ void __launch_bounds__(128) spmm_short_kernel(const SpmmArgs a) {
                 }
                 accumulate_four<VEC>(acc, v, wvec);
             }
+        }
+        if (MULTI) {
             const float sc = __ldg(a.scales + k);
 #pragma unroll
             for (int i = 0; i < VEC; ++i) facc[i] = __fadd_rn(facc[i], __fmul_rn((float)acc[i], sc));
         }
+    }
+    if (active) {
         float *o = a.out + row * a.ldo + off;
+        if (!MULTI) {
+            // one segment: 0 + acc * scale, the same two roundings as the segmented form
+            const float sc = __ldg(a.scales);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) facc[i] = __fadd_rn(0.f, __fmul_rn((float)acc[i], sc));
+        }
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
             facc[i] = finish_value(facc[i], row, min(off + i, a.f - 1), a);
@@ -373,7 +429,7 @@ __global__ void __launch_bounds__(128) spmm_short_kernel(const SpmmArgs a) {
         if (VEC == 16 && off + 16 <= a.f && (a.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                reinterpret_cast<float4 *>(o)[i] = make_float4(facc[4 * i], facc[4 * i + 1], facc[4 * i + 2], facc[4 * i + 3]);
+                __stcs(reinterpret_cast<float4 *>(o) + i, make_float4(facc[4 * i], facc[4 * i + 1], facc[4 * i + 2], facc[4 * i + 3]));
         } else {
 #pragma unroll
             for (int i = 0; i < VEC; ++i)
@@ -610,8 +666,13 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
         const int64_t threads = (a.n_rows - a.n_long) * a.G;
         const int64_t sb = ceil_div(threads, 128);
         if (sb > 0x7fffffff) return TANGO_ESIZE;
-        if (vec == 16) spmm_short_kernel<16, MODE><<<(unsigned)sb, 128, 0, stream>>>(a);
-        else spmm_short_kernel<4, MODE><<<(unsigned)sb, 128, 0, stream>>>(a);
+        if (a.nseg > 1) {
+            if (vec == 16) spmm_short_kernel<16, MODE, true><<<(unsigned)sb, 128, 0, stream>>>(a);
+            else spmm_short_kernel<4, MODE, true><<<(unsigned)sb, 128, 0, stream>>>(a);
+        } else {
+            if (vec == 16) spmm_short_kernel<16, MODE, false><<<(unsigned)sb, 128, 0, stream>>>(a);
+            else spmm_short_kernel<4, MODE, false><<<(unsigned)sb, 128, 0, stream>>>(a);
+        }
         TANGO_LAUNCH_CHECK();
     }
     if (a.n_units > 0 || dense) {
@@ -661,8 +722,8 @@ static bool try_incidence_contig(SpmmArgs &a, const tango_spmm_plan *plan, cudaS
     if (a.n_long < a.n_rows) {
         const int64_t sb = ceil_div((a.n_rows - a.n_long) * a.G, 128);
         if (sb > 0x7fffffff) { rc = TANGO_ESIZE; return true; }
-        if (short_vec == 16) spmm_short_kernel<16, MODE_COPY><<<(unsigned)sb, 128, 0, stream>>>(a);
-        else spmm_short_kernel<4, MODE_COPY><<<(unsigned)sb, 128, 0, stream>>>(a);
+        if (short_vec == 16) spmm_short_kernel<16, MODE_COPY, false><<<(unsigned)sb, 128, 0, stream>>>(a);
+        else spmm_short_kernel<4, MODE_COPY, false><<<(unsigned)sb, 128, 0, stream>>>(a);
         if (cudaPeekAtLastError() != cudaSuccess) { rc = TANGO_ECUDA; return true; }
     }
     if (a.n_units > 0) {

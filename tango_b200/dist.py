@@ -21,7 +21,7 @@ import torch.nn.functional as F
 from torch.autograd.function import Function, once_differentiable
 
 from . import config
-from .graph import Graph, RowPartition, balanced_bounds, uniform_bounds
+from .graph import HUB_BLOCK_MIN_DENSITY, Graph, HubBlock, RowPartition, balanced_bounds, uniform_bounds
 
 
 def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_rows: int, group=None,
@@ -89,6 +89,17 @@ class DistGraph:
         self.bwd = RowPartition(csr[0], csr[1], None, n, rank, world, bounds, layout, order)
         self.shard_rows, self.n_local, self.local_ids = self.fwd.shard_rows, self.fwd.n_local, self.fwd.local_ids
         self.r0, self.r1 = self.fwd.r0, self.fwd.r1
+        # dense hub block of this rank's rows (global scale mode: one scale, unsegmented rows): the rank's longest
+        # rows x the most referenced rows of the gathered table, multiplied on the tensor cores
+        self.hubs = {}
+        side = config.hub_block()
+        if scale_mode == "global" and side > 0 and g.device.type == "cuda" and g.num_edges() >= 4_000_000:
+            rows_side = max(128, side // world // 128 * 128)
+            for key, part in (("fwd", self.fwd), ("bwd", self.bwd)):
+                hub = HubBlock(part.indptr_flat, part.indices, world * self.shard_rows, rows_side, side,
+                               HUB_BLOCK_MIN_DENSITY)
+                if hub.ok:
+                    self.hubs[key] = hub
         self.in_norm = g.in_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
         self.out_norm = g.out_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
         if transport == "peer" and world > 1:
@@ -167,7 +178,11 @@ def _spmm_gathered(dg: DistGraph, part: RowPartition, q_all: torch.Tensor, scale
     out = torch.empty((dg.n_local, f), dtype=torch.float32, device=q_all.device)
     feats = q_all[:, :f] if q_all.shape[1] != f else q_all
     if dg.scale_mode == "global":
-        K._csr_spmm(out, part.indptr_flat, part.indices, feats, scales, part.schedule_flat, 1, row_scale, bias, relu)
+        hub = dg.hubs.get("fwd" if part is dg.fwd else "bwd")
+        if hub is not None and q_all.shape[1] == (f + 15) // 16 * 16:
+            K._csr_spmm(out, hub.indptr, hub.indices, feats, scales, hub.schedule, 1, row_scale, bias, relu)
+        else:
+            K._csr_spmm(out, part.indptr_flat, part.indices, feats, scales, part.schedule_flat, 1, row_scale, bias, relu)
     else:
         K._csr_spmm(out, part.indptr, part.indices, feats, scales, part.schedule, dg.world, row_scale, bias, relu)
     return out

@@ -303,7 +303,7 @@ def _incidence_spmm(out, indptr, edge_ids, E, scale, sched=None):
     del keep
 
 
-ROWWISE_SDDMM_MIN_DEGREE = 32     # average edges per row from which mySDDMM_int8("dot") walks rows
+ROWWISE_SDDMM_MIN_DEGREE = 0      # average edges per row from which mySDDMM_int8("dot") walks rows (0: always)
 
 
 def _sddmm_dot_rows(out, scaleOut, indptr, indices, edge_ids, U, V, scaleU, scaleV, sched=None) -> bool:
@@ -316,7 +316,8 @@ def _sddmm_dot_rows(out, scaleOut, indptr, indices, edge_ids, U, V, scaleU, scal
     if sched is not None:
         order = sched.row_order
         plan_obj = SpmmPlan(sched.units.data_ptr() if sched.n_units else None, sched.n_units, None, 0, None, 0,
-                            sched.threshold, order.data_ptr() if order.numel() else None, -1)
+                            sched.threshold, order.data_ptr() if order.numel() else None,
+                            sched.n_long if order.numel() else -1)
         plan, keep = ctypes.byref(plan_obj), (plan_obj,)
     with torch.cuda.device(U.device):
         rc = lib.tango_sddmm_dot_rows(_p(indptr), _pi(indices), _p(edge_ids), n_rows, _p(U2), ldu, _p(V2), ldv, h, d,
@@ -325,7 +326,7 @@ def _sddmm_dot_rows(out, scaleOut, indptr, indices, edge_ids, U, V, scaleU, scal
     if rc == _lib.TANGO_EALIGN:
         return False
     check(rc, "mySDDMM_int8(dot, rows)")
-    launch_counter[0] += 1
+    launch_counter[0] += 1 + (sched is not None and sched.n_long < n_rows)
     return True
 
 
@@ -454,9 +455,9 @@ def mySDDMM_int8(g, op, U, V, scaleU, scaleV, isReduce, reverse=False):
     done = False
     if (op == "dot" and src.numel() >= ROWWISE_SDDMM_MIN_DEGREE * g.num_nodes() and U.shape[1:] == V.shape[1:]
             and U.dim() == 3 and U.shape[0] == g.num_nodes() == V.shape[0]):
-        # walk the rows of the fixed endpoint: V's row stays in registers, only U is gathered.  Worth it when rows
-        # are long enough to fill a warp's batches; on a graph with a handful of edges per row the endpoint-list
-        # kernel (32 edges per warp, whatever their rows) is the faster one.
+        # walk the rows of the fixed endpoint: V's row stays in registers, only U is gathered (half the gathered
+        # bytes of the endpoint-list kernel, and half its index stream); long rows get a warp, rows of a few edges a
+        # group of lanes each.
         indptr, indices, edge_ids = _bundle(g, reverse)
         done = _sddmm_dot_rows(out, scale, indptr, indices, edge_ids, U, V, scaleU, scaleV, _schedule(g, reverse))
     if not done:
