@@ -472,8 +472,9 @@ def run_ours(args):
     hub_info = None
     if world == 1 and getattr(g, "_hubs", None):
         hb = g._hubs.get("csc")
-        hub_info = {"side": int(hb.dense.shape[0]), "edges_in_block": hb.n_block_edges,
-                    "share_of_edges": hb.n_block_edges / n_edges, "density": hb.density}
+        hub_info = {"rows": int(hb.rows.numel()), "cols": int(hb.cols.numel()), "tiles_128x128": hb.n_tiles,
+                    "edges_in_region": hb.n_block_edges, "share_of_edges": hb.n_block_edges / n_edges,
+                    "density": hb.density}
     secondary = None
     if world == 1 and not args.no_secondary and name == "gcn_c5":
         # outside the timed region: the same epoch with every edge gathered (no dense hub block), the GAT epoch on
@@ -962,8 +963,9 @@ def main():
     ap.add_argument("--transport", default="auto", choices=["auto", "nccl", "peer"],
                     help="multi-GPU exchange: NCCL collectives, or stores into peer memory + rendezvous kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--hub-block", type=int, default=16384,
-                    help="side of the dense hub block of the unweighted aggregation (tensor cores); 0 = gather every edge")
+    ap.add_argument("--hub-block", type=int, default=163840,
+                    help="largest side of the dense hub region of the unweighted aggregation (tensor cores); "
+                         "0 = gather every edge")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the untimed extras of the 1-GPU line (GAT epoch, per-primitive numbers)")
     ap.add_argument("--scale-mode", default="global", choices=["global", "shard"],

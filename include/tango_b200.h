@@ -174,22 +174,27 @@ typedef struct tango_spmm_plan {
                                   that the warps of a CTA finish together); NULL = natural order */
     int64_t n_long_rows;       /* with row_order: rows row_order[0, n_long_rows) get one warp each, the shorter rows
                                   after them are handled by groups of lanes (several rows per warp); -1 = all long */
-    /* Optional dense hub block (tango_spmm_copy_u only; all zero / NULL = none).  On a power-law graph a few
-     * thousand rows and a few thousand source columns hold a large share of all edges, and that sub-matrix is dense
-     * enough (tens of percent) to be multiplied as a dense 0/1 int8 matrix on the tensor cores instead of being
-     * gathered edge by edge: partial[r, :] = sum_c dense_a[r, c] * Nq[dense_cols[c], :], exact int32, added into the
-     * scratch row of heavy row r (r < dense_rows: the first dense_rows entries of heavy_rows are the block's rows, in
-     * the order of dense_a's rows).  The CSR handed to the entry point must then hold only the edges OUTSIDE the
-     * block, every block row must be listed in heavy_rows (its remaining edges are covered by units, possibly none)
-     * and row_order must list the heavy rows first: its first n_skip_rows entries are left to units + finalize. */
-    const int8_t *dense_a;     /* [dense_rows, dense_lda] int8, entries 0 or 1 (edge multiplicity) */
-    int64_t dense_lda;         /* >= dense_n_cols, multiple of 16 */
-    int64_t dense_rows;        /* multiple of 128 is best; <= n_heavy */
-    const int32_t *dense_cols; /* [dense_n_cols] feature-row id of every column of the block */
-    int64_t dense_n_cols;      /* multiple of 16 */
-    int8_t *dense_b;           /* scratch [dense_n_cols, round_up(f, 16)] int8: the block's feature rows, packed */
-    int *dense_status;         /* optional device word that receives TANGO_ETIMEOUT if a bounded wait of the GEMM expires */
-    int64_t n_skip_rows;       /* leading entries of row_order owned by units + finalize (0 without a dense block) */
+    /* Optional dense hub region (tango_spmm_copy_u only; all zero / NULL = none).  With rows ranked by length and
+     * columns by how often they are referenced, the adjacency of a power-law graph is dense in its top-left corner:
+     * that staircase-shaped region is multiplied as dense 0/1 int8 tiles on the tensor cores instead of being
+     * gathered edge by edge.  Row tile i (128 rows: heavy rows 128 i .. 128 i + 127, i.e. the first dense_rows entries
+     * of heavy_rows in order) owns a run of stored 128 x 128 tiles; dense_units lists work items (row tile, index of
+     * the first stored tile, first column tile, number of tiles); column tile k covers the feature rows
+     * dense_cols[128 k .. 128 k + 127].  Every work item adds partial[r, :] = sum_c tile[r, c] * Nq[dense_cols[c], :]
+     * (exact int32) into the scratch row of its heavy rows.  The CSR handed to the entry point must then hold only
+     * the edges OUTSIDE the region, every region row must be listed in heavy_rows (its remaining edges are covered by
+     * units, possibly none) and row_order must list the heavy rows first: its first n_skip_rows entries are left to
+     * units + finalize. */
+    const int8_t *dense_a;       /* [dense_n_tiles * 128, 128] int8: the stored tiles, row-major, entries = multiplicity */
+    int64_t dense_n_tiles;
+    const int32_t *dense_units;  /* [dense_n_units, 4] int32, 16-byte aligned */
+    int64_t dense_n_units;
+    int64_t dense_rows;          /* multiple of 128, <= n_heavy */
+    const int32_t *dense_cols;   /* [dense_n_cols] feature-row id of every column of the region */
+    int64_t dense_n_cols;        /* multiple of 128 */
+    int8_t *dense_b;             /* scratch [dense_n_cols, round_up(f, 16)] int8: the region's feature rows, packed */
+    int *dense_status;           /* optional device word that receives TANGO_ETIMEOUT if a bounded wait of the GEMM expires */
+    int64_t n_skip_rows;         /* leading entries of row_order owned by units + finalize (0 without a dense region) */
 } tango_spmm_plan;
 
 /* out[v,:] = sum_k scales[k] * float(sum_{j in segment k of row v} Nq[indices[j], :]) for v < n_rows.

@@ -31,7 +31,9 @@ class SpmmPlan(Structure):
         ("row_order", c_void_p),
         ("n_long_rows", c_int64),
         ("dense_a", c_void_p),
-        ("dense_lda", c_int64),
+        ("dense_n_tiles", c_int64),
+        ("dense_units", c_void_p),
+        ("dense_n_units", c_int64),
         ("dense_rows", c_int64),
         ("dense_cols", c_void_p),
         ("dense_n_cols", c_int64),

@@ -9,7 +9,7 @@ from __future__ import annotations
 from ._lib import ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_TRUNC
 
 _state = {"rounding": "reference", "seed": 0, "share_quantized_inputs": False, "step_counter": None,
-          "hub_block": 16384}
+          "hub_block": 163840}
 
 
 def set_rounding(mode: str = "reference", seed: int = 0) -> None:
@@ -67,10 +67,11 @@ def step_counter():
 
 
 def set_hub_block(side: int) -> None:
-    """Side length (rows = columns) of the dense hub block that graph_preprocess builds for the unweighted
-    aggregation on large power-law graphs; 0 switches it off (every edge is gathered, as the reference's CSR SpMM
-    does).  Results are bit-identical either way: the block's product is an exact int32 sum like the gathered one.
-    Applies to graphs preprocessed after the call."""
+    """Largest side (rows and columns, rounded down to 128) of the dense hub region that graph_preprocess builds for
+    the unweighted aggregation on large power-law graphs -- inside it only tiles dense enough to pay are taken; 0
+    switches it off (every edge is gathered, as the reference's CSR SpMM does).  Results are bit-identical either
+    way: the region's product is an exact int32 sum like the gathered one.  Applies to graphs preprocessed after
+    the call."""
     if side < 0:
         raise ValueError(side)
     _state["hub_block"] = int(side)

@@ -61,11 +61,13 @@ __device__ __forceinline__ float inv_scale(float s) {
     return isinf(inv) ? 0.f : inv;
 }
 
-// Internal (not exported): ws[r, c] += sum_k a[r, k] * b[k, c] as exact int32 with the tcgen05 int8 GEMM, integer
-// atomics into ws.  a is [m, lda] (reduction contiguous), b is [k, ldb] (reduction index = row), both 16-byte aligned
-// with leading dimensions that are multiples of 16.  Defined in igemm_tcgen05.cu, used by the SpMM's dense hub block.
-int igemm_accumulate_i32(const int8_t *a, int64_t lda, const int8_t *b, int64_t ldb, int64_t m, int64_t n, int64_t k,
-                         int32_t *ws, int64_t ldws, int *status, cudaStream_t stream);
+// Internal (not exported): the dense hub region of the SpMM on the tcgen05 int8 GEMM.  `tiles` holds n_tiles stored
+// 128 x 128 int8 tiles ([n_tiles * 128, 128], row-major); work item u = (row tile, first stored tile, first column
+// tile, tiles) adds sum_t tile[first + t] . b[128 (col tile + t) .. , :] into ws rows 128 * row tile .. with integer
+// atomics.  b is [k, ldb] (k a multiple of 128, ldb a multiple of 16), ws has m rows.  Defined in igemm_tcgen05.cu.
+int igemm_accumulate_tiles_i32(const int8_t *tiles, int64_t n_tiles, const int32_t *units, int64_t n_units,
+                               const int8_t *b, int64_t ldb, int64_t m, int64_t n, int64_t k, int32_t *ws,
+                               int64_t ldws, int *status, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------- Philox4x32-10
 struct Philox {

@@ -49,6 +49,7 @@ struct GemmParams {
     float *absmax;
     int *status;
     uint32_t tmem_cols;
+    const int4 *tile_units;   // igemm_kernel: CTA x works on unit x = (row tile, first stored A tile, first k block, k blocks)
     int tma_store;   // persistent kernel: the epilogue hands 32 x 16 fp32 boxes to the TMA engine (needs ldo % 4 == 0)
 };
 
@@ -174,11 +175,17 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // the swizzle needs 1024-byte aligned tiles
     const uint32_t stage_bytes = kABytes + p.b_bytes;
-    const int m0 = blockIdx.x * kTileM;
+    // Regular mode: CTA (x, y, z) = (row tile, column tile, slice of the reduction).  Tile-list mode (the SpMM's dense
+    // hub region): CTA x takes work item x; its A tiles are stored one after the other as [128, 128] boxes.
+    int m0 = blockIdx.x * kTileM;
     const int n0 = blockIdx.y * p.n_tile;
-    const int kb_begin = blockIdx.z * p.kb_per_split;
-    const int kb_end = min(p.kb_total, kb_begin + p.kb_per_split);
-    const int n_iter = kb_end - kb_begin;
+    int kb_begin = blockIdx.z * p.kb_per_split;
+    int n_iter = min(p.kb_total, kb_begin + p.kb_per_split) - kb_begin;
+    int a_tile0 = -1;
+    if (p.tile_units) {
+        const int4 u = __ldg(p.tile_units + blockIdx.x);
+        m0 = u.x * kTileM; a_tile0 = u.y; kb_begin = u.z; n_iter = u.w;
+    }
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -214,7 +221,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                 const uint32_t a_dst = smem_base + s * stage_bytes, b_dst = a_dst + kABytes;
                 const int kc = (kb_begin + it) * kBlockK;
                 mbar_expect_tx(full, stage_bytes);
-                if (!p.a_mn) tma_load_2d(a_dst, &tm_a, full, kc, m0);
+                if (a_tile0 >= 0) tma_load_2d(a_dst, &tm_a, full, 0, (a_tile0 + it) * kTileM);
+                else if (!p.a_mn) tma_load_2d(a_dst, &tm_a, full, kc, m0);
                 else tma_load_2d(a_dst, &tm_a, full, m0, kc);
                 if (!p.b_mn) {
                     tma_load_2d(b_dst, &tm_b, full, kc, n0);
@@ -701,7 +709,6 @@ struct GemmCall {
     float *out; int64_t ldo; int32_t *ws; int64_t ldws;
     const float *sa, *sb, *bias; float *absmax; int *status;
     const float *out_row_scale = nullptr;
-    int pipeline_bytes = 98304;   // shared memory for the TMA ring of igemm_kernel (98304 lets two CTAs share an SM)
 };
 
 static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
@@ -721,7 +728,7 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
     p.b_boxes = c.b_mn ? (int)ceil_div(p.n_tile, 128) : 1;
     p.b_bytes = c.b_mn ? p.b_boxes * kABytes : (int)round_up((int64_t)p.n_tile * kBlockK, 1024);
     const int stage_bytes = kABytes + p.b_bytes;
-    p.stages = c.pipeline_bytes / stage_bytes;
+    p.stages = 98304 / stage_bytes;
     if (p.stages < 2) p.stages = 2;
     if (p.stages > 6) p.stages = 6;
     p.mode = c.mode; p.out = c.out; p.ldo = c.ldo; p.ws = c.ws; p.ldws = c.ldws;
@@ -785,18 +792,44 @@ static int launch_gemm(const GemmCall &c, cudaStream_t stream) {
     return TANGO_OK;
 }
 
-int igemm_accumulate_i32(const int8_t *a, int64_t lda, const int8_t *b, int64_t ldb, int64_t m, int64_t n, int64_t k,
-                         int32_t *ws, int64_t ldws, int *status, cudaStream_t stream) {
-    if (m <= 0 || n <= 0 || k <= 0) return TANGO_OK;
-    // D[m, n] += A[m, k] . B[k, n]: A K-major, B stored with the reduction index as its row; two splits of the
-    // reduction when one wave of tiles would leave SMs idle
-    const int64_t tiles = ceil_div(m, kTileM) * ceil_div(n, 256);
-    int splits = (int)(kNumSMs / (tiles > 0 ? tiles : 1));
-    if (splits < 1) splits = 1;
-    if (splits > 8) splits = 8;
-    GemmCall c{a, lda, 0, b, ldb, 1, m, n, k, 1, splits, nullptr, 0, ws, ldws, nullptr, nullptr, nullptr, nullptr, status};
-    c.pipeline_bytes = 196608;    // one CTA per SM: a deeper ring instead of a second resident CTA
-    return launch_gemm(c, stream);
+int igemm_accumulate_tiles_i32(const int8_t *tiles, int64_t n_tiles, const int32_t *units, int64_t n_units,
+                               const int8_t *b, int64_t ldb, int64_t m, int64_t n, int64_t k, int32_t *ws,
+                               int64_t ldws, int *status, cudaStream_t stream) {
+    if (n_units <= 0 || n <= 0) return TANGO_OK;
+    if (m <= 0 || k <= 0 || n_tiles <= 0 || m % kTileM || k % kBlockK) return TANGO_EINVAL;
+    if (m > 0x7fffffff || k > 0x7fffffff || n_tiles * kTileM > 0x7fffffff || n_units > 0x7fffffff) return TANGO_ESIZE;
+    if (!aligned(tiles, 16) || !aligned(b, 16) || ldb % 16 || !aligned(units, 16)) return TANGO_EALIGN;
+    GemmParams p{};
+    p.M = (int)m; p.N = (int)n; p.K = (int)k;
+    const int n_tiles_n = (int)ceil_div(n, 256);
+    p.n_tile = (int)round_up(ceil_div(n, n_tiles_n), 16);
+    p.kb_total = (int)(k / kBlockK);
+    p.kb_per_split = p.kb_total;
+    p.a_mn = 0; p.b_mn = 1;
+    p.b_boxes = (int)ceil_div(p.n_tile, 128);
+    p.b_bytes = p.b_boxes * kABytes;
+    const int stage_bytes = kABytes + p.b_bytes;
+    // work items outnumber the SMs several times: two CTAs per SM when the ring still gets three stages each
+    p.stages = 98304 / stage_bytes;
+    if (p.stages < 3) p.stages = 196608 / stage_bytes;
+    if (p.stages > 6) p.stages = 6;
+    if (p.stages < 2) p.stages = 2;
+    p.mode = 1; p.ws = ws; p.ldws = ldws; p.status = status;
+    p.tile_units = reinterpret_cast<const int4 *>(units);
+    p.tmem_cols = 32;
+    while ((int)p.tmem_cols < p.n_tile) p.tmem_cols <<= 1;
+    CUtensorMap tm_a, tm_b;
+    int rc = make_map(&tm_a, tiles, kBlockK, n_tiles * kTileM, kBlockK, kBlockK, kTileM);   // one box = one stored tile
+    if (rc) return rc;
+    rc = make_map(&tm_b, b, n, k, ldb, 128, kBlockK);
+    if (rc) return rc;
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024;
+    TANGO_CUDA_TRY(cudaFuncSetAttribute(igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    const dim3 grid((unsigned)n_units, (unsigned)n_tiles_n, 1);
+    if (grid.y > 65535) return TANGO_ESIZE;
+    igemm_kernel<<<grid, 192, smem, stream>>>(tm_a, tm_b, p);
+    TANGO_LAUNCH_CHECK();
+    return TANGO_OK;
 }
 
 }  // namespace tango

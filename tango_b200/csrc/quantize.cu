@@ -188,6 +188,77 @@ __global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__
     }
 }
 
+// Contiguous fp32 input of any row width (ldx == cols, e.g. 602 columns: rows that are only 8-byte aligned) to int8
+// rows padded to ldq: a CTA takes R consecutive rows, whose floats are ONE contiguous, 16-byte aligned span -- read
+// with perfectly coalesced 128-bit loads whatever the row width -- rounds them, lays the bytes out at the padded
+// pitch in shared memory (pad bytes zero), and writes the block, which is contiguous in the output too, with
+// coalesced 128-bit stores.  R is a multiple of 16, so a block starts on a multiple of four elements and a float4
+// never straddles two Philox blocks.
+__global__ void __launch_bounds__(256) quantize_repitch_kernel(const float *__restrict__ x, int64_t rows, int cols,
+                                                               const float *__restrict__ row_scale,
+                                                               const float *__restrict__ scale, int8_t *__restrict__ q,
+                                                               int ldq, int R, int mode, uint64_t seed, uint64_t call0,
+                                                               const unsigned long long *__restrict__ step,
+                                                               const PushTargets push) {
+    extern __shared__ __align__(16) int8_t rp_tile[];
+    const uint64_t call = effective_call(call0, step);
+    const float inv = inv_scale(__ldg(scale));
+    const Philox ph{(uint32_t)seed, (uint32_t)(seed >> 32)};
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int pad = ldq - cols;
+    for (int64_t r0 = (int64_t)blockIdx.x * R; r0 < rows; r0 += (int64_t)gridDim.x * R) {
+        const int nr = (int)min((int64_t)R, rows - r0);
+        const int n_el = nr * cols;
+        for (int i = tid; i < nr * pad; i += nthr) rp_tile[(i / pad) * ldq + cols + i % pad] = 0;
+        const float *base = x + r0 * cols;
+        const uint64_t flat_base = (uint64_t)r0 * (uint64_t)cols;      // multiple of 16 elements
+        const int n4 = n_el >> 2;
+        for (int i = tid; i < n4; i += nthr) {
+            const float4 v4 = __ldcs(reinterpret_cast<const float4 *>(base) + i);
+            const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+            int r = (4 * i) / cols, c = 4 * i - r * cols;
+            uint4 rnd = make_uint4(0, 0, 0, 0);
+            if (mode == TANGO_ROUND_STOCHASTIC) {
+                const uint64_t blk = (flat_base >> 2) + (uint64_t)i;
+                rnd = ph((uint32_t)blk, (uint32_t)(blk >> 32), (uint32_t)call, (uint32_t)(call >> 32));
+            }
+            const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+            float rs = row_scale ? __ldg(row_scale + r0 + r) : 1.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float t = row_scale ? __fmul_rn(v[e], rs) : v[e];
+                t = __fmul_rn(t, inv);
+                const float u = (mode == TANGO_ROUND_STOCHASTIC) ? __fmul_rn((float)(rr[e] >> 8), 5.9604644775390625e-08f) : 0.f;
+                rp_tile[r * ldq + c] = (int8_t)round_to_i8(t, mode, u);
+                if (++c == cols) {
+                    c = 0; ++r;
+                    if (row_scale && e < 3 && r < nr) rs = __ldg(row_scale + r0 + r);
+                }
+            }
+        }
+        for (int k = (n4 << 2) + tid; k < n_el; k += nthr) {          // last block only: up to three leftover elements
+            const int r = k / cols, c = k - r * cols;
+            float t = base[k];
+            if (row_scale) t = __fmul_rn(t, __ldg(row_scale + r0 + r));
+            t = __fmul_rn(t, inv);
+            float u = 0.f;
+            if (mode == TANGO_ROUND_STOCHASTIC) {
+                uint64_t cached = ~0ull;
+                uint4 rnd;
+                u = sr_uniform(ph, flat_base + (uint64_t)k, call, cached, rnd);
+            }
+            rp_tile[r * ldq + c] = (int8_t)round_to_i8(t, mode, u);
+        }
+        __syncthreads();
+        const int ppr = ldq >> 4, pieces = nr * ppr;
+        for (int i = tid; i < pieces; i += nthr) {
+            const int r = i / ppr, c0 = (i - r * ppr) << 4;
+            store_piece(q, push, r0 + r, ldq, c0, *reinterpret_cast<const uint4 *>(rp_tile + (size_t)i * 16));
+        }
+        __syncthreads();
+    }
+}
+
 // Generic (unaligned output) version: one thread per output byte.
 __global__ void __launch_bounds__(256) quantize_scalar_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
                                                               int64_t ldx, const float *__restrict__ row_scale,
@@ -308,6 +379,20 @@ static int launch_quantize(const float *x, int64_t rows, int64_t cols, int64_t l
         if (ldq % 16 != 0) return TANGO_EALIGN;      // every piece of a pushed row is one aligned 128-bit store
     } else if (ldq == cols && ldx == cols && !row_scale) {  // contiguous in and out: one flat row (same flat index)
         cols = rows * cols; rows = 1; ldx = ldq = cols;
+    }
+    // contiguous rows of any width, padded int8 rows: the block-repitching kernel streams both sides fully coalesced
+    if (rows >= 16 && ldx == cols && aligned(x, 16) && ldq % 16 == 0 && ldq <= 4096 && cols < (1 << 24) &&
+        (push.n > 0 || aligned(q, 16))) {
+        int R = (int)((12288 / cols) / 16 * 16);
+        if (R < 16) R = 16;
+        while ((int64_t)R * ldq > 40960 && R > 16) R -= 16;
+        if ((int64_t)R * cols < (1 << 28)) {
+            const int grid = stream_grid(ceil_div(rows, R) * 256, 256, 8);
+            quantize_repitch_kernel<<<grid, 256, (size_t)R * ldq, stream>>>(x, rows, (int)cols, row_scale, scale, q, (int)ldq, R,
+                                                                       mode, seed, call, step, push);
+            TANGO_LAUNCH_CHECK();
+            return TANGO_OK;
+        }
     }
     if (push.n > 0 || ((ldq % 16 == 0 || rows == 1) && aligned(q, 16))) {
         const int lw = (aligned(x, 16) && (rows == 1 || ldx % 4 == 0)) ? 4 : (aligned(x, 8) && (rows == 1 || ldx % 2 == 0)) ? 2 : 1;

@@ -421,10 +421,24 @@ __global__ void __launch_bounds__(128, MULTI ? 8 : 10) spmm_short_kernel(const S
 #pragma unroll
             for (int i = 0; i < VEC; ++i) facc[i] = __fadd_rn(0.f, __fmul_rn((float)acc[i], sc));
         }
+        // short rows are as much epilogue as gather: the optional per-element steps are decided once, not per element
+        if (a.row_scale) {
+            const float rs = __ldg(a.row_scale + row);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-            facc[i] = finish_value(facc[i], row, min(off + i, a.f - 1), a);
-            if (off + i < a.f) amax = fmaxf(amax, fabsf(facc[i]));
+            for (int i = 0; i < VEC; ++i) facc[i] = __fmul_rn(facc[i], rs);
+        }
+        if (a.bias) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) facc[i] = __fadd_rn(facc[i], __ldg(a.bias + min(off + i, a.f - 1)));
+        }
+        if (a.relu) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) facc[i] = fmaxf(facc[i], 0.f);
+        }
+        if (a.out_absmax) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i)
+                if (off + i < a.f) amax = fmaxf(amax, fabsf(facc[i]));
         }
         if (VEC == 16 && off + 16 <= a.f && (a.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) {
 #pragma unroll
@@ -579,16 +593,17 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
         a.n_heavy = plan->n_heavy; a.ws = plan->ws; a.ws_ld = plan->ws_ld; a.split_threshold = plan->split_threshold;
         TANGO_CUDA_TRY(cudaMemsetAsync(a.ws, 0, sizeof(int32_t) * (size_t)(a.n_heavy * a.nseg * a.ws_ld), stream));
     }
-    const bool dense = plan && plan->dense_a && plan->dense_rows > 0 && plan->dense_n_cols > 0;
+    const bool dense = plan && plan->dense_a && plan->dense_rows > 0 && plan->dense_n_cols > 0 && plan->dense_n_units > 0;
     if (dense) {
         // dense hub block: pack the block's feature rows, multiply on the tensor cores, add into the heavy rows'
         // int32 scratch (cleared above); the gather kernels below then cover only the edges outside the block
         if (MODE != MODE_COPY || a.nseg != 1 || plan->n_units < 0 || !plan->heavy_rows || !plan->ws ||
-            plan->dense_rows > plan->n_heavy || !plan->dense_cols || !plan->dense_b || plan->dense_lda < plan->dense_n_cols ||
+            plan->dense_rows > plan->n_heavy || !plan->dense_cols || !plan->dense_b || !plan->dense_units ||
+            plan->dense_n_tiles <= 0 || plan->dense_rows % 128 || plan->dense_n_cols % 128 ||
             plan->n_skip_rows != plan->n_heavy || !plan->row_order || plan->ws_ld < a.f)
             return TANGO_EINVAL;
-        if (a.ld % 16 || !aligned(a.feat, 16) || plan->dense_lda % 16 || plan->dense_n_cols % 16 ||
-            !aligned(plan->dense_a, 16) || !aligned(plan->dense_b, 16))
+        if (a.ld % 16 || !aligned(a.feat, 16) || !aligned(plan->dense_a, 16) || !aligned(plan->dense_b, 16) ||
+            !aligned(plan->dense_units, 16))
             return TANGO_EALIGN;
         if (plan->n_units == 0) {      // no unit set the scratch fields above
             a.heavy_rows = plan->heavy_rows; a.n_heavy = plan->n_heavy; a.ws = plan->ws; a.ws_ld = plan->ws_ld;
@@ -609,8 +624,9 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
             }
             TANGO_LAUNCH_CHECK();
         }
-        const int rc = igemm_accumulate_i32(plan->dense_a, plan->dense_lda, plan->dense_b, ldb, plan->dense_rows, a.f,
-                                            plan->dense_n_cols, a.ws, a.ws_ld, plan->dense_status, stream);
+        const int rc = igemm_accumulate_tiles_i32(plan->dense_a, plan->dense_n_tiles, plan->dense_units,
+                                                  plan->dense_n_units, plan->dense_b, ldb, plan->dense_rows, a.f,
+                                                  plan->dense_n_cols, a.ws, a.ws_ld, plan->dense_status, stream);
         if (rc) return rc;
     }
     if (plan && plan->n_skip_rows > 0) {

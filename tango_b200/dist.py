@@ -24,6 +24,9 @@ from . import config
 from .graph import HUB_BLOCK_MIN_DENSITY, Graph, HubBlock, RowPartition, balanced_bounds, uniform_bounds
 
 
+HUB_BLOCK_MIN_EDGES = 4_000_000     # smaller graphs are launch-bound: the dense hub block would not pay for its launches
+
+
 def all_gather_quantized(q_local: torch.Tensor, s_local: torch.Tensor, shard_rows: int, group=None,
                          gather_scales: bool = True):
     """Gathers every rank's int8 shard ([<= shard_rows, ld], same ld everywhere) and scale.
@@ -93,10 +96,9 @@ class DistGraph:
         # rows x the most referenced rows of the gathered table, multiplied on the tensor cores
         self.hubs = {}
         side = config.hub_block()
-        if scale_mode == "global" and side > 0 and g.device.type == "cuda" and g.num_edges() >= 4_000_000:
-            rows_side = max(128, side // world // 128 * 128)
+        if scale_mode == "global" and side > 0 and g.device.type == "cuda" and g.num_edges() >= HUB_BLOCK_MIN_EDGES:
             for key, part in (("fwd", self.fwd), ("bwd", self.bwd)):
-                hub = HubBlock(part.indptr_flat, part.indices, world * self.shard_rows, rows_side, side,
+                hub = HubBlock(part.indptr_flat, part.indices, world * self.shard_rows, side, side,
                                HUB_BLOCK_MIN_DENSITY)
                 if hub.ok:
                     self.hubs[key] = hub

@@ -270,8 +270,12 @@ class SpmmSchedule:
         if force_heavy is None:
             # rows in order of decreasing length: the warps of a CTA then work on rows of similar length and the
             # longest rows start first
-            self.row_order = torch.argsort(row_deg, descending=True, stable=True).to(torch.int32)
+            order = torch.argsort(row_deg, descending=True, stable=True)
             self.n_long = int((row_deg > SHORT_ROW_NNZ).sum())
+            # the short rows (a lane group each) are taken in natural order: neighbouring groups then read neighbouring
+            # row bounds and index runs and write neighbouring output rows
+            order[self.n_long:] = torch.sort(order[self.n_long:])[0]
+            self.row_order = order.to(torch.int32)
             heavy = torch.nonzero(row_deg > threshold).flatten()
         else:
             assert nseg == 1
@@ -283,9 +287,11 @@ class SpmmSchedule:
             is_heavy[heavy] = True
             rest = torch.nonzero(~is_heavy).flatten()
             rest = rest[torch.argsort(row_deg[rest], descending=True, stable=True)]
+            n_rest_long = int((row_deg[rest] > SHORT_ROW_NNZ).sum())
+            rest[n_rest_long:] = torch.sort(rest[n_rest_long:])[0]         # short rows in natural order (see above)
             self.row_order = torch.cat([heavy, rest]).to(torch.int32)
             self.n_skip = int(heavy.numel())
-            self.n_long = self.n_skip + int((row_deg[rest] > SHORT_ROW_NNZ).sum())
+            self.n_long = self.n_skip + n_rest_long
         self.n_block_rows = int((row_deg > BLOCK_ROW_NNZ).sum())   # rows that deserve a whole CTA in row-team kernels
         self.n_heavy = int(heavy.numel())
         self.heavy_rows = heavy.to(torch.int32)
@@ -309,60 +315,109 @@ class SpmmSchedule:
         self.n_units = int(self.units.shape[0])
 
 
-HUB_BLOCK_MIN_DENSITY = 0.04   # below this a dense int8 product costs more than gathering the block's edges
+HUB_BLOCK_MIN_DENSITY = 0.035   # a 128 x 128 tile below this density costs more as a dense int8 product than its
+                                # edges cost to gather (break-even measured at about 2.7 %)
+HUB_TILE = 128
 
 
 class HubBlock:
-    """The dense hub block of an aggregation matrix (CSR-like `indptr`, `indices` over `n_cols` feature rows): its
-    `rows` (the block_rows longest rows) x `cols` (the block_cols most referenced columns) sub-matrix as a dense int8
-    0/1 array `dense` [rows, cols], the remaining edges as a CSR of their own (`indptr`, `indices`: every edge of the
-    matrix is in exactly one of the two), and the row schedule of that remainder with the block's rows forced through
-    the int32 scratch, where the tensor-core product of the block and the gathered remainder meet.
+    """The dense hub region of an aggregation matrix (CSR-like `indptr`, `indices` over `n_cols` feature rows).
 
-    On the power-law graphs this library trains on, 7 % of the rows x 7 % of the columns hold 44 % of the edges at a
-    density of 19 %: multiplying that block as a dense matrix replaces 50 M 256-byte gathers through L2 with a
-    16384 x 16384 x 256 int8 product.  Exact int32 either way, so results do not change by a bit."""
+    Rows are ranked by length and columns by how often they are referenced; in that order the matrix of a power-law
+    graph is densest in its top-left corner and thins out smoothly, so the region worth multiplying as a dense 0/1
+    int8 matrix on the tensor cores is a staircase: row tile i (128 rows) keeps its first `kend[i]` column tiles
+    (128 columns each), the prefix that maximises (edges covered x cost of gathering an edge - tiles x cost of a tile
+    product) for tiles of at least `min_density`.  The region is stored tile by tile (`dense`: [n_tiles * 128, 128]
+    int8, multiplicities), cut into work items `units` = (row tile, first stored tile, first column tile, tiles) of
+    bounded length for the GEMM kernel; `cols` lists the feature rows of the columns used.  The edges outside the
+    region form a CSR of their own (`indptr`, `indices`), whose row schedule forces the region's rows through the
+    int32 scratch, where the tensor-core product and the gathered remainder meet.  Exact int32 either way, so results
+    do not change by a bit.
 
-    def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, n_cols: int, block_rows: int = 16384,
-                 block_cols: int = 16384, min_density: float = HUB_BLOCK_MIN_DENSITY):
+    On the 232,965-node / 114.6 M-edge graph the region holds about two thirds of the edges in 24 K tiles (0.4 GB)."""
+
+    def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, n_cols: int, max_rows: int = 163840,
+                 max_cols: int = 163840, min_density: float = HUB_BLOCK_MIN_DENSITY):
         dev = indptr.device
+        T = HUB_TILE
         ip = indptr.long()
         n_rows = ip.numel() - 1
         row_deg = ip[1:] - ip[:-1]
-        kr = min(block_rows, n_rows) // 128 * 128
-        ks = min(block_cols, n_cols) // 128 * 128
+        ntr = min(max_rows, n_rows) // T
+        ntc = min(max_cols, n_cols) // T
         self.ok = False
-        if kr <= 0 or ks <= 0:
+        if ntr <= 0 or ntc <= 0 or indices.numel() == 0:
             return
         col_deg = torch.bincount(indices.long(), minlength=n_cols)
-        rows = torch.argsort(row_deg, descending=True, stable=True)[:kr]
-        cols = torch.argsort(col_deg, descending=True, stable=True)[:ks]
+        rows = torch.argsort(row_deg, descending=True, stable=True)[:ntr * T]
+        cols = torch.argsort(col_deg, descending=True, stable=True)[:ntc * T]
         row_slot = torch.full((n_rows,), -1, dtype=torch.int64, device=dev)
-        row_slot[rows] = torch.arange(kr, device=dev)
+        row_slot[rows] = torch.arange(ntr * T, device=dev)
         col_pos = torch.full((n_cols,), -1, dtype=torch.int64, device=dev)
-        col_pos[cols] = torch.arange(ks, device=dev)
+        col_pos[cols] = torch.arange(ntc * T, device=dev)
         edge_row = torch.repeat_interleave(torch.arange(n_rows, device=dev), row_deg)
         rs, cp = row_slot[edge_row], col_pos[indices.long()]
-        in_blk = (rs >= 0) & (cp >= 0)
-        self.n_block_edges = int(in_blk.sum())
-        self.density = self.n_block_edges / float(kr * ks)
-        if self.density < min_density:
+        cand = (rs >= 0) & (cp >= 0)
+        cnt = torch.bincount((rs[cand] // T) * ntc + cp[cand] // T, minlength=ntr * ntc).view(ntr, ntc)
+        # per row tile: the prefix of column tiles with the largest net benefit; one tile costs as much as gathering
+        # min_density * T * T edges (min_density == 0: every tile inside the caps is taken)
+        if min_density > 0:
+            gain = torch.cumsum(cnt.double() - min_density * T * T, dim=1)
+            best, arg = gain.max(dim=1)
+            kend = torch.where(best > 0, arg + 1, torch.zeros_like(arg))
+        else:
+            kend = torch.full((ntr,), ntc, dtype=torch.int64, device=dev)
+        used = torch.nonzero(kend > 0).flatten()
+        if used.numel() == 0:
             return
-        dense = torch.zeros(kr * ks, dtype=torch.int8, device=dev)
-        dense.index_put_((rs[in_blk] * ks + cp[in_blk],), torch.ones(1, dtype=torch.int8, device=dev).expand(
-            self.n_block_edges), accumulate=True)            # multiplicity (1 on a simple graph)
-        self.dense = dense.view(kr, ks)
+        ntr = int(used.max()) + 1                      # row tiles 0 .. ntr-1 take part (some may have no tile)
+        kend = kend[:ntr]
+        self.kend = kend
+        tile_base = torch.cumsum(kend, 0) - kend
+        n_tiles = int(kend.sum())
+        ks = int(kend.max()) * T
+        in_blk = cand & (rs < ntr * T)
+        in_blk &= (cp // T) < kend[(rs // T).clamp(max=ntr - 1)]
+        self.n_block_edges = int(in_blk.sum())
+        self.n_tiles = n_tiles
+        self.density = self.n_block_edges / float(n_tiles * T * T)
+        rb, cb = rs[in_blk], cp[in_blk]
+        tile = tile_base[rb // T] + cb // T
+        dense = torch.zeros(n_tiles * T * T, dtype=torch.int8, device=dev)
+        dense.index_put_(((tile * T + rb % T) * T + cb % T,),
+                         torch.ones(1, dtype=torch.int8, device=dev).expand(self.n_block_edges), accumulate=True)
+        self.dense = dense.view(n_tiles * T, T)
+        # GEMM work items of bounded length, longest first
+        chunk = max(8, min(128, -(-n_tiles // (148 * 4))))
+        n_chunks = (kend + chunk - 1) // chunk
+        rep = torch.repeat_interleave(torch.arange(ntr, device=dev), n_chunks)
+        first = torch.cumsum(n_chunks, 0) - n_chunks
+        k0 = (torch.arange(rep.numel(), device=dev) - first[rep]) * chunk
+        length = torch.minimum(kend[rep] - k0, torch.full_like(k0, chunk))
+        order = torch.argsort(length, descending=True, stable=True)
+        self.units = torch.stack([rep, tile_base[rep] + k0, k0, length], dim=1)[order].to(torch.int32).contiguous()
         keep = ~in_blk
         self.indices = indices[keep].contiguous()
         tail_deg = row_deg - torch.bincount(edge_row[in_blk], minlength=n_rows)
         tip = torch.zeros(n_rows + 1, dtype=torch.int64, device=dev)
         torch.cumsum(tail_deg, 0, out=tip[1:])
         self.indptr = tip.to(torch.int32)
-        self.rows = rows.to(torch.int32)
-        self.cols = cols.to(torch.int32).contiguous()
-        self.schedule = SpmmSchedule(self.indptr, force_heavy=rows)
+        self.rows = rows[:ntr * T].to(torch.int32)
+        self.cols = cols[:ks].to(torch.int32).contiguous()
+        self.schedule = SpmmSchedule(self.indptr, force_heavy=rows[:ntr * T])
         self.schedule.hub = self
         self.ok = True
+
+    def to_dense(self) -> torch.Tensor:
+        """The region as an ordinary [rows, cols] int32 matrix (zero outside the staircase); for tests."""
+        T = HUB_TILE
+        out = torch.zeros((self.rows.numel(), self.cols.numel()), dtype=torch.int32, device=self.dense.device)
+        base = torch.cumsum(self.kend, 0) - self.kend
+        for i in range(self.kend.numel()):
+            for k in range(int(self.kend[i])):
+                t = int(base[i]) + k
+                out[i * T:(i + 1) * T, k * T:(k + 1) * T] = self.dense[t * T:(t + 1) * T].int()
+        return out
 
 
 def balanced_bounds(weights: torch.Tensor, world: int):

@@ -249,7 +249,8 @@ def _make_plan(sched: Optional[SpmmSchedule], f: int, device):
     keep = [plan, ws]
     if hub is not None:
         packed = torch.empty((hub.cols.numel(), ws_ld), dtype=torch.int8, device=device)
-        plan.dense_a, plan.dense_lda, plan.dense_rows = hub.dense.data_ptr(), hub.dense.stride(0), hub.dense.shape[0]
+        plan.dense_a, plan.dense_n_tiles, plan.dense_rows = hub.dense.data_ptr(), hub.n_tiles, hub.rows.numel()
+        plan.dense_units, plan.dense_n_units = hub.units.data_ptr(), hub.units.shape[0]
         plan.dense_cols, plan.dense_n_cols = hub.cols.data_ptr(), hub.cols.numel()
         plan.dense_b, plan.dense_status = packed.data_ptr(), _status_word(device).data_ptr()
         plan.n_skip_rows = sched.n_skip
@@ -453,7 +454,7 @@ def mySDDMM_int8(g, op, U, V, scaleU, scaleV, isReduce, reverse=False):
     out = torch.empty(out_shape, dtype=torch.float32, device=src.device)
     scale = torch.zeros((1,), dtype=torch.float32, device=src.device) if isReduce else torch.Tensor()
     done = False
-    if (op == "dot" and src.numel() >= ROWWISE_SDDMM_MIN_DEGREE * g.num_nodes() and U.shape[1:] == V.shape[1:]
+    if (op == "dot" and src.numel() > 0 and src.numel() >= ROWWISE_SDDMM_MIN_DEGREE * g.num_nodes() and U.shape[1:] == V.shape[1:]
             and U.dim() == 3 and U.shape[0] == g.num_nodes() == V.shape[0]):
         # walk the rows of the fixed endpoint: V's row stays in registers, only U is gathered (half the gathered
         # bytes of the endpoint-list kernel, and half its index stream); long rows get a warp, rows of a few edges a

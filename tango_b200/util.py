@@ -11,9 +11,10 @@ def graph_preprocess(graph: Graph, hub_block=None) -> Graph:
     """Materialises the CSR / CSC index bundles (and the long-row schedules of the SpMM kernels) once, so that no
     operator call pays for a sort.  `graph.coo`, `graph.inc_in` and `graph.inc_out` are derived on access.
 
-    hub_block: side length of the dense hub block that the unweighted aggregation (csr_SPMM / spmm_copy_u) multiplies
-    on the tensor cores instead of gathering (see graph.HubBlock); None takes config.hub_block() (0 = off), and the
-    block is then only built for graphs large and skewed enough to profit; an explicit side is always honoured."""
+    hub_block: largest side (rows, columns) of the dense hub region that the unweighted aggregation (csr_SPMM /
+    spmm_copy_u) multiplies on the tensor cores instead of gathering (see graph.HubBlock); None takes
+    config.hub_block() (0 = off), and the region is then only built for graphs large enough to profit and only from
+    tiles dense enough to pay; an explicit side is always honoured and takes every tile inside it."""
     assert graph.device.type == "cuda", "graph must be on GPU"
     side = config.hub_block() if hub_block is None else int(hub_block)
     forced = hub_block is not None

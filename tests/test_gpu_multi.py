@@ -16,18 +16,25 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out_dir, balance, scale_mode, transport="nccl"):
+def _worker(rank, world, port, out_dir, balance, scale_mode, transport="nccl", hub=0):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     import torch.nn.functional as F
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import tango_b200.dist as tdist
+    from tango_b200 import config
     from tango_b200.dist import DistGCN, DistGraph, allreduce_grads
     from tango_b200.graph import rmat_graph
     n = 5003
     g = rmat_graph(n, 120000, 17, device=dev)
+    config.set_hub_block(hub)
+    if hub:
+        tdist.HUB_BLOCK_MIN_EDGES = 0          # force the dense hub region on this small graph:
+        tdist.HUB_BLOCK_MIN_DENSITY = 0.0      # every tile inside the 256 x 256 caps
     dg = DistGraph(g, rank, world, balance=balance, scale_mode=scale_mode, transport=transport)
+    assert bool(dg.hubs) == bool(hub)
     torch.manual_seed(4)
     model = DistGCN(dg, 100, 32, 7, 1).to(dev)
     gen = torch.Generator().manual_seed(9)
@@ -49,11 +56,11 @@ def _worker(rank, world, port, out_dir, balance, scale_mode, transport="nccl"):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("balance,scale_mode,transport", [("dealt", "global", "nccl"), ("nnz", "global", "nccl"),
-                                                          ("rows", "shard", "nccl"), ("dealt", "shard", "nccl"),
-                                                          ("cyclic", "global", "nccl"), ("dealt", "global", "peer"),
-                                                          ("nnz", "global", "peer")])
-def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode, transport):
+@pytest.mark.parametrize("balance,scale_mode,transport,hub",
+                         [("dealt", "global", "nccl", 0), ("nnz", "global", "nccl", 0), ("rows", "shard", "nccl", 0),
+                          ("dealt", "shard", "nccl", 0), ("cyclic", "global", "nccl", 0), ("dealt", "global", "peer", 0),
+                          ("nnz", "global", "peer", 0), ("dealt", "global", "peer", 256), ("dealt", "global", "nccl", 256)])
+def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode, transport, hub):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.nn.functional as F
@@ -61,7 +68,7 @@ def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode, tra
     from tango_b200.gnn import GCN
     from tango_b200.graph import rmat_graph
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), balance, scale_mode, transport), nprocs=world,
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), balance, scale_mode, transport, hub), nprocs=world,
              join=True)
     n = 5003
     g = rmat_graph(n, 120000, 17, device="cuda")

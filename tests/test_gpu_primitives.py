@@ -540,9 +540,9 @@ def test_row_gather_probe_runs_and_validates(cuda):
 @pytest.mark.parametrize("f", [256, 41, 64])
 @pytest.mark.parametrize("reverse", [False, True])
 def test_copy_u_with_dense_hub_block_is_bit_identical(cuda, f, reverse):
-    """Aggregation with the hub block multiplied on the tensor cores (forced here on a small graph: 256 x 256 block,
-    i.e. two 128-row GEMM tiles, next to rows that are sliced by length) against the oracle and against the
-    all-gather path: same bits."""
+    """Aggregation with the dense hub region multiplied on the tensor cores (forced here on a small graph: all tiles
+    of the top 256 x 256 corner, then -- hub_block=-1 below -- a density-selected staircase) against the oracle and
+    against the gather-only path: same bits."""
     import tango_b200 as T
     from tango_b200 import kernels as K
     from tango_b200.graph import rmat_graph
@@ -572,3 +572,11 @@ def test_copy_u_with_dense_hub_block_is_bit_identical(cuda, f, reverse):
     assert not g._hubs
     plain = K.csr_SPMM(g, nt, _scale_t(sc), reverse, rs, bias, True)
     assert torch.equal(plain, got)
+    # a staircase chosen by density (several row tiles with different extents, several work items per row tile)
+    from tango_b200.graph import HubBlock
+    ipt, idt, _ = g.adj_csr if reverse else g.adj_csc
+    hub = HubBlock(ipt, idt, n, 4096, 4096, 0.02)
+    assert hub.ok and hub.kend.numel() > 2 and int(hub.kend.min()) < int(hub.kend.max())
+    g._hubs = {key: hub}
+    stair = K.csr_SPMM(g, nt, _scale_t(sc), reverse, rs, bias, True)
+    assert K.device_status() == 0 and torch.equal(stair, got)

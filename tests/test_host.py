@@ -320,29 +320,40 @@ def test_dw_workspace_query_saturates_instead_of_wrapping():
 
 
 def test_hub_block_partitions_the_edges_exactly():
-    """Dense hub block + remaining CSR = the original adjacency, edge for edge; the block's rows lead heavy_rows and
-    row_order, and the row kernels are told to skip them."""
+    """Dense hub region (stored tile by tile) + remaining CSR = the original adjacency, edge for edge; the region's
+    rows lead heavy_rows and row_order, the row kernels are told to skip them, and the GEMM work items cover every
+    stored tile exactly once."""
     g = rmat_graph(3000, 60000, 5, device="cpu")
     ip, idx, _ = g.adj_csc
     n = g.num_nodes()
-    hub = HubBlock(ip, idx, n, 256, 384, 0.0)
-    assert hub.ok and hub.dense.shape == (256, 384) and 0 < hub.density < 1
     full = torch.zeros((n, n), dtype=torch.int32)
     rows = torch.repeat_interleave(torch.arange(n), (ip[1:] - ip[:-1]).long())
     full.index_put_((rows, idx.long()), torch.ones(1, dtype=torch.int32).expand(idx.numel()), accumulate=True)
-    rest = torch.zeros_like(full)
-    trows = torch.repeat_interleave(torch.arange(n), (hub.indptr[1:] - hub.indptr[:-1]).long())
-    rest.index_put_((trows, hub.indices.long()), torch.ones(1, dtype=torch.int32).expand(hub.indices.numel()),
-                    accumulate=True)
-    assert int(rest[hub.rows.long()[:, None], hub.cols.long()[None, :]].sum()) == 0      # nothing of the block remains
-    rest[hub.rows.long()[:, None], hub.cols.long()[None, :]] += hub.dense.int()
-    assert torch.equal(full, rest)
-    s = hub.schedule
-    assert s.n_skip == s.n_heavy >= 256 and torch.equal(s.heavy_rows[:256], hub.rows)
-    assert torch.equal(s.row_order[:s.n_skip], s.heavy_rows)
-    assert sorted(s.row_order.tolist()) == list(range(n))
-    tail_deg = (hub.indptr[1:] - hub.indptr[:-1]).long()
-    listed = s.row_order[s.n_skip:].long()
-    assert bool((tail_deg[listed] <= s.threshold).all())
-    # a sparse block is refused
+    for caps in ((256, 384, 0.0), (1024, 1024, 0.035)):
+        hub = HubBlock(ip, idx, n, *caps)
+        assert hub.ok and 0 < hub.density < 1 and hub.dense.shape == (hub.n_tiles * 128, 128)
+        if caps[2] == 0.0:
+            assert hub.kend.tolist() == [3, 3]                      # every tile inside the caps
+        else:
+            assert hub.kend[0] == hub.kend.max() and hub.kend.min() >= 0   # a staircase
+        rest = torch.zeros_like(full)
+        trows = torch.repeat_interleave(torch.arange(n), (hub.indptr[1:] - hub.indptr[:-1]).long())
+        rest.index_put_((trows, hub.indices.long()), torch.ones(1, dtype=torch.int32).expand(hub.indices.numel()),
+                        accumulate=True)
+        rest[hub.rows.long()[:, None], hub.cols.long()[None, :]] += hub.to_dense()
+        assert torch.equal(full, rest)
+        covered = torch.zeros(hub.n_tiles, dtype=torch.int32)
+        base = torch.cumsum(hub.kend, 0) - hub.kend
+        for rt, t0, k0, cnt in hub.units.tolist():
+            assert t0 == int(base[rt]) + k0 and k0 + cnt <= int(hub.kend[rt])
+            covered[t0:t0 + cnt] += 1
+        assert bool((covered == 1).all())
+        s = hub.schedule
+        nr = hub.rows.numel()
+        assert s.n_skip == s.n_heavy >= nr and torch.equal(s.heavy_rows[:nr], hub.rows)
+        assert torch.equal(s.row_order[:s.n_skip], s.heavy_rows)
+        assert sorted(s.row_order.tolist()) == list(range(n))
+        tail_deg = (hub.indptr[1:] - hub.indptr[:-1]).long()
+        assert bool((tail_deg[s.row_order[s.n_skip:].long()] <= s.threshold).all())
+    # nothing is dense enough at a bar of 90 %
     assert not HubBlock(ip, idx, n, 256, 384, 0.9).ok
