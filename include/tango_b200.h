@@ -167,8 +167,8 @@ typedef struct tango_spmm_plan {
     int64_t n_units;
     const int32_t *heavy_rows; /* [n_heavy] */
     int64_t n_heavy;
-    int32_t *ws;               /* [n_heavy * nseg, ws_ld] int32 scratch */
-    int64_t ws_ld;             /* >= round_up(F, 16) */
+    int32_t *ws;               /* [n_heavy * nseg, ws_ld] int32 scratch, 16-byte aligned */
+    int64_t ws_ld;             /* >= round_up(F, 16), a multiple of 4 */
     int32_t split_threshold;
     const int32_t *row_order;  /* optional [n_rows]: warp w works on row row_order[w] (e.g. rows sorted by degree, so
                                   that the warps of a CTA finish together); NULL = natural order */
@@ -273,6 +273,31 @@ int tango_gat_edge_softmax_bwd(const int32_t *indptr, const int32_t *indices, co
                                const int32_t *row_order, int64_t n_block_rows, int64_t n_rows, const int8_t *elq,
                                const int8_t *erq, int h, const float *sl, const float *sr, float slope, const float *a,
                                const float *da, float *dz, float *dz_absmax, tango_stream_t stream);
+
+/* The same attention weights without an fp32 copy of them, in two steps.  The reference materialises the logits, the
+ * weights and their transposed int8 copy as E x H tensors (evaluation/test_gat.py:141-152, cuda/SPMM.py:38-47); here
+ * step 1 keeps only the softmax statistics of every destination row, row_m[v,h] = max_j z_j and
+ * row_inv[v,h] = 1 / sum_j exp(z_j - max) (fp32 [N, H]; rows without edges are left untouched), and a_absmax
+ * (optional, must hold 0) receives max|a| / 127 -- the largest weight of a row is exp(0) * row_inv, so the int8 scale
+ * of `a` is known before any weight is formed.  Step 2 writes aq[eid(j),h] = round_mode(exp(z_j - row_m) * row_inv /
+ * a_scale[0]) clamped to [-127,127], int8 [E, H] in edge-id order: exactly what quantising the fp32 weights of
+ * tango_gat_edge_softmax with that scale gives, rounding stream included (element index eid * H + h).  The
+ * gradient pass recomputes the weights from the statistics instead of reading them. */
+int tango_gat_edge_softmax_stats(const int32_t *indptr, const int32_t *indices, const int32_t *row_order,
+                                 int64_t n_block_rows, int64_t n_rows, const int8_t *elq, const int8_t *erq, int h,
+                                 const float *sl, const float *sr, float slope, float *row_m, float *row_inv,
+                                 float *a_absmax, tango_stream_t stream);
+int tango_gat_edge_softmax_quantized(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                                     const int32_t *row_order, int64_t n_block_rows, int64_t n_rows, const int8_t *elq,
+                                     const int8_t *erq, int h, const float *sl, const float *sr, float slope,
+                                     const float *row_m, const float *row_inv, const float *a_scale, int8_t *aq,
+                                     int mode, uint64_t seed, uint64_t call, const uint64_t *step,
+                                     tango_stream_t stream);
+int tango_gat_edge_softmax_bwd_stats(const int32_t *indptr, const int32_t *indices, const int32_t *edge_ids,
+                                     const int32_t *row_order, int64_t n_block_rows, int64_t n_rows, const int8_t *elq,
+                                     const int8_t *erq, int h, const float *sl, const float *sr, float slope,
+                                     const float *row_m, const float *row_inv, const float *da, float *dz,
+                                     float *dz_absmax, tango_stream_t stream);
 
 /* Edge softmax of plain fp32 scores: for every destination row v (CSC order) and head h
  *   a[eid(j),h] = softmax_j( z[eid(j),h] * zmul )     over the incoming edges j of v,

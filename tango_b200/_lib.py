@@ -79,6 +79,11 @@ _SIGS = {
     "tango_sddmm_elementwise": ([c_int, P, P, c_int64, P, c_int64, P, c_int64, c_int64, P, P, P, P, P], c_int),
     "tango_gat_edge_softmax": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P], c_int),
     "tango_gat_edge_softmax_bwd": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P, P, P], c_int),
+    "tango_gat_edge_softmax_stats": ([P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P, P], c_int),
+    "tango_gat_edge_softmax_quantized": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P, P, c_int,
+                                          c_uint64, c_uint64, P, P], c_int),
+    "tango_gat_edge_softmax_bwd_stats": ([P, P, P, P, c_int64, c_int64, P, P, c_int, P, P, c_float, P, P, P, P, P, P],
+                                         c_int),
     "tango_quantize_push": ([P, c_int64, c_int64, c_int64, P, P, P, c_int, c_int64, c_int64, c_int, c_uint64, c_uint64,
                              P, P], c_int),
     "tango_quantize_relu_grad_push": ([P, c_int64, P, c_int64, c_int64, c_int64, P, P, P, c_int, c_int64, c_int64, c_int,

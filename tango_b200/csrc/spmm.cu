@@ -536,20 +536,37 @@ __global__ void __launch_bounds__(128) incidence_contig_kernel(const SpmmArgs a)
     }
 }
 
-// Finishes the rows that were cut into units: one thread per (heavy row, feature byte).
+// Finishes the rows that went through the int32 scratch (rows cut into units, rows of the dense hub region): one
+// thread per (heavy row, four features) -- 128-bit scratch loads and output stores when the row pitch allows.
 __global__ void __launch_bounds__(256) spmm_finalize_kernel(const SpmmArgs a) {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int f4 = (a.f + 3) >> 2;
     float amax = 0.f;
-    if (t < a.n_heavy * a.f) {
-        const int64_t hs = t / a.f;
-        const int col = (int)(t - hs * a.f);
+    if (t < a.n_heavy * f4) {
+        const int64_t hs = t / f4;
+        const int col0 = (int)(t - hs * f4) << 2;
         const int64_t row = __ldg(a.heavy_rows + hs);
-        float facc = 0.f;
-        for (int k = 0; k < a.nseg; ++k)
-            facc = __fadd_rn(facc, __fmul_rn((float)a.ws[(hs * a.nseg + k) * a.ws_ld + col], __ldg(a.scales + k)));
-        facc = finish_value(facc, row, col, a);
-        a.out[row * a.ldo + col] = facc;
-        amax = fabsf(facc);
+        float facc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int k = 0; k < a.nseg; ++k) {
+            const int32_t *w = a.ws + (hs * a.nseg + k) * a.ws_ld + col0;
+            const int4 v = *reinterpret_cast<const int4 *>(w);       // ws_ld is a multiple of 16: always in bounds
+            const float sc = __ldg(a.scales + k);
+            facc[0] = __fadd_rn(facc[0], __fmul_rn((float)v.x, sc));
+            facc[1] = __fadd_rn(facc[1], __fmul_rn((float)v.y, sc));
+            facc[2] = __fadd_rn(facc[2], __fmul_rn((float)v.z, sc));
+            facc[3] = __fadd_rn(facc[3], __fmul_rn((float)v.w, sc));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            facc[i] = finish_value(facc[i], row, min(col0 + i, a.f - 1), a);
+            if (col0 + i < a.f) amax = fmaxf(amax, fabsf(facc[i]));
+        }
+        float *o = a.out + row * a.ldo + col0;
+        if (col0 + 4 <= a.f && (a.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) {
+            *reinterpret_cast<float4 *>(o) = make_float4(facc[0], facc[1], facc[2], facc[3]);
+        } else {
+            for (int i = 0; i < 4 && col0 + i < a.f; ++i) o[i] = facc[i];
+        }
     }
     if (a.out_absmax) {
         amax = warp_max(amax);
@@ -588,7 +605,7 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
     if (plan && plan->n_units > 0) {
         if (!plan->units || !plan->heavy_rows || !plan->ws || plan->ws_ld < a.f || plan->n_heavy <= 0)
             return TANGO_EINVAL;
-        if (!aligned(plan->units, 16)) return TANGO_EALIGN;
+        if (!aligned(plan->units, 16) || !aligned(plan->ws, 16) || plan->ws_ld % 4) return TANGO_EALIGN;
         a.units = plan->units; a.n_units = plan->n_units; a.heavy_rows = plan->heavy_rows;
         a.n_heavy = plan->n_heavy; a.ws = plan->ws; a.ws_ld = plan->ws_ld; a.split_threshold = plan->split_threshold;
         TANGO_CUDA_TRY(cudaMemsetAsync(a.ws, 0, sizeof(int32_t) * (size_t)(a.n_heavy * a.nseg * a.ws_ld), stream));
@@ -603,7 +620,7 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
             plan->n_skip_rows != plan->n_heavy || !plan->row_order || plan->ws_ld < a.f)
             return TANGO_EINVAL;
         if (a.ld % 16 || !aligned(a.feat, 16) || !aligned(plan->dense_a, 16) || !aligned(plan->dense_b, 16) ||
-            !aligned(plan->dense_units, 16))
+            !aligned(plan->dense_units, 16) || !aligned(plan->ws, 16) || plan->ws_ld % 4)
             return TANGO_EALIGN;
         if (plan->n_units == 0) {      // no unit set the scratch fields above
             a.heavy_rows = plan->heavy_rows; a.n_heavy = plan->n_heavy; a.ws = plan->ws; a.ws_ld = plan->ws_ld;
@@ -692,7 +709,7 @@ static int launch_spmm(SpmmArgs &a, const tango_spmm_plan *plan, cudaStream_t st
         TANGO_LAUNCH_CHECK();
     }
     if (a.n_units > 0 || dense) {
-        const int64_t fb = ceil_div(a.n_heavy * a.f, 256);
+        const int64_t fb = ceil_div(a.n_heavy * ((a.f + 3) / 4), 256);
         spmm_finalize_kernel<<<(unsigned)fb, 256, 0, stream>>>(a);
         TANGO_LAUNCH_CHECK();
     }
@@ -717,6 +734,7 @@ static bool try_incidence_contig(SpmmArgs &a, const tango_spmm_plan *plan, cudaS
     if (plan && plan->n_units > 0) {
         if (!plan->units || !plan->heavy_rows || !plan->ws || plan->ws_ld < f || plan->n_heavy <= 0 ||
             !aligned(plan->units, 16)) { rc = TANGO_EINVAL; return true; }
+        if (!aligned(plan->ws, 16) || plan->ws_ld % 4) { rc = TANGO_EALIGN; return true; }
         a.units = plan->units; a.n_units = plan->n_units; a.heavy_rows = plan->heavy_rows;
         a.n_heavy = plan->n_heavy; a.ws = plan->ws; a.ws_ld = plan->ws_ld; a.split_threshold = plan->split_threshold;
         if (cudaMemsetAsync(a.ws, 0, sizeof(int32_t) * (size_t)(a.n_heavy * a.ws_ld), stream) != cudaSuccess) {
@@ -743,7 +761,7 @@ static bool try_incidence_contig(SpmmArgs &a, const tango_spmm_plan *plan, cudaS
         if (cudaPeekAtLastError() != cudaSuccess) { rc = TANGO_ECUDA; return true; }
     }
     if (a.n_units > 0) {
-        const int64_t fb = ceil_div(a.n_heavy * a.f, 256);
+        const int64_t fb = ceil_div(a.n_heavy * ((a.f + 3) / 4), 256);
         spmm_finalize_kernel<<<(unsigned)fb, 256, 0, stream>>>(a);
         if (cudaPeekAtLastError() != cudaSuccess) rc = TANGO_ECUDA;
     }

@@ -236,6 +236,53 @@ class _gat_attention_fused(Function):
         return None, d_el, d_er, None
 
 
+class _gat_aggregate_fused(Function):
+    """Attention + aggregation of a GAT layer with no fp32 copy of the attention weights:
+
+        out[v,h,:] = sum_e Q(a)[e,h] * Q(ft)[src(e),h,:],   a = edge_softmax(leaky_relu(Q(el)[src] + Q(er)[dst]))
+
+    Same arithmetic, bit for bit, as _gat_attention_fused followed by spmm_u_mul_e (and hence the same int8 weights
+    as the reference's sddmm_u_add_v -> LeakyReLU -> edge_softmax -> quantize chain, evaluation/test_gat.py:141-152,
+    cuda/SPMM.py:38-47), but the weights exist only as the int8 tensor the aggregation reads: one pass keeps the
+    softmax statistics of every destination (which already fix the int8 scale), a second writes the int8 weights,
+    and the backward pass recomputes the weights from the statistics."""
+
+    @staticmethod
+    def forward(ctx, g, ft, el, er, slope):
+        mode, seed = config.mode_for("quantize"), config.seed()
+        n, h = el.shape[0], el.shape[1]
+        elq, sl = kernels.quantize(el.reshape(n, h), mode=mode, seed=seed, align=1)
+        erq, sr = kernels.quantize(er.reshape(n, h), mode=mode, seed=seed, align=1)
+        m, inv, sa = kernels.gat_edge_softmax_stats(g, elq, erq, sl, sr, slope)
+        sN = kernels.cuda_kernels.get_scale(ft)
+        call = kernels.next_call() if mode == kernels.ROUND_STOCHASTIC else 0
+        aq = kernels.gat_edge_softmax_quantized(g, elq, erq, sl, sr, m, inv, sa, slope, mode, seed, call)
+        Nq, _ = kernels.quantize(ft, sN, mode=mode, seed=seed)
+        out = kernels.spmm_u_mul_e_int8(g, Nq, aq, sN * sa)
+        ctx.g, ctx.slope, ctx.shapes = g, slope, (el.shape, er.shape)
+        ctx.save_for_backward(elq, erq, sl, sr, m, inv, sa, aq, Nq, sN)
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_out):
+        elq, erq, sl, sr, m, inv, sa, aq, Nq, sN = ctx.saved_tensors
+        g = ctx.g
+        mode, seed = config.mode_for("quantize"), config.seed()
+        dZq, sdZ = kernels.quantize(d_out, mode=mode, seed=seed)
+        d_ft = kernels.spmm_u_mul_e_int8(g, dZq, aq, sdZ * sa, True) if ctx.needs_input_grad[1] else None
+        d_el = d_er = None
+        if ctx.needs_input_grad[2] or ctx.needs_input_grad[3]:
+            da, _ = kernels.mySDDMM_int8(g, "dot", Nq, dZq, sN, sdZ, False)          # [E, H, 1] fp32
+            dz, sdz = kernels.gat_edge_softmax_bwd_stats(g, elq, erq, sl, sr, m, inv, da, ctx.slope)
+            dzq, sdz = kernels.quantize(dz, sdz, mode=mode, seed=seed, align=1)
+            if ctx.needs_input_grad[2]:
+                d_el = kernels.incidence_SPMM(g, dzq, sdz, True).view(ctx.shapes[0])
+            if ctx.needs_input_grad[3]:
+                d_er = kernels.incidence_SPMM(g, dzq, sdz).view(ctx.shapes[1])
+        return None, d_ft, d_el, d_er, None
+
+
 class QGATConv(nn.Module):
     """Graph attention layer on the quantized operators (evaluation/test_gat.py:30-169): QLinear projection,
     int8 u_add_v edge logits, LeakyReLU, edge softmax (fp32), int8 u_mul_e aggregation."""
@@ -280,14 +327,18 @@ class QGATConv(nn.Module):
         el = (ft * self.attn_l).sum(dim=-1).unsqueeze(-1)
         er = (ft * self.attn_r).sum(dim=-1).unsqueeze(-1)
         sa = None
-        if self._fused:
+        no_drop = not (self.training and self.attn_drop.p > 0)
+        if self._fused == "weights" or (self._fused is True and (get_attention or not no_drop)):
             a, sa = _gat_attention_fused.apply(graph, el, er, self._slope)
             if self.training and self.attn_drop.p > 0:
                 a, sa = self.attn_drop(a), None       # dropout rescales a: its absmax has to be taken again
-        else:
+        elif not self._fused:
             e = self.leaky_relu(sddmm_u_add_v.apply(graph, el, er))
             a = self.attn_drop(edge_softmax(graph, e))
-        rst = spmm_u_mul_e.apply(graph, ft, a, sa)
+        if self._fused is True and no_drop and not get_attention:
+            rst = _gat_aggregate_fused.apply(graph, ft, el, er, self._slope)      # no fp32 attention tensor at all
+        else:
+            rst = spmm_u_mul_e.apply(graph, ft, a, sa)
         if self.res_fc is not None:
             rst = rst + self.res_fc(h).view(*prefix, -1, self._out_feats)
         if self.bias is not None:

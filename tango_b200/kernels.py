@@ -598,6 +598,65 @@ def gat_edge_softmax_bwd(g, elq, erq, sl, sr, a, da, slope: float = 0.2, want_sc
     return (dz, sdz) if want_scale else dz
 
 
+def _gat_rows(g):
+    sched = _schedule(g, False)
+    order = sched.row_order if sched is not None else None
+    return order, (sched.n_block_rows if sched is not None else 0)
+
+
+def gat_edge_softmax_stats(g, elq, erq, sl, sr, slope: float = 0.2):
+    """Step 1 of the attention weights without an fp32 copy: per-row softmax statistics (m, inv) [N, H] and the int8
+    scale of the weights, max|a| / 127."""
+    indptr, indices, _ = _bundle(g, False)
+    h = elq.shape[1]
+    elq, erq = elq.reshape(elq.shape[0], -1).contiguous(), erq.reshape(erq.shape[0], -1).contiguous()
+    m = torch.empty((g.num_nodes(), h), dtype=torch.float32, device=elq.device)
+    inv = torch.empty_like(m)
+    sa = torch.zeros(1, dtype=torch.float32, device=elq.device)
+    order, nb = _gat_rows(g)
+    with torch.cuda.device(elq.device):
+        check(lib.tango_gat_edge_softmax_stats(_p(indptr), _p(indices), _p(order), nb, g.num_nodes(), _p(elq), _p(erq),
+                                               h, _p(sl), _p(sr), float(slope), _p(m), _p(inv), _p(sa), _stream()),
+              "gat_edge_softmax_stats")
+    launch_counter[0] += 1
+    return m, inv, sa
+
+
+def gat_edge_softmax_quantized(g, elq, erq, sl, sr, m, inv, sa, slope: float = 0.2, mode: int = ROUND_NEAREST,
+                               seed: int = 0, call: int = 0) -> torch.Tensor:
+    """Step 2: the int8 attention weights [E, H] in edge-id order, written once."""
+    indptr, indices, edge_ids = _bundle(g, False)
+    h = elq.shape[1]
+    elq, erq = elq.reshape(elq.shape[0], -1).contiguous(), erq.reshape(erq.shape[0], -1).contiguous()
+    aq = torch.empty((g.num_edges(), h), dtype=torch.int8, device=elq.device)
+    order, nb = _gat_rows(g)
+    with torch.cuda.device(elq.device):
+        check(lib.tango_gat_edge_softmax_quantized(_p(indptr), _p(indices), _p(edge_ids), _p(order), nb, g.num_nodes(),
+                                                   _p(elq), _p(erq), h, _p(sl), _p(sr), float(slope), _p(m), _p(inv),
+                                                   _p(sa), _p(aq), mode, seed, call, _p(config.step_counter()),
+                                                   _stream()), "gat_edge_softmax_quantized")
+    launch_counter[0] += 1
+    return aq
+
+
+def gat_edge_softmax_bwd_stats(g, elq, erq, sl, sr, m, inv, da, slope: float = 0.2):
+    """Gradient with respect to the edge logits, the weights recomputed from the statistics; returns (dz [E, H] fp32,
+    max|dz| / 127)."""
+    indptr, indices, edge_ids = _bundle(g, False)
+    h = elq.shape[1]
+    elq, erq = elq.reshape(elq.shape[0], -1).contiguous(), erq.reshape(erq.shape[0], -1).contiguous()
+    da = da.reshape(-1, h).contiguous()
+    dz = torch.empty_like(da)
+    sdz = torch.zeros(1, dtype=torch.float32, device=elq.device)
+    order, nb = _gat_rows(g)
+    with torch.cuda.device(elq.device):
+        check(lib.tango_gat_edge_softmax_bwd_stats(_p(indptr), _p(indices), _p(edge_ids), _p(order), nb, g.num_nodes(),
+                                                   _p(elq), _p(erq), h, _p(sl), _p(sr), float(slope), _p(m), _p(inv),
+                                                   _p(da), _p(dz), _p(sdz), _stream()), "gat_edge_softmax_bwd_stats")
+    launch_counter[0] += 1
+    return dz, sdz
+
+
 def edge_softmax_fwd(g, z: torch.Tensor, zmul: float = 1.0, want_scale: bool = False):
     """Softmax of fp32 edge scores z [E, H, ...] (times zmul) over the incoming edges of every destination; the
     reference calls dgl.ops.edge_softmax (evaluation/test_HGT.py:60).  Returns fp32 of z's shape."""
