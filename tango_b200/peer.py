@@ -71,16 +71,28 @@ class SharedBuffer:
         self.local = torch.as_tensor(_RawCuda(ptr.value, nbytes), device=device)
         self.ptrs_dev = torch.tensor(self.ptrs, dtype=torch.int64, device=device)
 
-    def release(self):
-        """Unmaps the peers' buffers and frees the own one (call on every rank, after a barrier)."""
+    def unmap_peers(self):
+        """First half of a release: closes this process's mappings of the other ranks' buffers."""
         with torch.cuda.device(self.device):
-            self.local = None
             for r, p in enumerate(self.ptrs):
                 if r != self.rank and p:
                     lib.tango_peer_close(p)
+        self.ptrs = [p if r == self.rank else None for r, p in enumerate(self.ptrs)]
+
+    def free_own(self):
+        """Second half: frees this rank's buffer.  CUDA IPC requires that every importer has closed its mapping
+        first, so all ranks must have finished unmap_peers() (a barrier) before any of them calls this."""
+        with torch.cuda.device(self.device):
+            self.local = None
             if self._own:
                 lib.tango_peer_free(self._own)
         self.ptrs, self._own = [], 0
+
+    def release(self):
+        """Unmap + free in one go: only for the error path of the constructor, where no peer holds a mapping of a
+        buffer whose set-up failed half-way, or for single-process use."""
+        self.unmap_peers()
+        self.free_own()
 
 
 class PeerTransport:
@@ -144,14 +156,17 @@ class PeerTransport:
         """Unmaps and frees every shared buffer (a collective: all ranks call it, with no kernel of theirs in flight).
         Tensors returned by `table()` must not be used afterwards."""
         torch.cuda.synchronize(self.device)
+        bufs = [buf for _tab, _ptrs, buf in self._tables.values()] + ([self._slots] if self._slots is not None else [])
         if dist.is_initialized():
-            dist.barrier(group=self.group)
-        for _tab, _ptrs, buf in self._tables.values():
-            buf.release()
+            dist.barrier(group=self.group)           # nobody launches anything that touches the buffers any more
+        for buf in bufs:
+            buf.unmap_peers()
+        if dist.is_initialized():
+            dist.barrier(group=self.group)           # every importer has closed its mappings: exporters may free
+        for buf in bufs:
+            buf.free_own()
         self._tables.clear()
-        if self._slots is not None:
-            self._slots.release()
-            self._slots = None
+        self._slots = None
 
     # ------------------------------------------------------------------------------------------------ gathered tables
     def table(self, key, rows: int, ld: int):

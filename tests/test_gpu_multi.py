@@ -52,7 +52,6 @@ def _worker(rank, world, port, out_dir, balance, scale_mode, transport="nccl", h
                 "grads": [p.grad.cpu() for p in model.parameters()],
                 "peer_status": dg.peer.status() if dg.peer is not None else 0}, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
-    dg.close()
     dist.destroy_process_group()
 
 
