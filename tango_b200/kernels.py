@@ -304,7 +304,10 @@ def _incidence_spmm(out, indptr, edge_ids, E, scale, sched=None):
     del keep
 
 
-ROWWISE_SDDMM_MIN_DEGREE = 0      # average edges per row from which mySDDMM_int8("dot") walks rows (0: always)
+# Average edges per row from which mySDDMM_int8("dot") walks rows.  On a graph with a handful of edges per row the
+# endpoint-list kernel (32 edges per warp, whatever their rows) measured faster than the row walk even with its
+# lane-group kernel for short rows (169,343 nodes / 1.3 M edges, 4 heads x 32: 0.060 ms against 0.069 ms).
+ROWWISE_SDDMM_MIN_DEGREE = 32
 
 
 def _sddmm_dot_rows(out, scaleOut, indptr, indices, edge_ids, U, V, scaleU, scaleV, sched=None) -> bool:
@@ -457,8 +460,8 @@ def mySDDMM_int8(g, op, U, V, scaleU, scaleV, isReduce, reverse=False):
     if (op == "dot" and src.numel() > 0 and src.numel() >= ROWWISE_SDDMM_MIN_DEGREE * g.num_nodes() and U.shape[1:] == V.shape[1:]
             and U.dim() == 3 and U.shape[0] == g.num_nodes() == V.shape[0]):
         # walk the rows of the fixed endpoint: V's row stays in registers, only U is gathered (half the gathered
-        # bytes of the endpoint-list kernel, and half its index stream); long rows get a warp, rows of a few edges a
-        # group of lanes each.
+        # bytes of the endpoint-list kernel, and half its index stream); long rows get a warp, the few short rows of
+        # such a graph a group of lanes each.
         indptr, indices, edge_ids = _bundle(g, reverse)
         done = _sddmm_dot_rows(out, scale, indptr, indices, edge_ids, U, V, scaleU, scaleV, _schedule(g, reverse))
     if not done:
