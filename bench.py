@@ -276,6 +276,9 @@ def run_ours(args):
     # Before any update: loss and an order-independent 64-bit checksum of the logits of the initial model.  With one
     # quantisation scale agreed by all ranks ("global" scale mode) every logit is bit-identical to the single-GPU
     # run, so both values must come out the same at 1, 2, 4 and 8 GPUs.
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()                 # the ranks finish partitioning seconds apart; their first rendezvous is bounded
     with torch.no_grad():
         logits0 = model(d_feats)
         ce0 = F.cross_entropy(logits0, d_labels, reduction="none")
@@ -288,6 +291,10 @@ def run_ours(args):
         step0 = {"loss_step0": float(loss0) / n,
                  "logits_step0_checksum": f"{int(sums[0]) & 0xFFFFFFFFFFFFFFFF:016x}",
                  "loss_rows_step0_checksum": f"{int(sums[1]) & 0xFFFFFFFFFFFFFFFF:016x}"}
+        if world > 1 and dg.peer is not None:
+            expired0 = torch.tensor([float(dg.peer.status() != 0)], device=dev)
+            dist.all_reduce(expired0)
+            step0["step0_peer_wait_expired"] = bool(float(expired0) != 0.0)   # if true the checksums mean nothing
         del logits0, ce0
 
     # The whole step (forward, loss, backward, gradient all-reduce, Adam) is captured once in a CUDA graph and
@@ -488,6 +495,11 @@ def run_ours(args):
         hub_info = {"rows": int(hb.rows.numel()), "cols": int(hb.cols.numel()), "tiles_128x128": hb.n_tiles,
                     "edges_in_region": hb.n_block_edges, "share_of_edges": hb.n_block_edges / n_edges,
                     "density": hb.density}
+    if world > 1 and dg.hubs.get("fwd") is not None:
+        hb = dg.hubs["fwd"]
+        hub_info = {"rank0_rows": int(hb.rows.numel()), "cols": int(hb.cols.numel()), "tiles_128x128": hb.n_tiles,
+                    "rank0_edges_in_region": hb.n_block_edges,
+                    "share_of_rank0_edges": hb.n_block_edges / max(1, int(dg.fwd.indices.numel())), "density": hb.density}
     secondary = None
     if world == 1 and not args.no_secondary and name == "gcn_c5":
         # outside the timed region: the same epoch with every edge gathered (no dense hub block), the GAT epoch on
