@@ -569,8 +569,8 @@ def run_ours(args):
     if world > 1:
         # The captured graph holds NCCL work and the peer-memory buffers are mapped by the other processes; all ranks
         # meet once more and then leave without tearing the communicator down under the graph.  (An orderly teardown
-        # -- graph, DistGraph.close(), destroy_process_group() -- is written but could not be exercised on 2+ GPUs
-        # before the GPU time of this build ran out, so the sequence that is known to work stays.)
+        # -- graph, DistGraph.close(), destroy_process_group() -- exists but has not been exercised on 2+ GPUs yet, so
+        # the sequence that is known to work stays.)
         dist.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()

@@ -22,6 +22,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 NAME = "tango_ref"
 SOURCES = ["quantization.cu", "SDDMM.cu", "QGEMM_backward.cu", "SPMM.cu"]
+DEFAULT_REFERENCE_ROOT = os.path.join(os.sep, "root", "reference")    # where the build container mounts the checkout
 
 
 def _cutlass_include():
@@ -40,7 +41,7 @@ def module_path():
     return None
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = True):
+def build(reference_root: str = DEFAULT_REFERENCE_ROOT, verbose: bool = True):
     src_dir = os.path.join(reference_root, "cuda", "src")
     if not os.path.isdir(src_dir):
         raise FileNotFoundError(f"no reference checkout at {reference_root}")
@@ -69,4 +70,4 @@ def load():
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REFERENCE_ROOT))
