@@ -146,7 +146,40 @@ def _worker(rank, world, port, out_dir):
     # transport selection is a host-side decision taken alike on all ranks: no CUDA device -> library collectives
     from tango_b200.dist import DistGraph
     dg = DistGraph(g, rank, world, transport="auto")
-    assert dg.transport == "nccl" and dg.peer is None and dg.n_local == dg.fwd.n_local
+    assert dg.transport == "nccl" and dg.peer is None and dg.n_local == dg.fwd.n_local and not dg.hubs
+    # an expired rendezvous on ONE rank reaches every rank through the gradient all-reduce (host logic of the peer
+    # transport's status word, with a stand-in for the transport: no GPU here)
+    from tango_b200._lib import TangoError
+    from tango_b200.dist import allreduce_grads
+    from tango_b200.peer import PeerTransport
+
+    class FakePeer:
+        status_word = PeerTransport.status_word
+        raise_if_expired = PeerTransport.raise_if_expired
+        reset_status = PeerTransport.reset_status
+
+        def __init__(self, expired):
+            self._status = torch.tensor([-4 if expired else 0], dtype=torch.int32)
+            self.group_status = torch.zeros(1)
+
+    lin = torch.nn.Linear(3, 2)
+    for p_ in lin.parameters():
+        p_.grad = torch.full_like(p_, float(rank + 1))
+    peer = FakePeer(expired=(rank == 1))
+    allreduce_grads(lin, peer=peer)
+    assert all(bool((p_.grad == 3.0).all()) for p_ in lin.parameters())        # 1 + 2: the gradients are untouched
+    assert float(peer.group_status) == 4.0
+    try:
+        peer.raise_if_expired()
+        raised = False
+    except TangoError:
+        raised = True
+    assert raised                                                               # on rank 0 too, whose own word is 0
+    peer.reset_status()
+    for p_ in lin.parameters():
+        p_.grad = torch.ones_like(p_)
+    allreduce_grads(lin, peer=peer)
+    peer.raise_if_expired()                                                     # nothing expired since the reset
     dist.destroy_process_group()
 
 
