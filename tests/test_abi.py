@@ -95,3 +95,50 @@ def test_ctypes_signatures_match_the_header():
             assert restype is ctypes.c_char_p
         else:
             assert restype is _ctype_of(ret), f"{name}: returns {ret}, bound as {restype.__name__}"
+
+
+def test_plan_struct_matches_the_header():
+    """tango_spmm_plan is passed by pointer from ctypes: its fields must have the names, order and C types of the
+    header's struct, or every pointer behind the first mismatch would be read from the wrong offset."""
+    from tango_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "tango_b200.h")).read()
+    body = re.search(r"typedef struct tango_spmm_plan \{(.*?)\} tango_spmm_plan;", text, flags=re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = []
+    for decl in body.split(";"):
+        decl = " ".join(decl.split())
+        if not decl:
+            continue
+        m = re.match(r"(.*?)(\w+)$", decl)
+        ctype, name = m.group(1).strip(), m.group(2)
+        if "*" in ctype:
+            want = ctypes.c_void_p
+        else:
+            want = {"int64_t": ctypes.c_int64, "int32_t": ctypes.c_int32, "int": ctypes.c_int}[ctype]
+        fields.append((name, want))
+    assert [(n, t) for n, t in _lib.SpmmPlan._fields_] == fields
+
+
+def test_dense_hub_region_arguments_are_validated_before_any_cuda_call():
+    from tango_b200 import _lib
+    L = _lib.lib
+    buf = (ctypes.c_int8 * 4096)()
+    base = ctypes.addressof(buf)
+    base = (base + 255) // 256 * 256                     # a 256-byte aligned address inside the buffer
+    plan = _lib.SpmmPlan()
+    plan.heavy_rows, plan.n_heavy, plan.ws, plan.ws_ld = base, 128, base, 16
+    plan.row_order, plan.n_long_rows = base, 128
+    plan.dense_a, plan.dense_n_tiles, plan.dense_units, plan.dense_n_units = base, 1, base, 1
+    plan.dense_rows, plan.dense_cols, plan.dense_n_cols, plan.dense_b = 128, base, 128, base
+    plan.n_skip_rows = 64                                # must equal n_heavy with a dense region
+    args = (base, base, 256, 1, base, 16, 16, base, None, None, 0, base, 16, None)
+    assert L.tango_spmm_copy_u(*args, ctypes.byref(plan), None) == -1
+    plan.n_skip_rows = 128
+    plan.dense_n_cols = 100                              # not a multiple of 128
+    assert L.tango_spmm_copy_u(*args, ctypes.byref(plan), None) == -1
+    plan.dense_n_cols = 128
+    plan.dense_a = base + 8                              # tiles must be 16-byte aligned
+    assert L.tango_spmm_copy_u(*args, ctypes.byref(plan), None) == -2
+    # the quantised attention entry point rejects an unknown rounding mode outright
+    assert L.tango_gat_edge_softmax_quantized(None, None, None, None, 0, 0, None, None, 4, None, None, 0.2, None, None,
+                                              None, None, 7, 0, 0, None, None) == -1
