@@ -390,3 +390,58 @@ def test_hub_block_partitions_the_edges_exactly():
         assert bool((tail_deg[s.row_order[s.n_skip:].long()] <= s.threshold).all())
     # nothing is dense enough at a bar of 90 %
     assert not HubBlock(ip, idx, n, 256, 384, 0.9).ok
+
+
+def _emulate_hub_aggregation(hub, feats_i64):
+    """What the kernels do with a HubBlock, in NumPy: every GEMM work item adds its run of stored tiles times the
+    matching 128-row slices of the packed hub features into the scratch rows of its row tile; the remaining edges are
+    gathered; both meet as exact integers."""
+    T = 128
+    n_rows = hub.indptr.numel() - 1
+    acc = np.zeros((n_rows, feats_i64.shape[1]), dtype=np.int64)
+    packed = feats_i64[hub.cols.numpy().astype(np.int64)]                       # gather_rows_kernel
+    dense = hub.dense.numpy().astype(np.int64)
+    rows = hub.rows.numpy().astype(np.int64)
+    for rt, t0, k0, cnt in hub.units.tolist():                                  # igemm_kernel, tile-list mode
+        part = np.zeros((T, feats_i64.shape[1]), dtype=np.int64)
+        for t in range(cnt):
+            part += dense[(t0 + t) * T:(t0 + t + 1) * T] @ packed[(k0 + t) * T:(k0 + t + 1) * T]
+        acc[rows[rt * T:(rt + 1) * T]] += part
+    ip = hub.indptr.numpy().astype(np.int64)
+    idx = hub.indices.numpy().astype(np.int64)
+    np.add.at(acc, np.repeat(np.arange(n_rows), np.diff(ip)), feats_i64[idx])    # the gather kernels on the remainder
+    return acc
+
+
+def test_hub_region_work_items_reproduce_the_aggregation():
+    g = rmat_graph(3000, 90000, 7, device="cpu")
+    ip, idx, _ = g.adj_csc
+    rng = np.random.default_rng(0)
+    nq = rng.integers(-127, 128, (3000, 24)).astype(np.int64)
+    want = O.spmm_copy_u_acc(ip.numpy().astype(np.int64), idx.numpy().astype(np.int64), nq)
+    for caps in ((512, 640, 0.0), (2048, 2048, 0.03)):
+        hub = HubBlock(ip, idx, 3000, *caps)
+        assert hub.ok and hub.units.shape[0] >= hub.kend.numel() - int((hub.kend == 0).sum())
+        np.testing.assert_array_equal(_emulate_hub_aggregation(hub, nq), want)
+
+
+def test_hub_region_on_a_row_partition_reproduces_the_aggregation():
+    """The multi-GPU form: every rank builds the hub region of ITS rows over the columns of the gathered table (rank
+    k's rows at k * shard_rows); emulated in NumPy, the ranks together give the unpartitioned aggregation."""
+    n, world = 2500, 3
+    g = rmat_graph(n, 80000, 9, device="cpu")
+    ip, idx, _ = g.adj_csc
+    rng = np.random.default_rng(1)
+    nq = rng.integers(-127, 128, (n, 16)).astype(np.int64)
+    want = O.spmm_copy_u_acc(ip.numpy().astype(np.int64), idx.numpy().astype(np.int64), nq)
+    order = torch.argsort(g.in_degrees() + g.out_degrees(), descending=True, stable=True)
+    parts = [RowPartition(ip, idx, None, n, r, world, None, "dealt", order) for r in range(world)]
+    shard = parts[0].shard_rows
+    table = np.zeros((world * shard, 16), dtype=np.int64)                        # what the exchange leaves on every rank
+    for r, p in enumerate(parts):
+        table[r * shard:r * shard + p.n_local] = nq[p.local_ids.numpy()]
+    for p in parts:
+        hub = HubBlock(p.indptr_flat, p.indices, world * shard, 256, 384, 0.0)
+        assert hub.ok and hub.n_block_edges > 0
+        got = _emulate_hub_aggregation(hub, table)
+        np.testing.assert_array_equal(got, want[p.local_ids.numpy()])
