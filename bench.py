@@ -527,7 +527,9 @@ def run_ours(args):
         del model, opt, d_feats, stage
         torch.cuda.empty_cache()
         # each extra is best effort: a failure here must not lose the headline line
-        for key, fn in (("gat_c4", lambda: _gat_epoch(g, dev)), ("cache_ablation", lambda: _cache_ablation(dev))):
+        for key, fn in (("gat_c4", lambda: _gat_epoch(g, dev)),
+                        ("gat_c4_int8_attention", lambda: _gat_epoch(g, dev, "int8")),
+                        ("cache_ablation", lambda: _cache_ablation(dev))):
             try:
                 secondary[key] = fn()
             except Exception as exc:                      # noqa: BLE001
@@ -577,16 +579,18 @@ def run_ours(args):
         os._exit(0)
 
 
-def _gat_epoch(g, dev):
+def _gat_epoch(g, dev, fused=True):
     """Epoch (forward + loss + backward + Adam) of the 2-layer GAT (4 heads x 64, then 1 head x 41 classes) on the
-    same 114.6 M-edge graph, launched kernel by kernel; CUDA events around 5 steps after 3 warm-up steps."""
+    same 114.6 M-edge graph, launched kernel by kernel; CUDA events around 5 steps after 3 warm-up steps.
+    fused=True: the attention weights are written as fp32 [E, H] by the fused softmax kernel; fused="int8": they only
+    ever exist as the int8 tensor the aggregation reads."""
     import torch
     import torch.nn.functional as F
     from tango_b200 import kernels as K
     from tango_b200.gnn import GAT
     n, _, in_feats, hidden, classes, _ = WORKLOADS["gat_c4"]
     torch.manual_seed(6)
-    model = GAT(g, 2, in_feats, hidden, classes, [4, 1]).to(dev)
+    model = GAT(g, 2, in_feats, hidden, classes, [4, 1], fused=fused).to(dev)
     opt = torch.optim.Adam(model.parameters(), lr=1e-2, weight_decay=5e-4)
     h_feats, h_labels = make_inputs("gat_c4", slice(0, n), False)
     feats, labels = h_feats.to(dev), h_labels.to(dev)
@@ -610,6 +614,7 @@ def _gat_epoch(g, dev):
     torch.cuda.synchronize()
     return {"metric": "gat_epoch_ms", "value": e0.elapsed_time(e1) / 5, "unit": "ms", "steps": 5, "warmup": 3,
             "layers": f"{in_feats}-4x{hidden}-{classes}", "edges": g.num_edges(), "loss": float(loss.detach()),
+            "attention_weights": "int8 only" if fused == "int8" else "fp32 [E, H] + int8 copy",
             "gpu_launches_per_step": K.launch_counter[0] // 5, "cuda_graph": False, "status_word": K.device_status()}
 
 

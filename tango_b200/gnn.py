@@ -327,17 +327,21 @@ class QGATConv(nn.Module):
         el = (ft * self.attn_l).sum(dim=-1).unsqueeze(-1)
         er = (ft * self.attn_r).sum(dim=-1).unsqueeze(-1)
         sa = None
-        no_drop = not (self.training and self.attn_drop.p > 0)
-        if self._fused == "weights" or (self._fused is True and (get_attention or not no_drop)):
-            a, sa = _gat_attention_fused.apply(graph, el, er, self._slope)
-            if self.training and self.attn_drop.p > 0:
-                a, sa = self.attn_drop(a), None       # dropout rescales a: its absmax has to be taken again
-        elif not self._fused:
-            e = self.leaky_relu(sddmm_u_add_v.apply(graph, el, er))
-            a = self.attn_drop(edge_softmax(graph, e))
-        if self._fused is True and no_drop and not get_attention:
-            rst = _gat_aggregate_fused.apply(graph, ft, el, er, self._slope)      # no fp32 attention tensor at all
+        # fused="int8": the attention weights never exist in fp32 (needs no attention dropout and no caller that wants
+        # the weights back); fused=True: one fused softmax pass writes them as fp32 [E, H]; fused=False: the
+        # reference's operator-by-operator chain
+        int8_path = (self._fused == "int8" and not get_attention
+                     and not (self.training and self.attn_drop.p > 0))
+        if int8_path:
+            rst = _gat_aggregate_fused.apply(graph, ft, el, er, self._slope)
         else:
+            if self._fused:
+                a, sa = _gat_attention_fused.apply(graph, el, er, self._slope)
+                if self.training and self.attn_drop.p > 0:
+                    a, sa = self.attn_drop(a), None   # dropout rescales a: its absmax has to be taken again
+            else:
+                e = self.leaky_relu(sddmm_u_add_v.apply(graph, el, er))
+                a = self.attn_drop(edge_softmax(graph, e))
             rst = spmm_u_mul_e.apply(graph, ft, a, sa)
         if self.res_fc is not None:
             rst = rst + self.res_fc(h).view(*prefix, -1, self._out_feats)
@@ -345,7 +349,7 @@ class QGATConv(nn.Module):
             rst = rst + self.bias.view(*((1,) * len(prefix)), self._num_heads, self._out_feats)
         if self.activation:
             rst = self.activation(rst)
-        return (rst, a) if get_attention else rst
+        return (rst, a) if get_attention else rst      # (get_attention never takes the int8 path, so `a` exists)
 
 
 class GAT(nn.Module):
