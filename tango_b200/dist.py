@@ -12,6 +12,7 @@ one-CTA rendezvous kernel for the barrier and the scale agreement (tango_b200.pe
 """
 from __future__ import annotations
 
+import warnings
 from typing import Optional
 
 import torch
@@ -101,7 +102,14 @@ class DistGraph:
                 hub = HubBlock(part.indptr_flat, part.indices, world * self.shard_rows, side, side,
                                HUB_BLOCK_MIN_DENSITY)
                 if hub.ok:
-                    self.hubs[key] = hub
+                    from . import kernels
+                    # purely local (no collective): a rank that drops its region still computes the same bits
+                    if kernels.hub_self_check(hub, part.indptr_flat, part.indices, part.schedule_flat,
+                                              world * self.shard_rows):
+                        self.hubs[key] = hub
+                    else:
+                        warnings.warn(f"rank {rank}: dense hub region of the {key} aggregation did not reproduce the "
+                                      "gathered result; not used", RuntimeWarning)
         self.in_norm = g.in_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
         self.out_norm = g.out_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
         if transport == "peer" and world > 1:

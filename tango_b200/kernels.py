@@ -273,6 +273,29 @@ def _csr_spmm(out, indptr, indices, U, scaleU, sched=None, nseg=1, row_scale=Non
     del keep
 
 
+def hub_self_check(hub, indptr, indices, plain_sched, n_feature_rows: int, f: int = 64) -> bool:
+    """Aggregates one random int8 table twice -- every edge gathered, and with the dense hub region `hub` on the tensor
+    cores -- and says whether the two results are the same bits (they must be: both are exact int32 sums, and with a
+    scale of 1 the fp32 outputs are those integers).  Run once when a hub region is built, so that a region that does
+    not reproduce the plain aggregation on this graph, device or driver is dropped instead of used."""
+    dev = indptr.device
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    q = torch.randint(-127, 128, (n_feature_rows, f), dtype=torch.int8, device=dev, generator=gen)
+    one = torch.ones(1, dtype=torch.float32, device=dev)
+    n_rows = indptr.numel() - 1
+    ref = torch.empty((n_rows, f), dtype=torch.float32, device=dev)
+    got = torch.full((n_rows, f), float("nan"), dtype=torch.float32, device=dev)
+    launches, status = launch_counter[0], device_status(dev)
+    try:
+        _csr_spmm(ref, indptr, indices, q, one, plain_sched, 1)
+        _csr_spmm(got, hub.indptr, hub.indices, q, one, hub.schedule, 1)
+        ok = bool(torch.equal(ref, got)) and device_status(dev) == status     # no bounded wait of the GEMM expired
+    except _lib.TangoError:
+        ok = False
+    launch_counter[0] = launches
+    return ok
+
+
 def _u_mul_e_spmm(indptr, indices, edge_ids, N, E, scale, sched=None):
     """N int8 [Nn, H, D]; E int8 [nnz or E, H] (edge-id order when edge_ids is given, CSR-slot order otherwise)."""
     assert N.dim() == 3

@@ -1,6 +1,8 @@
 """graph_preprocess of the reference's cuda/util.py:5-11, for the DGL-free `Graph`."""
 from __future__ import annotations
 
+import warnings
+
 from . import config
 from .graph import HUB_BLOCK_MIN_DENSITY, Graph, HubBlock, SpmmSchedule
 
@@ -25,5 +27,10 @@ def graph_preprocess(graph: Graph, hub_block=None) -> Graph:
         if side > 0 and (forced or graph.num_edges() >= HUB_BLOCK_MIN_EDGES):
             hub = HubBlock(indptr, indices, graph.num_nodes(), side, side, 0.0 if forced else HUB_BLOCK_MIN_DENSITY)
             if hub.ok:
-                graph._hubs[fmt] = hub
+                from . import kernels
+                if kernels.hub_self_check(hub, indptr, indices, graph._plans[fmt], graph.num_nodes()):
+                    graph._hubs[fmt] = hub
+                else:
+                    warnings.warn(f"dense hub region of the {fmt} aggregation did not reproduce the gathered result; "
+                                  "not used", RuntimeWarning)
     return graph

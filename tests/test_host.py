@@ -445,3 +445,30 @@ def test_hub_region_on_a_row_partition_reproduces_the_aggregation():
         assert hub.ok and hub.n_block_edges > 0
         got = _emulate_hub_aggregation(hub, table)
         np.testing.assert_array_equal(got, want[p.local_ids.numpy()])
+
+
+def test_hub_self_check_accepts_a_faithful_region_and_rejects_a_lossy_one(monkeypatch):
+    """kernels.hub_self_check compares the aggregation with and without the dense hub region on one random table.
+    With the native call replaced by the NumPy emulation it must say yes; with an emulation that forgets the dense
+    part (what a broken GEMM pass would amount to) it must say no."""
+    from tango_b200 import kernels as K
+    g = rmat_graph(2000, 60000, 3, device="cpu")
+    ip, idx, _ = g.adj_csc
+    hub = HubBlock(ip, idx, 2000, 512, 512, 0.0)
+    assert hub.ok and hub.n_block_edges > 0
+
+    def fake(drop_dense):
+        def _csr_spmm(out, indptr, indices, U, scaleU, sched=None, nseg=1, *a, **k):
+            feats = U.numpy().astype(np.int64)
+            if getattr(sched, "hub", None) is not None and not drop_dense:
+                acc = _emulate_hub_aggregation(sched.hub, feats)
+            else:
+                acc = O.spmm_copy_u_acc(indptr.numpy().astype(np.int64), indices.numpy().astype(np.int64), feats)
+            out.copy_(torch.from_numpy(acc.astype(np.float32)))
+        return _csr_spmm
+
+    assert hub.schedule.hub is hub
+    monkeypatch.setattr(K, "_csr_spmm", fake(False))
+    assert K.hub_self_check(hub, ip, idx, SpmmSchedule(ip), 2000, f=16)
+    monkeypatch.setattr(K, "_csr_spmm", fake(True))
+    assert not K.hub_self_check(hub, ip, idx, SpmmSchedule(ip), 2000, f=16)
