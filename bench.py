@@ -1095,7 +1095,22 @@ def main():
     ap.add_argument("--suite", default=None, choices=["primitives", "dist_phases"],
                     help="per-primitive numbers on the QLinear and SpMM/SDDMM configurations instead of the epoch")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, sddmm_rows, gemm) and exit")
+    ap.add_argument("--deadline", type=int, default=1500,
+                    help="seconds after which a run that has not finished gives up with exit code 124 (0 = never): "
+                         "a rank that waits for one that died must not block whatever launched it")
     args = ap.parse_args()
+    if args.deadline > 0:
+        import threading
+
+        def give_up():
+            sys.stderr.write(f"bench.py: not finished after {args.deadline} s "
+                             f"(rank {os.environ.get('RANK', '0')}): giving up\n")
+            sys.stderr.flush()
+            os._exit(124)
+
+        watchdog = threading.Timer(args.deadline, give_up)
+        watchdog.daemon = True
+        watchdog.start()
     if args.suite == "primitives":
         run_primitives(args)
     elif args.suite == "dist_phases":

@@ -2,6 +2,7 @@
 NVLS is switched off for these child processes."""
 import os
 import socket
+import time
 
 import pytest
 import torch
@@ -14,6 +15,23 @@ def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
+
+
+def _spawn_with_deadline(fn, args, world, deadline_s=300):
+    """mp.spawn, but a rank that never comes back fails the test instead of blocking the whole run: after the
+    deadline the children started here (and only those) are terminated."""
+    ctx = mp.spawn(fn, args=args, nprocs=world, join=False)
+    t0 = time.monotonic()
+    while not ctx.join(timeout=5):          # raises if a child raised (and ends the others)
+        if time.monotonic() - t0 > deadline_s:
+            for p in ctx.processes:
+                if p.is_alive():
+                    p.terminate()
+            for p in ctx.processes:
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
+            pytest.fail(f"ranks still running after {deadline_s} s")
 
 
 def _worker(rank, world, port, out_dir, balance, scale_mode, transport="nccl", hub=0):
@@ -67,8 +85,7 @@ def test_two_gpu_gcn_matches_single_gpu(cuda, tmp_path, balance, scale_mode, tra
     from tango_b200.gnn import GCN
     from tango_b200.graph import rmat_graph
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), balance, scale_mode, transport, hub), nprocs=world,
-             join=True)
+    _spawn_with_deadline(_worker, (world, _free_port(), str(tmp_path), balance, scale_mode, transport, hub), world)
     n = 5003
     g = rmat_graph(n, 120000, 17, device="cuda")
     T.graph_preprocess(g)
