@@ -1095,10 +1095,13 @@ def main():
     ap.add_argument("--suite", default=None, choices=["primitives", "dist_phases"],
                     help="per-primitive numbers on the QLinear and SpMM/SDDMM configurations instead of the epoch")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (spmm_f256, spmm_f48, sddmm_rows, gemm) and exit")
-    ap.add_argument("--deadline", type=int, default=1500,
-                    help="seconds after which a run that has not finished gives up with exit code 124 (0 = never): "
-                         "a rank that waits for one that died must not block whatever launched it")
+    ap.add_argument("--deadline", type=int, default=None,
+                    help="seconds after which a run that has not finished gives up with exit code 124 (0 = never; "
+                         "default 1500 for the GPU arm, never for the CPU reference arm): a rank that waits for one "
+                         "that died must not block whatever launched it")
     args = ap.parse_args()
+    if args.deadline is None:
+        args.deadline = 0 if args.impl == "reference" else 1500
     if args.deadline > 0:
         import threading
 
