@@ -99,17 +99,22 @@ class DistGraph:
         side = config.hub_block()
         if scale_mode == "global" and side > 0 and g.device.type == "cuda" and g.num_edges() >= HUB_BLOCK_MIN_EDGES:
             for key, part in (("fwd", self.fwd), ("bwd", self.bwd)):
-                hub = HubBlock(part.indptr_flat, part.indices, world * self.shard_rows, side, side,
-                               HUB_BLOCK_MIN_DENSITY)
-                if hub.ok:
-                    from . import kernels
-                    # purely local (no collective): a rank that drops its region still computes the same bits
-                    if kernels.hub_self_check(hub, part.indptr_flat, part.indices, part.schedule_flat,
-                                              world * self.shard_rows):
+                # The region is an optimisation with a bit-identical result, decided per rank with no collective: a
+                # rank that cannot build it, or whose region does not reproduce the gathered aggregation, goes
+                # without (and says so) while the other ranks keep theirs.
+                from . import kernels
+                try:
+                    hub = HubBlock(part.indptr_flat, part.indices, world * self.shard_rows, side, side,
+                                   HUB_BLOCK_MIN_DENSITY)
+                    if hub.ok and kernels.hub_self_check(hub, part.indptr_flat, part.indices, part.schedule_flat,
+                                                         world * self.shard_rows):
                         self.hubs[key] = hub
-                    else:
+                    elif hub.ok:
                         warnings.warn(f"rank {rank}: dense hub region of the {key} aggregation did not reproduce the "
                                       "gathered result; not used", RuntimeWarning)
+                except (RuntimeError, AssertionError, IndexError, ValueError) as exc:
+                    warnings.warn(f"rank {rank}: dense hub region of the {key} aggregation not built: {exc}",
+                                  RuntimeWarning)
         self.in_norm = g.in_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
         self.out_norm = g.out_degrees()[self.local_ids].float().clamp(min=1).pow(-0.5).contiguous()
         if transport == "peer" and world > 1:
