@@ -37,22 +37,22 @@ def test_rendezvous_wait_expires_reports_and_recovers(cuda):
         torch.cuda.synchronize()
         return float(out)
 
-    # round 1: rank 1 never arrives -> rank 0 gives up after the limit, says so, and returns its own value
+    # rendezvous 1: rank 1 never arrives -> rank 0 gives up after the limit, says so, and returns its own value
     got = call(0, 3.0)
     assert int(status[0]) == TANGO_ETIMEOUT
     assert got == 3.0
     assert int(rnd[0]) == 1
-    # the late rank arrives in round 1: rank 0's word is there, so it neither waits long nor reports anything
+    # the late rank arrives in rendezvous 1: rank 0's word is there, so it neither waits long nor reports anything
     got = call(1, 7.0)
     assert int(status[1]) == 0 and got == 7.0
-    # round 2: the other rank's word is in place before rank 0 calls (written here as the peer's kernel would) ->
-    # the round completes, the maximum is taken over both ranks, and the status word is left alone
+    # rendezvous 2: the other rank's word is in place before rank 0 calls (written here as the peer's kernel would) ->
+    # the rendezvous completes, the maximum is taken over both ranks, and the status word is left alone
     status[0].zero_()
     for s in slots:
         s[(2 & 1) * world + 1] = _word(2, 11.0)
     got = call(0, 5.0)
     assert int(status[0]) == 0 and got == 11.0 and int(rnd[0]) == 2
-    # a word that still carries an older round does not take part in the maximum
+    # a word that still carries an older rendezvous number does not take part in the maximum
     status[0].zero_()
-    got = call(0, 2.0)            # round 3, bank 1 holds rank 1's round-1 word (7.0): expires, 7.0 must be ignored
+    got = call(0, 2.0)            # rendezvous 3, bank 1 holds rank 1's word of rendezvous 1 (7.0): expires, 7.0 must be ignored
     assert int(status[0]) == TANGO_ETIMEOUT and got == 2.0
